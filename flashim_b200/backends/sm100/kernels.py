@@ -1,0 +1,507 @@
+"""The sm_100a CUDA backend: ``torch.library`` custom ops around the C ABI of ``libflashim_sm100.so`` and their
+registration into the op registry (the role flashim/backends/cuda/conv.py plays for FlashIM's JIT CUDA kernels: ctypes
+launch on torch's current stream, non-zero return code -> ``RuntimeError``, fake implementations for tracing).
+
+Implementations are registered as ``"sm100"`` for compute capability 10.0 only and require ``Feature.TCGEN05`` and
+``Feature.SM100A_KERNELS``; :func:`register` takes the registry to register into, so the same code can register into
+FlashIM's own ``flashim.ops`` (see ``flashim_b200.integration``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from collections import OrderedDict
+
+import torch
+from torch import Tensor
+
+from flashim_b200 import _native
+from flashim_b200.quant.tensor import (
+    BLOCK, Int8Tensor, QuantizedTensor, padded_channels, swizzle_scales, swizzled_scale_bytes,
+)
+
+E4M3 = torch.float8_e4m3fn
+_IN_DTYPES = {torch.float32: _native.DTYPE_F32, torch.bfloat16: _native.DTYPE_BF16}
+_CHECK_EVERY_CALL = os.environ.get("FLASHIM_B200_CHECK", "0") == "1"
+
+# ---- status word --------------------------------------------------------------------------------------------------------
+_STATUS: dict[int, Tensor] = {}
+
+
+def status_word(device: torch.device) -> Tensor:
+    """The per-device int32 word the kernels' bounded waits report to (zero while everything is healthy)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _STATUS.get(index)
+    if word is None:
+        word = _STATUS[index] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+    return word
+
+
+def check_status(device: torch.device | str | None = None) -> None:
+    """Synchronise and raise if a kernel on ``device`` abandoned work because one of its waits ran out."""
+    device = torch.device(device if device is not None else "cuda")
+    word = status_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        raise RuntimeError(f"sm100 kernel gave up waiting: {_native.STATUS.get(code, hex(code))}; outputs are invalid")
+
+
+def _stream(t: Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _finish(code: int, what: str, device: torch.device) -> None:
+    _native.check(code, what)
+    if _CHECK_EVERY_CALL:
+        check_status(device)
+
+
+def _nhwc(value: Tensor) -> Tensor:
+    """``[B, C, H, W]`` -> its bf16 ``[B, H, W, C]`` memory (zero-copy for channels-last bf16 input)."""
+    if value.dtype != torch.bfloat16:
+        value = value.to(torch.bfloat16)
+    pixels = value.permute(0, 2, 3, 1)
+    if not pixels.is_contiguous() or pixels.data_ptr() % 16:
+        pixels = pixels.contiguous() if not pixels.is_contiguous() else pixels.clone()
+    return pixels
+
+
+# ---- custom ops: depthwise -------------------------------------------------------------------------------------------
+
+
+@torch.library.custom_op("flashim_b200::dw5x5_bf16", mutates_args=())
+def dw5x5_bf16(pixels: Tensor, weight: Tensor, bias: Tensor, act: int) -> Tensor:
+    b, h, w, c = pixels.shape
+    out = torch.empty((b, h, w, c), device=pixels.device, dtype=torch.bfloat16)
+    code = _native.library().fim_dw5x5_bf16(
+        pixels.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), b, h, w, c, act,
+        status_word(pixels.device).data_ptr(), _stream(pixels))
+    _finish(code, f"dw5x5_bf16 {tuple(pixels.shape)}", pixels.device)
+    return out
+
+
+@dw5x5_bf16.register_fake
+def _(pixels, weight, bias, act):
+    return pixels.new_empty(pixels.shape, dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("flashim_b200::dw5x5_mxfp8", mutates_args=())
+def dw5x5_mxfp8(pixels: Tensor, weight: Tensor, bias: Tensor, act: int, swizzled: bool) -> tuple[Tensor, Tensor]:
+    b, h, w, c = pixels.shape
+    rows = b * h * w
+    out = torch.empty((rows, c), device=pixels.device, dtype=E4M3)
+    if swizzled:
+        scales = torch.zeros(swizzled_scale_bytes(rows, c // BLOCK), device=pixels.device, dtype=torch.uint8)
+    else:
+        scales = torch.empty((rows, c // BLOCK), device=pixels.device, dtype=torch.uint8)
+    code = _native.library().fim_dw5x5_mxfp8(
+        pixels.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), scales.data_ptr(), int(swizzled), b, h, w, c,
+        act, status_word(pixels.device).data_ptr(), _stream(pixels))
+    _finish(code, f"dw5x5_mxfp8 {tuple(pixels.shape)}", pixels.device)
+    return out, scales
+
+
+@dw5x5_mxfp8.register_fake
+def _(pixels, weight, bias, act, swizzled):
+    b, h, w, c = pixels.shape
+    rows = b * h * w
+    scales = pixels.new_empty((swizzled_scale_bytes(rows, c // BLOCK),) if swizzled else (rows, c // BLOCK), dtype=torch.uint8)
+    return pixels.new_empty((rows, c), dtype=E4M3), scales
+
+
+@torch.library.custom_op("flashim_b200::dw5x5_relu_int8", mutates_args=())
+def dw5x5_relu_int8(pixels: Tensor, weight: Tensor, bias: Tensor, scale: Tensor) -> Tensor:
+    b, h, w, c = pixels.shape
+    out = torch.empty((b * h * w, c), device=pixels.device, dtype=torch.int8)
+    code = _native.library().fim_dw5x5_relu_int8(
+        pixels.data_ptr(), weight.data_ptr(), bias.data_ptr(), scale.data_ptr(), out.data_ptr(), b, h, w, c,
+        status_word(pixels.device).data_ptr(), _stream(pixels))
+    _finish(code, f"dw5x5_relu_int8 {tuple(pixels.shape)}", pixels.device)
+    return out
+
+
+@dw5x5_relu_int8.register_fake
+def _(pixels, weight, bias, scale):
+    b, h, w, c = pixels.shape
+    return pixels.new_empty((b * h * w, c), dtype=torch.int8)
+
+
+# ---- custom ops: quantisers -------------------------------------------------------------------------------------------
+
+
+@torch.library.custom_op("flashim_b200::quantize_mxfp8_static", mutates_args=())
+def quantize_mxfp8_static(value: Tensor, exponent: Tensor) -> Tensor:
+    channels = value.shape[-1]
+    rows = value.numel() // channels
+    out = torch.empty((*value.shape[:-1], padded_channels(channels)), device=value.device, dtype=E4M3)
+    code = _native.library().fim_quantize_mxfp8_static(
+        value.data_ptr(), _IN_DTYPES[value.dtype], exponent.data_ptr(), out.data_ptr(), rows, channels, _stream(value))
+    _finish(code, f"quantize_mxfp8_static {tuple(value.shape)}", value.device)
+    return out
+
+
+@quantize_mxfp8_static.register_fake
+def _(value, exponent):
+    return value.new_empty((*value.shape[:-1], padded_channels(value.shape[-1])), dtype=E4M3)
+
+
+@torch.library.custom_op("flashim_b200::quantize_mxfp8_dynamic", mutates_args=())
+def quantize_mxfp8_dynamic(value: Tensor, swizzled: bool) -> tuple[Tensor, Tensor]:
+    channels = value.shape[-1]
+    rows = value.numel() // channels
+    out = torch.empty(value.shape, device=value.device, dtype=E4M3)
+    if swizzled:
+        scales = torch.zeros(swizzled_scale_bytes(rows, channels // BLOCK), device=value.device, dtype=torch.uint8)
+    else:
+        scales = torch.empty((rows, channels // BLOCK), device=value.device, dtype=torch.uint8)
+    code = _native.library().fim_quantize_mxfp8_dynamic(
+        value.data_ptr(), _IN_DTYPES[value.dtype], out.data_ptr(), scales.data_ptr(), int(swizzled), rows, channels,
+        _stream(value))
+    _finish(code, f"quantize_mxfp8_dynamic {tuple(value.shape)}", value.device)
+    return out, scales
+
+
+@quantize_mxfp8_dynamic.register_fake
+def _(value, swizzled):
+    channels = value.shape[-1]
+    rows = value.numel() // channels
+    scales = value.new_empty((swizzled_scale_bytes(rows, channels // BLOCK),) if swizzled else (rows, channels // BLOCK),
+                             dtype=torch.uint8)
+    return value.new_empty(value.shape, dtype=E4M3), scales
+
+
+@torch.library.custom_op("flashim_b200::quantize_int8_static", mutates_args=())
+def quantize_int8_static(value: Tensor, scale: Tensor) -> Tensor:
+    out = torch.empty(value.shape, device=value.device, dtype=torch.int8)
+    code = _native.library().fim_quantize_int8_static(
+        value.data_ptr(), _IN_DTYPES[value.dtype], scale.data_ptr(), out.data_ptr(), value.numel(), _stream(value))
+    _finish(code, f"quantize_int8_static {tuple(value.shape)}", value.device)
+    return out
+
+
+@quantize_int8_static.register_fake
+def _(value, scale):
+    return value.new_empty(value.shape, dtype=torch.int8)
+
+
+# ---- custom ops: tcgen05 convs -----------------------------------------------------------------------------------------
+
+_OUT_DTYPES = {
+    _native.OUT_BF16: torch.bfloat16, _native.OUT_F32: torch.float32, _native.OUT_E4M3_STATIC: E4M3,
+    _native.OUT_E4M3_DYNAMIC: E4M3, _native.OUT_INT8: torch.int8, _native.OUT_INT32: torch.int32,
+}
+
+
+def _out_size(size: int, k: int, p: int, d: int) -> int:
+    return size + 2 * p - d * (k - 1)
+
+
+def _geometry(x: Tensor, cout: int, kh, kw, ph, pw, dh, dw) -> _native.ConvGeometry:
+    b, h, w, cin = x.shape
+    return _native.ConvGeometry(b, h, w, cin, cout, kh, kw, 1, 1, ph, pw, dh, dw)
+
+
+def _epilogue(bias, residual, act: int, out_mode: int, out_exponent=None, out_scales=None, out_scale=None):
+    ep = _native.ConvEpilogue()
+    ep.bias = _ptr(bias)
+    ep.residual = _ptr(residual)
+    if residual is not None:
+        for i, s in enumerate(residual.stride()):
+            ep.res_stride[i] = s
+        ep.res_channels = residual.shape[-1]
+    ep.act, ep.out_mode = act, out_mode
+    ep.out_exponent, ep.out_scales, ep.out_scale = _ptr(out_exponent), _ptr(out_scales), _ptr(out_scale)
+    return ep
+
+
+@torch.library.custom_op("flashim_b200::mxfp8_conv2d", mutates_args=())
+def mxfp8_conv2d_launch(
+    x: Tensor, act_exponent: Tensor | None, act_scales: Tensor | None, weight: Tensor, weight_scales: Tensor,
+    bias: Tensor | None, residual: Tensor | None, out_exponent: Tensor | None,
+    kh: int, kw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
+) -> tuple[Tensor, Tensor]:
+    b, h, w, _ = x.shape
+    cout = weight.shape[0]
+    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    out = torch.empty((b, ho, wo, cout), device=x.device, dtype=_OUT_DTYPES[out_mode])
+    if out_mode == _native.OUT_E4M3_DYNAMIC:
+        out_scales = torch.zeros(swizzled_scale_bytes(b * ho * wo, cout // BLOCK), device=x.device, dtype=torch.uint8)
+    else:
+        out_scales = torch.empty(0, device=x.device, dtype=torch.uint8)
+    geometry = _geometry(x, cout, kh, kw, ph, pw, dh, dw)
+    epilogue = _epilogue(bias, residual, act, out_mode, out_exponent, out_scales if out_scales.numel() else None)
+    code = _native.library().fim_mxfp8_conv2d(
+        x.data_ptr(), _ptr(act_exponent), _ptr(act_scales), weight.data_ptr(), weight_scales.data_ptr(),
+        ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
+    _finish(code, f"mxfp8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw}", x.device)
+    return out, out_scales
+
+
+@mxfp8_conv2d_launch.register_fake
+def _(x, act_exponent, act_scales, weight, weight_scales, bias, residual, out_exponent, kh, kw, ph, pw, dh, dw, act, out_mode):
+    b, h, w, _ = x.shape
+    cout = weight.shape[0]
+    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    n = swizzled_scale_bytes(b * ho * wo, cout // BLOCK) if out_mode == _native.OUT_E4M3_DYNAMIC else 0
+    return x.new_empty((b, ho, wo, cout), dtype=_OUT_DTYPES[out_mode]), x.new_empty((n,), dtype=torch.uint8)
+
+
+@torch.library.custom_op("flashim_b200::int8_conv2d", mutates_args=())
+def int8_conv2d_launch(
+    x: Tensor, weight: Tensor, a_scale: Tensor | None, w_scale: Tensor | None, bias: Tensor | None, residual: Tensor | None,
+    out_scale: Tensor | None, kh: int, kw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
+) -> Tensor:
+    b, h, w, _ = x.shape
+    cout = weight.shape[0]
+    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    out = torch.empty((b, ho, wo, cout), device=x.device, dtype=_OUT_DTYPES[out_mode])
+    geometry = _geometry(x, cout, kh, kw, ph, pw, dh, dw)
+    epilogue = _epilogue(bias, residual, act, out_mode, out_scale=out_scale)
+    code = _native.library().fim_int8_conv2d(
+        x.data_ptr(), weight.data_ptr(), _ptr(a_scale), _ptr(w_scale), ctypes.byref(geometry), ctypes.byref(epilogue),
+        out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
+    _finish(code, f"int8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw}", x.device)
+    return out
+
+
+@int8_conv2d_launch.register_fake
+def _(x, weight, a_scale, w_scale, bias, residual, out_scale, kh, kw, ph, pw, dh, dw, act, out_mode):
+    b, h, w, _ = x.shape
+    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    return x.new_empty((b, ho, wo, weight.shape[0]), dtype=_OUT_DTYPES[out_mode])
+
+
+# ---- weight-scale layout cache (ops whose signature carries plain int8 exponents) ----------------------------------------
+
+_SWIZZLED: OrderedDict = OrderedDict()
+
+
+def swizzled_weight_scales(weight_exponent: Tensor) -> Tensor:
+    """The 128x4-swizzled E8M0 bytes of ``weight_exponent`` ``[Cout, K/32]``, computed once per tensor (keyed on its
+    storage, shape and version; the source tensor is kept alive by the entry so the key cannot be reused)."""
+    key = (weight_exponent.data_ptr(), tuple(weight_exponent.shape), weight_exponent._version, weight_exponent.device)
+    hit = _SWIZZLED.get(key)
+    if hit is not None:
+        _SWIZZLED.move_to_end(key)
+        return hit[1]
+    packed = swizzle_scales(weight_exponent)
+    _SWIZZLED[key] = (weight_exponent, packed)
+    if len(_SWIZZLED) > 512:
+        _SWIZZLED.popitem(last=False)
+    return packed
+
+
+# ---- eligibility ---------------------------------------------------------------------------------------------------------
+
+
+def _cuda(*tensors) -> bool:
+    return all(t is None or (isinstance(t, Tensor) and t.is_cuda) for t in tensors)
+
+
+def _conv_geometry_ok(x, cout, k_total, kh, kw, sh, sw, ph, pw, dh, dw) -> bool:
+    if x.ndim != 4 or not x.is_contiguous() or (sh, sw) != (1, 1):
+        return False
+    cin = x.shape[-1]
+    return cin % 32 == 0 and cout % 32 == 0 and k_total == kh * kw * cin and min(kh, kw, dh, dw) >= 1 and min(ph, pw) >= 0
+
+
+def _residual_ok(residual, cout) -> bool:
+    return residual is None or (residual.ndim == 4 and residual.dtype == torch.bfloat16 and residual.shape[-1] <= cout)
+
+
+def _depthwise_ok(value, weight, bias) -> bool:
+    return (
+        _cuda(value, weight, bias) and value.ndim == 4 and value.shape[1] % 32 == 0
+        and value.dtype in (torch.bfloat16, torch.float32, torch.float16)
+        and tuple(weight.shape) == (25, value.shape[1]) and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+        and tuple(bias.shape) == (value.shape[1],) and bias.dtype == torch.float32 and bias.is_contiguous()
+    )
+
+
+# ---- registration ---------------------------------------------------------------------------------------------------------
+
+
+def register(ops=None, device_spec=None, feature=None) -> None:
+    """Register the sm100 implementations into ``ops`` (default: :mod:`flashim_b200.ops`). ``device_spec`` and ``feature``
+    are the registry's ``DeviceSpec`` class and ``Feature`` enum (FlashIM's own when registering into ``flashim.ops``)."""
+    own = ops is None
+    if own:
+        from flashim_b200 import ops
+        from flashim_b200.ops._registry import DeviceSpec as device_spec
+        from flashim_b200.platforms import Feature as feature
+
+    spec = device_spec("cuda", (10, 0), (10, 0))
+    requires = [feature.TCGEN05, feature.TMA]
+    if hasattr(feature, "SM100A_KERNELS"):
+        requires.append(feature.SM100A_KERNELS)
+    have = _native.available
+    act_code = _native.ACT
+
+    def mxfp8_when(x, channel_exponent, weight, weight_exponent, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False,
+                   residual=None, out_exponent=None):
+        return (
+            have() and _cuda(x, channel_exponent, weight, weight_exponent, bias, residual, out_exponent)
+            and x.dtype == E4M3 and weight.dtype == E4M3 and weight.is_contiguous()
+            and _conv_geometry_ok(x, weight.shape[0], weight.shape[1], kh, kw, sh, sw, ph, pw, dh, dw)
+            and channel_exponent.dtype == torch.int8 and tuple(channel_exponent.shape) == (x.shape[-1] // 32,)
+            and weight_exponent.dtype == torch.int8 and tuple(weight_exponent.shape) == (weight.shape[0], weight.shape[1] // 32)
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == weight.shape[0]))
+            and _residual_ok(residual, weight.shape[0])
+        )
+
+    @ops.mxfp8_conv2d.register("sm100", device=spec, requires=requires, priority=3, when=mxfp8_when)
+    def mxfp8_conv2d(x, channel_exponent, weight, weight_exponent, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False,
+                     residual=None, out_exponent=None):
+        mode = _native.OUT_BF16 if out_exponent is None else _native.OUT_E4M3_STATIC
+        exponent = None if out_exponent is None else out_exponent.to(device=x.device, dtype=torch.int8).contiguous()
+        out, _ = mxfp8_conv2d_launch(
+            x, channel_exponent.contiguous(), None, weight, swizzled_weight_scales(weight_exponent),
+            None if bias is None else bias.contiguous(), residual, exponent, kh, kw, ph, pw, dh, dw,
+            act_code["relu" if relu else "none"], mode)
+        return out
+
+    def fused_when(x, act_scale, weight, weight_scales, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, act="none", residual=None,
+                   out_exponent=None, dynamic_out=False, out_fp32=False):
+        per_pixel = act_scale.dtype == torch.uint8
+        return (
+            have() and _cuda(x, act_scale, weight, weight_scales, bias, residual, out_exponent)
+            and x.dtype == E4M3 and weight.dtype == E4M3 and weight.is_contiguous() and weight_scales.dtype == torch.uint8
+            and _conv_geometry_ok(x, weight.shape[0], weight.shape[1], kh, kw, sh, sw, ph, pw, dh, dw)
+            and act in act_code and _residual_ok(residual, weight.shape[0])
+            and (not per_pixel or (kh, kw, ph, pw) == (1, 1, 0, 0))
+            and (per_pixel or (act_scale.dtype == torch.int8 and tuple(act_scale.shape) == (x.shape[-1] // 32,)))
+            and (out_exponent is None) + (not dynamic_out) + (not out_fp32) >= 2
+        )
+
+    if hasattr(ops, "mxfp8_conv2d_fused"):
+        @ops.mxfp8_conv2d_fused.register("sm100", device=spec, requires=requires, priority=3, when=fused_when)
+        def mxfp8_conv2d_fused(x, act_scale, weight, weight_scales, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, act="none",
+                               residual=None, out_exponent=None, dynamic_out=False, out_fp32=False):
+            per_pixel = act_scale.dtype == torch.uint8
+            if out_fp32:
+                mode = _native.OUT_F32
+            elif dynamic_out:
+                mode = _native.OUT_E4M3_DYNAMIC
+            else:
+                mode = _native.OUT_BF16 if out_exponent is None else _native.OUT_E4M3_STATIC
+            out, scales = mxfp8_conv2d_launch(
+                x, None if per_pixel else act_scale, act_scale if per_pixel else None, weight, weight_scales, bias, residual,
+                out_exponent, kh, kw, ph, pw, dh, dw, act_code[act], mode)
+            return (out, scales) if dynamic_out else out
+
+    def int8_when(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, residual=None,
+                  out_scale=None):
+        return (
+            have() and _cuda(x, weight, a_scale, w_scale, bias, residual, out_scale)
+            and x.dtype == torch.int8 and weight.dtype == torch.int8 and weight.is_contiguous()
+            and _conv_geometry_ok(x, weight.shape[0], weight.shape[1], kh, kw, sh, sw, ph, pw, dh, dw)
+            and a_scale.numel() == 1 and w_scale.numel() == weight.shape[0]
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == weight.shape[0]))
+            and _residual_ok(residual, weight.shape[0])
+        )
+
+    @ops.int8_conv2d.register("sm100", device=spec, requires=requires, priority=3, when=int8_when)
+    def int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, residual=None,
+                    out_scale=None):
+        scale = None if out_scale is None else out_scale.to(device=x.device, dtype=torch.float32).reshape(1)
+        return int8_conv2d_launch(
+            x, weight, a_scale.float().reshape(1), w_scale.float().contiguous(), None if bias is None else bias.contiguous(),
+            residual, scale, kh, kw, ph, pw, dh, dw, act_code["relu" if relu else "none"],
+            _native.OUT_BF16 if out_scale is None else _native.OUT_INT8)
+
+    if hasattr(ops, "int8_conv2d_accumulators"):
+        def acc_when(x, weight, kh, kw, sh, sw, ph, pw, dh, dw):
+            return (have() and _cuda(x, weight) and x.dtype == torch.int8 and weight.dtype == torch.int8
+                    and weight.is_contiguous()
+                    and _conv_geometry_ok(x, weight.shape[0], weight.shape[1], kh, kw, sh, sw, ph, pw, dh, dw))
+
+        @ops.int8_conv2d_accumulators.register("sm100", device=spec, requires=requires, priority=3, when=acc_when)
+        def int8_conv2d_accumulators(x, weight, kh, kw, sh, sw, ph, pw, dh, dw):
+            return int8_conv2d_launch(x, weight, None, None, None, None, None, kh, kw, ph, pw, dh, dw, 0, _native.OUT_INT32)
+
+    # -- depthwise ---------------------------------------------------------------------------------------------------
+    dw_requires = [feature.TMA] + ([feature.SM100A_KERNELS] if hasattr(feature, "SM100A_KERNELS") else [])
+
+    def dw_when(value, weight, bias, *rest, **kw):
+        return have() and _depthwise_ok(value, weight, bias)
+
+    @ops.depthwise5x5_relu_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_when)
+    def depthwise5x5_relu_mxfp8(value, weight, bias):
+        q, scales = dw5x5_mxfp8(_nhwc(value), weight, bias, act_code["relu"], True)
+        return q, scales.view(torch.float8_e8m0fnu)
+
+    def dw_int8_when(value, weight, bias, scale):
+        return dw_when(value, weight, bias) and _cuda(scale) and scale.numel() == 1
+
+    @ops.depthwise5x5_relu_int8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_int8_when)
+    def depthwise5x5_relu_int8(value, weight, bias, scale):
+        return dw5x5_relu_int8(_nhwc(value), weight, bias, scale.float().reshape(1))
+
+    if hasattr(ops, "depthwise5x5_act"):
+        def dw_act_when(value, weight, bias, act="gelu"):
+            return dw_when(value, weight, bias) and act in act_code
+
+        @ops.depthwise5x5_act.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_act_when)
+        def depthwise5x5_act(value, weight, bias, act="gelu"):
+            return dw5x5_bf16(_nhwc(value), weight, bias, act_code[act])
+
+        @ops.depthwise5x5_act_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_act_when)
+        def depthwise5x5_act_mxfp8(value, weight, bias, act="gelu"):
+            return dw5x5_mxfp8(_nhwc(value), weight, bias, act_code[act], True)
+
+    # -- quantisers ---------------------------------------------------------------------------------------------------
+    def quantize_when(value, scale_exponent):
+        return (
+            have() and _cuda(value, scale_exponent) and value.ndim >= 2 and value.dtype in _IN_DTYPES
+            and value.is_contiguous() and value.data_ptr() % 16 == 0
+            and tuple(scale_exponent.shape) == (padded_channels(value.shape[-1]) // 32,)
+        )
+
+    @ops.quantize_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=quantize_when)
+    def quantize_mxfp8(value, scale_exponent):
+        exponent = scale_exponent if scale_exponent.dtype == torch.int8 else scale_exponent.to(torch.int8)
+        return _make_quantized(quantize_mxfp8_static(value, exponent.contiguous()), scale_exponent, value)
+
+    def _make_quantized(values, scale_exponent, value):
+        qt = getattr(ops, "QuantizedTensor", None) or _quantized_tensor_type(ops)
+        exponent = scale_exponent if scale_exponent.dtype == torch.int8 else scale_exponent.to(torch.int8)
+        return qt(values, exponent, tuple(value.shape))
+
+    def quantize_int8_when(value, scale, *, channel_scale=None):
+        return (have() and channel_scale is None and _cuda(value, scale) and value.dtype in _IN_DTYPES
+                and value.is_contiguous() and value.data_ptr() % 16 == 0 and scale.numel() == 1)
+
+    @ops.quantize_int8.register("sm100", device=spec, requires=dw_requires, priority=3, when=quantize_int8_when)
+    def quantize_int8(value, scale, *, channel_scale=None):
+        scale32 = scale.to(device=value.device, dtype=torch.float32).reshape(())
+        return _int8_tensor_type(ops)(quantize_int8_static(value, scale32.reshape(1)), scale32)
+
+    if hasattr(ops, "quantize_mxfp8_dynamic"):
+        def dynamic_when(value):
+            return (have() and _cuda(value) and value.dtype in _IN_DTYPES and value.is_contiguous()
+                    and value.shape[-1] % 32 == 0 and value.data_ptr() % 16 == 0)
+
+        @ops.quantize_mxfp8_dynamic.register("sm100", device=spec, requires=dw_requires, priority=3, when=dynamic_when)
+        def quantize_mxfp8_dynamic_impl(value):
+            return quantize_mxfp8_dynamic(value, True)
+
+
+def _quantized_tensor_type(ops):
+    """The ``QuantizedTensor`` class of the registry's own package (FlashIM's when registered into ``flashim.ops``)."""
+    if ops.__name__.startswith("flashim."):
+        from flashim.quant.tensor import QuantizedTensor as theirs
+        return theirs
+    return QuantizedTensor
+
+
+def _int8_tensor_type(ops):
+    if ops.__name__.startswith("flashim."):
+        from flashim.quant.tensor import Int8Tensor as theirs
+        return theirs
+    return Int8Tensor

@@ -1,0 +1,299 @@
+// Shared device / host helpers for the sm_100a kernels: PTX wrappers (mbarrier, TMA, tcgen05 / tensor memory),
+// number-format conversions with the exact rounding the FlashIM reference prescribes, bounded waits and the status
+// word they report to.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fim {
+
+// ---- return codes of the C entry points (0 ok; positive cudaError_t values pass through) -----------------------
+constexpr int kOk = 0;
+constexpr int kBadLayout = -1;    // pointer alignment / shape the kernel cannot address
+constexpr int kBadArgument = -2;  // null pointer, negative size, unknown mode
+constexpr int kNoDriver = -3;     // cuTensorMapEncodeTiled could not be resolved / failed
+constexpr int kUnsupported = 99;  // a tile or geometry outside what is compiled in
+
+// ---- device status word: written once by the first CTA whose bounded wait ran out --------------------------------
+constexpr int kStatusWaitFull = 0x101;       // producer -> MMA barrier never completed
+constexpr int kStatusWaitEmpty = 0x102;      // MMA -> producer barrier never completed
+constexpr int kStatusWaitTmemFull = 0x103;   // MMA -> epilogue barrier never completed
+constexpr int kStatusWaitTmemEmpty = 0x104;  // epilogue -> MMA barrier never completed
+constexpr int kStatusWaitRows = 0x105;       // depthwise row ring barrier never completed
+
+__host__ __device__ constexpr int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+#if defined(__CUDACC__)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ---- mbarrier -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Longest time any wait inside a kernel may take before the CTA gives up (a healthy pipeline completes a phase in
+// microseconds). Two seconds keeps a broken launch from hanging the device while never tripping on a busy GPU.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Bounded wait on an mbarrier phase. Returns false when the CTA must abandon its work: either this wait exceeded
+// kWaitLimitNs (the status word then receives `code`, first writer wins) or another thread of the CTA already
+// raised `*abort_flag` (a word in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t start = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 31u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- TMA ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---- tensor memory + tcgen05 ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// All tcgen05 operations this thread issued so far arrive on `bar` when they complete.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 tensor-memory columns, replicated into the four 32-lane quarters.
+__device__ __forceinline__ void tc_copy_scales(uint32_t tmem_addr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// This thread's lane of tensor memory, 32 consecutive 32-bit columns starting at `addr`.
+__device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are `row_bytes` (32, 64 or 128) long and
+// swizzled with the matching TMA mode: 8-row groups are `8 * row_bytes` apart (stride byte offset), the leading
+// offset is unused because one swizzle span covers the whole K extent of the tile.
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t smem_addr, uint32_t row_bytes) {
+  const uint64_t layout = row_bytes == 128 ? 2ull : (row_bytes == 64 ? 4ull : 6ull);
+  uint64_t d = (smem_addr & 0x3FFFFu) >> 4;
+  d |= static_cast<uint64_t>((8u * row_bytes) >> 4) << 32;
+  d |= 1ull << 46;  // descriptor version of this architecture
+  d |= layout << 61;
+  return d;
+}
+// Descriptor of one 512-byte scale tile (32 rows x 16 bytes, no swizzle): 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr) {
+  uint64_t d = (smem_addr & 0x3FFFFu) >> 4;
+  d |= static_cast<uint64_t>(128u >> 4) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
+// ---- number formats ------------------------------------------------------------------------------------------------
+
+// Unbiased E8M0 exponent of a block with maximum magnitude `amax`: the fp32 expression ceil(log2(amax / 448)) clamped
+// to [-127, 127], -127 for amax == 0. The result only depends on which side of an integer the fp32 logarithm falls;
+// log2f decides that except within 1e-3 of an integer, where the double-precision logarithm rounded to fp32 is used
+// (it reproduces the fp32 rounding of k + epsilon to k for values a few ulp above 448 * 2**k).
+__device__ __forceinline__ int e8m0_exponent(float amax) {
+  if (amax == 0.0f) return -127;
+  const float v = __fdiv_rn(amax, 448.0f);
+  float l = log2f(v);
+  const float frac = l - floorf(l);
+  if (!(frac > 1e-3f && frac < 1.0f - 1e-3f)) l = static_cast<float>(log2(static_cast<double>(v)));
+  const float c = fminf(fmaxf(ceilf(l), -127.0f), 127.0f);
+  return static_cast<int>(c);
+}
+
+// 2**e for e in [-127, 127], exact (2**-127 is a subnormal).
+__device__ __forceinline__ float exp2_int(int e) { return scalbnf(1.0f, e); }
+
+// Two fp32 -> two E4M3 bytes (round to nearest even, saturating to +-448); `lo` lands in the low byte.
+__device__ __forceinline__ uint16_t e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  return static_cast<uint32_t>(e4m3x2(a, b)) | (static_cast<uint32_t>(e4m3x2(c, d)) << 16);
+}
+
+// round_half_even(value / scale) saturated to [-127, 127]: a true IEEE division, as the reference's quantiser.
+__device__ __forceinline__ int int8_code(float value, float scale) {
+  const float q = rintf(__fdiv_rn(value, scale));
+  return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// GELU, erf form, in the operation order of torch's CPU kernel: x * 0.5 * (1 + erf(x * sqrt(1/2))).
+__device__ __forceinline__ float gelu_erf(float x) { return x * 0.5f * (1.0f + erff(x * 0.70710678118654752440f)); }
+
+constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2;
+__device__ __forceinline__ float activate(float x, int act) {
+  if (act == kActRelu) return fmaxf(x, 0.0f);
+  if (act == kActGelu) return gelu_erf(x);
+  return x;
+}
+
+// Byte offset of element (row, group) in the 128-row x 4-group swizzled scale layout with `group_tiles` tiles per row tile.
+__device__ __forceinline__ size_t swizzled_scale_offset(size_t row, int group, int group_tiles) {
+  return ((row >> 7) * group_tiles + (group >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (group & 3);
+}
+
+#endif  // __CUDACC__
+
+// ---- host: tensor maps without linking libcuda ---------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+inline CUtensorMapSwizzle swizzle_for_bytes(int inner_bytes) {
+  if (inner_bytes == 128) return CU_TENSOR_MAP_SWIZZLE_128B;
+  if (inner_bytes == 64) return CU_TENSOR_MAP_SWIZZLE_64B;
+  if (inner_bytes == 32) return CU_TENSOR_MAP_SWIZZLE_32B;
+  return CU_TENSOR_MAP_SWIZZLE_NONE;
+}
+
+// Tiled tensor map over `rank` dimensions (innermost first). `strides_bytes` has rank-1 entries (dimension 0 is dense).
+inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return kNoDriver;
+  cuuint64_t d[5], s[4];
+  cuuint32_t b[5], e[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = 1;
+    if (i + 1 < rank) s[i] = strides_bytes[i];
+  }
+  const CUresult r = fn(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kNoDriver;
+}
+
+}  // namespace fim

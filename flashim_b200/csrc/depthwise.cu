@@ -1,0 +1,291 @@
+// Depthwise 5x5 (pad 2, stride 1) + bias + activation on bf16 NHWC, with three epilogues: bf16, dynamic MXFP8,
+// static INT8. Arithmetic follows FlashIM's torch reference (flashim/ops/conv.py:30-61): bf16 inputs and weights,
+// fp32 FMA chain ordered (ky, kx) from zero, bias added last.
+//
+// Layout of the work. A CTA owns 64 channels x (4 * warps) columns x `tile_rows` rows of one image. Input rows
+// (with their 2-pixel halo, zero-filled outside the image by TMA) stream through a ring of single-row stages in
+// shared memory; a lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 x 2 weights and five rows
+// of partial sums in registers, and finishes one output row per input row. A 32-channel MX block is 16 adjacent
+// lanes, reduced with shuffles.
+#include "common.cuh"
+#include "flashim_sm100.h"
+
+namespace fim {
+namespace {
+
+constexpr int kChannels = 64;  // per CTA: one 128-byte line per pixel
+constexpr int kCols = 4;       // output columns per lane
+constexpr int kStages = 8;     // single-row stages in the ring
+constexpr int kMaxWarps = 10;
+
+enum { kOutBf16 = 0, kOutMx = 1, kOutInt8 = 2 };
+
+struct DwParams {
+  const uint32_t* weight;  // bf16x2 words, [25][C/2]
+  const float* bias;
+  void* out;
+  uint8_t* scales;
+  const float* scale;  // INT8
+  int batch, height, width, channels;
+  int tile_rows, tiles_x, tiles_y, channel_tiles;
+  int act, swizzled;
+  int* status;
+};
+
+template <int MODE>
+__device__ __forceinline__ void emit_row(const DwParams& p, const float (&acc)[kCols][2], const float2 bias, int b, int y,
+                                         int x0, int c, bool lane_active, float int8_scale) {
+  const int groups = p.channels >> 5;
+#pragma unroll
+  for (int j = 0; j < kCols; ++j) {
+    const int x = x0 + j;
+    const bool store = lane_active && x < p.width;  // warp-uniform in x; shuffles below run for every lane
+    const size_t pixel = (static_cast<size_t>(b) * p.height + y) * p.width + x;
+    float lo = activate(acc[j][0] + bias.x, p.act);
+    float hi = activate(acc[j][1] + bias.y, p.act);
+    if (MODE == kOutBf16) {
+      if (store) reinterpret_cast<uint32_t*>(p.out)[(pixel * p.channels + c) >> 1] = pack_bf16(lo, hi);
+    } else if (MODE == kOutMx) {
+      float amax = lane_active ? fmaxf(fabsf(lo), fabsf(hi)) : 0.0f;
+#pragma unroll
+      for (int m = 1; m < 16; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+      const int e = e8m0_exponent(amax);
+      const float inv = exp2_int(-e);
+      if (store) {
+        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] = e4m3x2(lo * inv, hi * inv);
+        if ((threadIdx.x & 15) == 0) {
+          const int g = c >> 5;
+          const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
+          p.scales[at] = static_cast<uint8_t>(e + 127);
+        }
+      }
+    } else {
+      const int qlo = int8_code(bf16_round(lo), int8_scale), qhi = int8_code(bf16_round(hi), int8_scale);
+      if (store) {
+        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] =
+            static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
+      }
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ int abort_flag;
+
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_cols = warps * kCols;
+  const int row_pixels = tile_cols + 4;
+  const uint32_t row_bytes = row_pixels * kChannels * 2;
+
+  // tile decode: x fastest, then y, channel tile, batch
+  int t = blockIdx.x;
+  const int tx = t % p.tiles_x; t /= p.tiles_x;
+  const int ty = t % p.tiles_y; t /= p.tiles_y;
+  const int ct = t % p.channel_tiles;
+  const int b = t / p.channel_tiles;
+  const int x_base = tx * tile_cols, y_base = ty * p.tile_rows, c_base = ct * kChannels;
+  const int rows_out = min(p.tile_rows, p.height - y_base);
+  const int rows_in = rows_out + 4;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], warps);
+    }
+    mbar_fence_init();
+    fence_async_proxy();
+    tma_prefetch_desc(&in_map);
+  }
+  __syncthreads();
+
+  auto issue_row = [&](int r) {  // input row r of this tile -> stage r % kStages
+    const int s = r % kStages;
+    mbar_expect_tx(&full_bar[s], row_bytes);
+    tma_load_4d(smem_raw + static_cast<size_t>(s) * row_bytes, &in_map, &full_bar[s], c_base, x_base - 2, y_base - 2 + r, b);
+  };
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < min(kStages - 1, rows_in); ++r) issue_row(r);
+  }
+
+  const int c = c_base + 2 * lane;
+  const bool lane_active = c < p.channels;
+  float2 w[25];
+#pragma unroll
+  for (int k = 0; k < 25; ++k) {
+    const uint32_t word = lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u;
+    w[k] = make_float2(bf16_lo(word), bf16_hi(word));
+  }
+  const float2 bias = lane_active ? make_float2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : make_float2(0.f, 0.f);
+  const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
+
+  float acc[5][kCols][2];
+#pragma unroll
+  for (int s = 0; s < 5; ++s)
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) acc[s][j][0] = acc[s][j][1] = 0.0f;
+
+  const int x0 = x_base + warp * kCols;
+  bool alive = true;
+  for (int r0 = 0; r0 < rows_in && alive; r0 += 5) {
+#pragma unroll
+    for (int ph = 0; ph < 5; ++ph) {
+      const int r = r0 + ph;
+      if (r >= rows_in) break;
+      // refill the stage that every warp released one row ago with the row kStages - 1 ahead
+      if (threadIdx.x == 0 && r + kStages - 1 < rows_in) {
+        if (r >= 1) {
+          const int back = r - 1;
+          if (!mbar_wait(&empty_bar[back % kStages], (back / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
+            alive = false;
+          }
+        }
+        if (alive) issue_row(r + kStages - 1);
+      }
+      alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;  // warp 0 learns of its lane 0 giving up
+      if (!alive) break;
+      const int s = r % kStages;
+      if (!mbar_wait(&full_bar[s], (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
+        alive = false;
+        break;
+      }
+      const uint32_t* row = reinterpret_cast<const uint32_t*>(smem_raw + static_cast<size_t>(s) * row_bytes) +
+                            (warp * kCols) * (kChannels / 2) + lane;
+      float in[kCols + 4][2];
+#pragma unroll
+      for (int j = 0; j < kCols + 4; ++j) {
+        const uint32_t word = row[j * (kChannels / 2)];
+        in[j][0] = bf16_lo(word);
+        in[j][1] = bf16_hi(word);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+#pragma unroll
+      for (int ky = 0; ky < 5; ++ky) {
+        const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
+#pragma unroll
+        for (int kx = 0; kx < 5; ++kx) {
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) {
+            acc[slot][j][0] = fmaf(in[j + kx][0], w[ky * 5 + kx].x, acc[slot][j][0]);
+            acc[slot][j][1] = fmaf(in[j + kx][1], w[ky * 5 + kx].y, acc[slot][j][1]);
+          }
+        }
+      }
+      // output row r - 4 has now received all five input rows
+      const int done = (ph + 1) % 5;
+      const int oy = r - 4;
+      if (oy >= 0 && oy < rows_out) emit_row<MODE>(p, acc[done], bias, b, y_base + oy, x0, c, lane_active, int8_scale);
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[done][j][0] = acc[done][j][1] = 0.0f;
+    }
+  }
+  if (!alive) {
+    // Give copies that are still in flight time to land before the shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  __syncthreads();
+}
+
+int pick_warps(int width) {
+  int best = 8;
+  double best_eff = 0.0;
+  for (int w = 5; w <= kMaxWarps; ++w) {
+    const int cols = w * kCols;
+    const double eff = static_cast<double>(width) / (static_cast<double>(ceil_div(width, cols)) * cols);
+    if (eff > best_eff + 1e-9 || (eff > best_eff - 1e-9 && w >= best)) {
+      best_eff = eff;
+      best = w;
+    }
+  }
+  return best;
+}
+
+int pick_tile_rows(int height, long long tiles_per_row_band) {
+  // Rows per CTA: tall enough that the 4 halo rows cost little, short enough that the grid fills 148 SMs several times.
+  const int candidates[] = {64, 50, 40, 32, 25, 20, 16, 10, 8};
+  for (int rows : candidates) {
+    if (rows > height && rows != 8) continue;
+    const long long ctas = tiles_per_row_band * ceil_div(height, rows);
+    if (ctas >= 148LL * 6) return rows;
+  }
+  return height < 8 ? height : 8;
+}
+
+template <int MODE>
+int launch(const void* value, const void* weight, const float* bias, void* out, void* scales, const float* scale, int swizzled,
+           int batch, int height, int width, int channels, int act, int* status, void* stream) {
+  if (value == nullptr || weight == nullptr || bias == nullptr || out == nullptr) return kBadArgument;
+  if (batch < 0 || height < 0 || width < 0 || channels <= 0 || act < 0 || act > 2) return kBadArgument;
+  if (channels % 32) return kUnsupported;
+  if (batch == 0 || height == 0 || width == 0) return kOk;
+  if ((reinterpret_cast<uintptr_t>(value) & 15u) || (reinterpret_cast<uintptr_t>(weight) & 3u) ||
+      (reinterpret_cast<uintptr_t>(out) & 3u)) {
+    return kBadLayout;
+  }
+  const int warps = pick_warps(width);
+  const int tile_cols = warps * kCols;
+  DwParams p;
+  p.weight = static_cast<const uint32_t*>(weight);
+  p.bias = bias;
+  p.out = out;
+  p.scales = static_cast<uint8_t*>(scales);
+  p.scale = scale;
+  p.batch = batch, p.height = height, p.width = width, p.channels = channels;
+  p.tiles_x = ceil_div(width, tile_cols);
+  p.channel_tiles = ceil_div(channels, kChannels);
+  p.tile_rows = pick_tile_rows(height, static_cast<long long>(p.tiles_x) * p.channel_tiles * batch);
+  p.tiles_y = ceil_div(height, p.tile_rows);
+  p.act = act, p.swizzled = swizzled, p.status = status;
+  const long long ctas = static_cast<long long>(p.tiles_x) * p.tiles_y * p.channel_tiles * batch;
+  if (ctas > 0x7fffffffLL) return kUnsupported;
+
+  CUtensorMap map;
+  const uint64_t dims[4] = {static_cast<uint64_t>(channels), static_cast<uint64_t>(width), static_cast<uint64_t>(height),
+                            static_cast<uint64_t>(batch)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(channels) * 2, static_cast<uint64_t>(width) * channels * 2,
+                               static_cast<uint64_t>(height) * width * channels * 2};
+  const uint32_t box[4] = {kChannels, static_cast<uint32_t>(tile_cols + 4), 1, 1};
+  const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != kOk) return rc;
+
+  const size_t smem = static_cast<size_t>(kStages) * (tile_cols + 4) * kChannels * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(dw5x5_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dw5x5_kernel<MODE><<<static_cast<unsigned>(ctas), warps * 32, smem, static_cast<cudaStream_t>(stream)>>>(map, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace fim
+
+using namespace fim;
+
+extern "C" int fim_dw5x5_bf16(const void* value, const void* weight, const float* bias, void* out, int batch, int height,
+                              int width, int channels, int act, int* status, void* stream) {
+  return launch<kOutBf16>(value, weight, bias, out, nullptr, nullptr, 0, batch, height, width, channels, act, status, stream);
+}
+
+extern "C" int fim_dw5x5_mxfp8(const void* value, const void* weight, const float* bias, void* out, void* scales, int swizzled,
+                               int batch, int height, int width, int channels, int act, int* status, void* stream) {
+  if (scales == nullptr) return kBadArgument;
+  return launch<kOutMx>(value, weight, bias, out, scales, nullptr, swizzled, batch, height, width, channels, act, status, stream);
+}
+
+extern "C" int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias, const float* scale, void* out,
+                                   int batch, int height, int width, int channels, int* status, void* stream) {
+  if (scale == nullptr) return kBadArgument;
+  return launch<kOutInt8>(value, weight, bias, out, nullptr, scale, 0, batch, height, width, channels, kActRelu, status, stream);
+}
+
+extern "C" int fim_abi_version(void) { return FIM_ABI_VERSION; }

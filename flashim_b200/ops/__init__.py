@@ -1,0 +1,44 @@
+"""Ops of the quantized conv path. Names and signatures are FlashIM's (flashim/ops/conv.py, flashim/ops/quantize.py)
+so a module written against ``flashim.ops`` runs unchanged; ops marked *extension* expose what the sm_100a epilogues add
+on top (GELU, per-pixel activation scales, dynamic requantisation, fp32 / int32 outputs).
+
+No op here carries a torch reference: if no registered implementation accepts a call, the call raises
+:class:`~flashim_b200.ops._registry.NoImplementation`.
+"""
+
+from flashim_b200.ops._registry import (  # noqa: F401
+    OPS, DeviceSpec, NoImplementation, Op, call_counts, configure, reset_call_counts, set_strict,
+)
+
+# -- FlashIM's ops (same name, same arguments) ---------------------------------------------------------------------
+quantize_mxfp8 = Op("quantize_mxfp8", doc="(value [..., C], scale_exponent int8 [Cp/32]) -> QuantizedTensor "
+                    "(flashim/ops/quantize.py:80-87)")
+quantize_int8 = Op("quantize_int8", doc="(value, scale, *, channel_scale=None) -> Int8Tensor "
+                   "(flashim/ops/quantize.py:93-100)")
+depthwise5x5_relu_mxfp8 = Op("depthwise5x5_relu_mxfp8", doc="(value [B,C,H,W] channels-last, weight bf16 [25,C], bias fp32 "
+                             "[C]) -> (E4M3 [B*H*W, C], swizzled E8M0) (flashim/ops/conv.py:30-44)")
+depthwise5x5_relu_int8 = Op("depthwise5x5_relu_int8", doc="(value, weight, bias, scale) -> int8 [B*H*W, C] "
+                            "(flashim/ops/conv.py:50-61)")
+mxfp8_conv2d = Op("mxfp8_conv2d", doc="(x E4M3 NHWC, channel_exponent, weight E4M3 [Cout, K], weight_exponent int8 "
+                  "[Cout, K/32], bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu, residual, out_exponent) -> bf16 / E4M3 "
+                  "NHWC (flashim/ops/conv.py:309-342)")
+int8_conv2d = Op("int8_conv2d", doc="(x int8 NHWC, weight int8 [Cout, K], a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, "
+                 "dh, dw, *, relu, residual, out_scale) -> bf16 / int8 NHWC (flashim/ops/conv.py:174-206)")
+
+# -- extensions --------------------------------------------------------------------------------------------------------
+quantize_mxfp8_dynamic = Op("quantize_mxfp8_dynamic", doc="(value [..., C]) -> (E4M3 [..., C], swizzled E8M0 bytes): "
+                            "per-(row, 32) dynamic MXFP8, the quantiser of flashim/quant/formats/mx.py:50-60 as an op")
+depthwise5x5_act = Op("depthwise5x5_act", doc="(value, weight, bias, act='gelu') -> bf16 [B, H, W, C]: depthwise + bias + "
+                      "activation with a dense output")
+depthwise5x5_act_mxfp8 = Op("depthwise5x5_act_mxfp8", doc="(value, weight, bias, act='gelu') -> (E4M3 [B*H*W, C], swizzled "
+                            "E8M0): depthwise5x5_relu_mxfp8 with a selectable activation")
+mxfp8_conv2d_fused = Op("mxfp8_conv2d_fused", doc="(x, act_scale, weight, weight_scales, bias, kh, kw, sh, sw, ph, pw, dh, "
+                        "dw, *, act, residual, out_exponent, dynamic_out, out_fp32): mxfp8_conv2d with per-pixel activation "
+                        "scales (act_scale uint8 swizzled) or static ones (int8 [Cin/32]), pre-swizzled weight scales, and "
+                        "the GELU / dynamic-requant / fp32 epilogues")
+int8_conv2d_accumulators = Op("int8_conv2d_accumulators", doc="(x, weight, kh, kw, sh, sw, ph, pw, dh, dw) -> int32 "
+                              "[B, Ho, Wo, Cout]: the raw sums of int8_conv2d")
+
+from flashim_b200.backends import load as _load_backends  # noqa: E402
+
+_load_backends()

@@ -1,0 +1,144 @@
+/* C ABI of libflashim_sm100.so: hand-written sm_100a (B200) kernels for FlashIM's quantized convolution path.
+ *
+ * Conventions, the same as FlashIM's own JIT CUDA backend (flashim/backends/cuda/csrc/conv.cu:218-234,
+ * flashim/backends/cuda/csrc/depthwise.cu:405-427; Python side flashim/backends/cuda/conv.py:39-47,119-128):
+ *   - plain device pointers, ints and `long long` strides only; no framework types;
+ *   - the caller allocates every input and output; the library keeps no buffer of its own;
+ *   - `stream` is a cudaStream_t passed as void*; every call is asynchronous on it;
+ *   - return value: 0 = launched; a positive value is a cudaError_t; FIM_ERR_* (negative) are argument errors
+ *     detected before any launch; FIM_ERR_UNSUPPORTED (99) = a geometry this build has no kernel for.
+ *   - activations are NHWC (`[B, H, W, C]`, C contiguous), which is the memory of a channels-last `[B, C, H, W]`
+ *     tensor; quantized weights are `[Cout, kh*kw*Cin]` in (ky, kx, c) order as FlashIM packs them
+ *     (flashim/quant/methods/conv2d.py:91-100,193-205).
+ *   - `status` (may be NULL) points to one zero-initialised int32 in device-accessible memory. Kernels that wait on
+ *     barriers bound every wait (2 s); a CTA whose wait runs out stores an FIM_STATUS_* code there (first writer wins),
+ *     abandons its tile and exits cleanly. A non-zero word after synchronisation means the output is invalid.
+ */
+#ifndef FLASHIM_SM100_H_
+#define FLASHIM_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FIM_ABI_VERSION 1
+
+#define FIM_ERR_LAYOUT (-1)
+#define FIM_ERR_ARGUMENT (-2)
+#define FIM_ERR_DRIVER (-3)
+#define FIM_ERR_UNSUPPORTED 99
+
+#define FIM_DTYPE_F32 0
+#define FIM_DTYPE_BF16 1
+
+#define FIM_ACT_NONE 0
+#define FIM_ACT_RELU 1
+#define FIM_ACT_GELU 2
+
+/* What the conv epilogue writes. */
+#define FIM_OUT_BF16 0         /* bf16 [B,Ho,Wo,Cout] */
+#define FIM_OUT_F32 1          /* fp32, before the bf16 rounding (MXFP8 only) */
+#define FIM_OUT_E4M3_STATIC 2  /* E4M3, static exponents `out_exponent[Cout/32]` applied to the bf16 result */
+#define FIM_OUT_E4M3_DYNAMIC 3 /* E4M3 + one E8M0 byte per (pixel, 32 channels) of the bf16 result */
+#define FIM_OUT_INT8 4         /* int8, static scale `out_scale` applied to the bf16 result (INT8 only) */
+#define FIM_OUT_INT32 5        /* raw int32 accumulators (INT8 only) */
+
+#define FIM_STATUS_WAIT_FULL 0x101
+#define FIM_STATUS_WAIT_EMPTY 0x102
+#define FIM_STATUS_WAIT_TMEM_FULL 0x103
+#define FIM_STATUS_WAIT_TMEM_EMPTY 0x104
+#define FIM_STATUS_WAIT_ROWS 0x105
+
+/* ABI version of the loaded library (FIM_ABI_VERSION at build time). */
+int fim_abi_version(void);
+
+/* ---- standalone quantisers ------------------------------------------------------------------------------------- */
+
+/* Static block-32 MXFP8: out[r, c] = e4m3(sat(value[r, c] / 2**exponent[c / 32])), channels zero-padded to a multiple
+ * of 32 in `out` ([rows, ceil32(channels)], 16-byte aligned). `value` is contiguous [rows, channels] of `dtype`.
+ * Replaces: ops.quantize_mxfp8 (flashim/ops/quantize.py:80-87; oracle flashim/quant/tensor.py:97-121). */
+int fim_quantize_mxfp8_static(const void* value, int dtype, const int8_t* exponent, void* out, long long rows,
+                              int channels, void* stream);
+
+/* Dynamic block-32 MXFP8 per (row, 32 channels): e = clamp(ceil(log2(amax / 448))) evaluated in fp32 (-127 for a zero
+ * block), out = e4m3(sat(value * 2**-e)); the E8M0 byte e + 127 is stored at [row, group] (`swizzled` == 0) or in the
+ * 128-row x 4-group swizzled layout the block-scaled GEMM reads (`swizzled` != 0; the caller zero-fills padding).
+ * Replaces: quantize_dynamic_2d + swizzle_scales (flashim/quant/formats/mx.py:50-86). */
+int fim_quantize_mxfp8_dynamic(const void* value, int dtype, void* out, void* scales, int swizzled, long long rows,
+                               int channels, void* stream);
+
+/* Static per-tensor INT8: out = sat127(round_half_even(value / *scale)), true division.
+ * Replaces: ops.quantize_int8 without channel_scale (flashim/ops/quantize.py:93-100; oracle
+ * flashim/quant/formats/int8.py:24-26). */
+int fim_quantize_int8_static(const void* value, int dtype, const float* scale, void* out, long long count, void* stream);
+
+/* ---- depthwise 5x5 (pad 2, stride 1) -------------------------------------------------------------------------- */
+
+/* out[b,y,x,c] = act(sum_{ky,kx} value[b,y+ky-2,x+kx-2,c] * weight[ky*5+kx, c] + bias[c]) with fp32 accumulation
+ * over bf16 inputs, written as bf16 NHWC. `value` bf16 NHWC, `weight` bf16 [25, C] (tap-major), `bias` fp32 [C].
+ * C must be a multiple of 64. Extension of the reference's depthwise producers (which always end in a quantiser):
+ * same operands and arithmetic as flashim/ops/conv.py:30-41. */
+int fim_dw5x5_bf16(const void* value, const void* weight, const float* bias, void* out, int batch, int height, int width,
+                   int channels, int act, int* status, void* stream);
+
+/* Depthwise + bias + act, the fp32 result quantised per (pixel, 32 channels) to MXFP8 without an intermediate bf16
+ * rounding: E4M3 [B*H*W, C] and E8M0 bytes (swizzled != 0: 128x4 swizzled layout; else [B*H*W, C/32]).
+ * With act = FIM_ACT_RELU and swizzled = 1 this replaces ops.depthwise5x5_relu_mxfp8 (flashim/ops/conv.py:30-44;
+ * kernel flashim/backends/triton/conv.py:47-130). */
+int fim_dw5x5_mxfp8(const void* value, const void* weight, const float* bias, void* out, void* scales, int swizzled,
+                    int batch, int height, int width, int channels, int act, int* status, void* stream);
+
+/* Depthwise + bias + ReLU rounded to bf16, then static INT8 with *scale (true division): int8 [B*H*W, C].
+ * Replaces ops.depthwise5x5_relu_int8 (flashim/ops/conv.py:50-61; C ABI flashim/backends/cuda/csrc/depthwise.cu:407-412). */
+int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias, const float* scale, void* out, int batch,
+                        int height, int width, int channels, int* status, void* stream);
+
+/* ---- implicit-GEMM conv2d on tcgen05 tensor cores ----------------------------------------------------------- */
+
+typedef struct FimConvGeometry {
+  int batch, height, width, cin, cout; /* cin, cout: physical (padded) channel counts, multiples of 32 */
+  int kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+} FimConvGeometry;
+
+typedef struct FimConvEpilogue {
+  const void* bias;          /* bf16 [cout] or NULL */
+  const void* residual;      /* bf16, addressed with the four element strides below, or NULL */
+  long long res_stride[4];   /* batch, row, column, channel */
+  int res_channels;          /* channels present in `residual` (<= cout) */
+  int act;                   /* FIM_ACT_* */
+  int out_mode;              /* FIM_OUT_* */
+  const int8_t* out_exponent;/* FIM_OUT_E4M3_STATIC: int8 [cout/32] */
+  void* out_scales;          /* FIM_OUT_E4M3_DYNAMIC: E8M0 bytes, swizzled 128x4 layout over rows = B*Ho*Wo */
+  const float* out_scale;    /* FIM_OUT_INT8: one fp32 */
+} FimConvEpilogue;
+
+/* Block-scaled MXFP8 conv: x E4M3 NHWC; activation scales either static (`act_exponent` int8 [cin/32], shared by every
+ * pixel and tap) or per pixel (`act_scales_swizzled`: E8M0 bytes in the 128x4 swizzled layout over rows = B*H*W; 1x1
+ * stride-1 unpadded convs only); weight E4M3 [cout, kh*kw*cin]; `weight_scales_swizzled`: E8M0 bytes of the
+ * [cout, kh*kw*cin/32] exponents in the 128x4 swizzled layout. fp32 accumulation in tensor memory, epilogue
+ * bias -> bf16 -> act -> residual -> requantisation as `epilogue` selects.
+ * Replaces ops.mxfp8_conv2d (flashim/ops/conv.py:309-342; kernel flashim/backends/triton/conv.py:1122-1192) and, with
+ * per-pixel scales, ops.mxfp8_scaled_mm (flashim/ops/gemm.py:40-52). */
+int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const void* act_scales_swizzled, const void* weight,
+                     const void* weight_scales_swizzled, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue,
+                     void* out, int* status, void* stream);
+
+/* INT8 conv: x int8 NHWC, weight int8 [cout, kh*kw*cin]; exact int32 accumulation in tensor memory; epilogue
+ * float(acc) * (*a_scale * w_scale[n]) + bias (separately rounded), ReLU, bf16, residual, optional INT8 requantisation.
+ * Replaces ops.int8_conv2d (flashim/ops/conv.py:174-206; kernel flashim/backends/triton/conv.py:702-805). */
+int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, const float* w_scale,
+                    const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status, void* stream);
+
+/* Tile configuration the conv entry points would use for a geometry (for reports and tests): writes
+ * {tile_rows, tile_cols, block_n, block_k, stages, ctas}. Returns 0 or FIM_ERR_UNSUPPORTED. */
+int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]);
+
+/* Force a tile configuration for the following conv launches of this process (0 = automatic); for sweeps and tests. */
+void fim_conv_force_block_n(int block_n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHIM_SM100_H_ */

@@ -81,3 +81,25 @@ def bf16_ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         bits = t.contiguous().view(torch.int16).to(torch.int32)
         return torch.where(bits < 0, -(bits & 0x7FFF), bits)
     return (key(a) - key(b)).abs()
+
+
+# Tests check the device status word after every launch (a kernel whose bounded wait ran out reports there).
+import os  # noqa: E402
+
+os.environ.setdefault("FLASHIM_B200_CHECK", "1")
+
+DEV = "cuda"
+
+
+def to_dev(*tensors):
+    out = tuple(None if t is None else t.to(DEV) for t in tensors)
+    return out if len(out) > 1 else out[0]
+
+
+def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def code_mismatch(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.cpu().contiguous().view(torch.uint8) != b.cpu().contiguous().view(torch.uint8)).float().mean())
