@@ -47,6 +47,7 @@ struct ConvParams {
   const float* out_scale;
   void* out;
   int* status;
+  int debug;  // timing experiments only: 1 = no activation loads, 2 = no weight loads, 4 = no output stores
 };
 
 struct SharedControl {
@@ -255,7 +256,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     // ===== TMA producer =====
     if (lane == 0) {
       const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * p.block_k;
-      const uint32_t tx_bytes = a_box_bytes + b_bytes + (INT8 ? 0u : kScaleTilesB * 512u + (dynamic_a ? 512u : 0u));
+      const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
+      const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? b_bytes : 0u) +
+                                (INT8 ? 0u : kScaleTilesB * 512u + (dynamic_a ? 512u : 0u));
       uint32_t it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x) {
@@ -274,11 +277,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               alive = false;
               break;
             }
-            mbar_expect_tx(&ctl.full[s], tx_bytes);
-            tma_load_4d(smem_a + static_cast<size_t>(s) * a_bytes, &act_map, &ctl.full[s], j * p.block_k,
-                        x0 + kx * p.dil_w - p.pad_w, y0 + ky * p.dil_h - p.pad_h, b);
+            if (tx_bytes != 0) {
+              mbar_expect_tx(&ctl.full[s], tx_bytes);
+            } else {
+              mbar_arrive(&ctl.full[s]);
+            }
+            if (load_a) {
+              tma_load_4d(smem_a + static_cast<size_t>(s) * a_bytes, &act_map, &ctl.full[s], j * p.block_k,
+                          x0 + kx * p.dil_w - p.pad_w, y0 + ky * p.dil_h - p.pad_h, b);
+            }
             const int k0 = tap * p.cin + j * p.block_k;
-            tma_load_2d(smem_b + static_cast<size_t>(s) * b_bytes, &weight_map, &ctl.full[s], k0, n0);
+            if (load_b) tma_load_2d(smem_b + static_cast<size_t>(s) * b_bytes, &weight_map, &ctl.full[s], k0, n0);
             if (!INT8) {
               const int w_tile = (k0 >> 5) >> 2;
 #pragma unroll
@@ -374,7 +383,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         uint32_t raw[32];
         tmem_load_32(lane_addr + c0, raw);
         tmem_load_wait();
-        if (valid) finish_chunk<INT8>(p, raw, n0 + c0, pixel, b, y, x, a_scale);
+        if (valid && !(p.debug & 4)) finish_chunk<INT8>(p, raw, n0 + c0, pixel, b, y, x, a_scale);
       }
       tc_fence_before();
       __syncwarp();
@@ -398,6 +407,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
 // ---- host ------------------------------------------------------------------------------------------------------------
 
 int g_forced_block_n = 0;
+int g_max_ctas = 0;
+int g_debug_flags = 0;
 
 struct Plan {
   int tile_h, tile_w, block_n, block_k, stages, ctas;
@@ -453,7 +464,8 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   pl.stages = kSmemBudget / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
-  pl.ctas = pl.total_tiles < 148 ? pl.total_tiles : 148;
+  const int sms = g_max_ctas > 0 && g_max_ctas < 148 ? g_max_ctas : 148;
+  pl.ctas = pl.total_tiles < sms ? pl.total_tiles : sms;
   *plan = pl;
   return kOk;
 }
@@ -538,6 +550,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.out_scale = ep->out_scale;
   p.out = out;
   p.status = status;
+  p.debug = g_debug_flags;
 
   // tensor maps: activations [B, H, W, Cin] (flat: [1, 1, B*H*W, Cin]) and weights [Cout, K]
   long long eff_b = g->batch, eff_h = g->height, eff_w = g->width;
@@ -601,4 +614,8 @@ extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_
   return kOk;
 }
 
-extern "C" void fim_conv_force_block_n(int block_n) { g_forced_block_n = block_n; }
+extern "C" void fim_conv_tune(int block_n, int max_ctas, int debug_flags) {
+  g_forced_block_n = block_n;
+  g_max_ctas = max_ctas;
+  g_debug_flags = debug_flags;
+}

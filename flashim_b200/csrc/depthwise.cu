@@ -221,10 +221,10 @@ int pick_tile_rows(int height, long long tiles_per_row_band) {
 template <int MODE>
 int launch(const void* value, const void* weight, const float* bias, void* out, void* scales, const float* scale, int swizzled,
            int batch, int height, int width, int channels, int act, int* status, void* stream) {
-  if (value == nullptr || weight == nullptr || bias == nullptr || out == nullptr) return kBadArgument;
   if (batch < 0 || height < 0 || width < 0 || channels <= 0 || act < 0 || act > 2) return kBadArgument;
   if (channels % 32) return kUnsupported;
   if (batch == 0 || height == 0 || width == 0) return kOk;
+  if (value == nullptr || weight == nullptr || bias == nullptr || out == nullptr) return kBadArgument;
   if ((reinterpret_cast<uintptr_t>(value) & 15u) || (reinterpret_cast<uintptr_t>(weight) & 3u) ||
       (reinterpret_cast<uintptr_t>(out) & 3u)) {
     return kBadLayout;

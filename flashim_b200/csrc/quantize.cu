@@ -148,8 +148,8 @@ using namespace fim;
 
 extern "C" int fim_quantize_mxfp8_static(const void* value, int dtype, const int8_t* exponent, void* out, long long rows,
                                          int channels, void* stream) {
+  if (rows == 0 && channels > 0) return kOk;
   if (value == nullptr || exponent == nullptr || out == nullptr || rows < 0 || channels <= 0) return kBadArgument;
-  if (rows == 0) return kOk;
   const int padded = (channels + 31) / 32 * 32;
   if (!aligned16(out)) return kBadLayout;
   const int elem = dtype == FIM_DTYPE_BF16 ? 2 : 4;
@@ -170,9 +170,9 @@ extern "C" int fim_quantize_mxfp8_static(const void* value, int dtype, const int
 
 extern "C" int fim_quantize_mxfp8_dynamic(const void* value, int dtype, void* out, void* scales, int swizzled, long long rows,
                                           int channels, void* stream) {
+  if (rows == 0 && channels > 0) return kOk;
   if (value == nullptr || out == nullptr || scales == nullptr || rows < 0 || channels <= 0) return kBadArgument;
   if (channels % 32) return kBadLayout;
-  if (rows == 0) return kOk;
   if (!aligned16(value) || !aligned16(out)) return kBadLayout;
   const int grid = grid_for(rows * (channels / 16), 16);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -191,8 +191,8 @@ extern "C" int fim_quantize_mxfp8_dynamic(const void* value, int dtype, void* ou
 
 extern "C" int fim_quantize_int8_static(const void* value, int dtype, const float* scale, void* out, long long count,
                                         void* stream) {
-  if (value == nullptr || scale == nullptr || out == nullptr || count < 0) return kBadArgument;
   if (count == 0) return kOk;
+  if (value == nullptr || scale == nullptr || out == nullptr || count < 0) return kBadArgument;
   if (!aligned16(value) || !aligned16(out)) return kBadLayout;
   const int grid = grid_for(count / 16 + 1, 16);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -135,8 +135,10 @@ int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, con
  * {tile_rows, tile_cols, block_n, block_k, stages, ctas}. Returns 0 or FIM_ERR_UNSUPPORTED. */
 int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]);
 
-/* Force a tile configuration for the following conv launches of this process (0 = automatic); for sweeps and tests. */
-void fim_conv_force_block_n(int block_n);
+/* Tuning and measurement hooks for the following conv launches of this process (all 0 = automatic / off):
+ * `block_n` forces the output-channel tile (64 / 128 / 256); `max_ctas` caps the persistent grid; `debug_flags` is for
+ * timing experiments only and makes results invalid (1: skip activation loads, 2: skip weight loads, 4: skip stores). */
+void fim_conv_tune(int block_n, int max_ctas, int debug_flags);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,68 @@
+"""The synthetic refiner stack built with ``flashim_b200.load`` against the CPU oracle's restatement of it."""
+
+import pytest
+import torch
+
+import oracle
+from tests.conftest import DEV, rel_l2, same_bytes
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _oracle_levels(levels, blocks, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [oracle.make_refiner_level_weights(c, blocks, g) for _, c in levels]
+
+
+def test_weights_match_the_oracle_generator():
+    import flashim_b200
+
+    levels = [[12, 64], [10, 128]]
+    model = flashim_b200.load("refiner-stack", "fp8", device=DEV, overrides={"arch.levels": levels, "arch.blocks": 2})
+    want = _oracle_levels(levels, 2, 4)
+    for level, ref in zip(model.levels, want):
+        assert same_bytes(level.proj.weight.cpu(), ref["proj"]["w"].view(torch.uint8))
+        assert torch.equal(level.blocks[1].down.weight_exponent.cpu(), ref["blocks"][1]["down"]["e"])
+        assert same_bytes(level.blocks[0].dw_weight.cpu(), ref["blocks"][0]["dw_w"])
+        assert same_bytes(level.head.bias.cpu(), ref["head"]["b"])
+        assert torch.equal(level.head.weight_scales.cpu(), oracle.swizzle_32_4_4(ref["head"]["e"]))
+
+
+def test_block_and_level_match_the_oracle():
+    import flashim_b200
+    from flashim_b200 import ops
+
+    levels = [[20, 128], [24, 64]]
+    model = flashim_b200.load("refiner-stack", "fp8", device=DEV, overrides={"arch.levels": levels, "arch.blocks": 2, "arch.chunk": 2})
+    refs = _oracle_levels(levels, 2, 4)
+    g = torch.Generator().manual_seed(7)
+    pyramid = [torch.randn(3, size, size, c, generator=g).to(BF16) for size, c in levels]
+    ops.reset_call_counts()
+    outs = model([p.to(DEV) for p in pyramid])
+    counts = ops.call_counts()
+    assert all(set(v) == {"sm100"} for v in counts.values()), counts  # nothing left the CUDA path
+    for x, level, ref, out in zip(pyramid, model.levels, refs, outs):
+        block = level.blocks[0](x.to(DEV))
+        assert rel_l2(block, oracle.refiner_block_ext(x, ref["blocks"][0])) < 5e-3
+        want = oracle.refiner_level_ext(x, ref)
+        assert out.shape == want.shape == (3, x.shape[1], x.shape[2], 32) and out.dtype == BF16
+        assert rel_l2(out[..., :4], want[..., :4]) < 3e-2
+    # chunked and unchunked execution produce the same bits (samples are independent)
+    model.chunk = 8
+    again = model([p.to(DEV) for p in pyramid])
+    assert all(same_bytes(a, b) for a, b in zip(outs, again))
+
+
+def test_cuda_graph_engine_replays_the_same_bits():
+    import flashim_b200
+
+    levels = [[16, 64]]
+    eager = flashim_b200.load("refiner-stack", "fp8", device=DEV, overrides={"arch.levels": levels, "arch.blocks": 1})
+    graphed = flashim_b200.load("refiner-stack", "fp8", device=DEV, engine="cuda-graph",
+                                overrides={"arch.levels": levels, "arch.blocks": 1})
+    assert graphed.build_report.engine == "cuda-graph" and graphed.run_config.digest() != eager.run_config.digest()
+    x = [torch.randn(2, 16, 16, 64, device=DEV).to(BF16)]
+    want = eager(x)[0]
+    for _ in range(3):
+        assert same_bytes(graphed(x)[0], want)
