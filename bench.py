@@ -234,6 +234,7 @@ class Int8Workload(ConvWorkload):
         self.a_scale = (self.host[0].float().abs().max() / 127).reshape(()).to(device)
         self.result_host = torch.empty((n, h, h, c), dtype=torch.bfloat16).pin_memory()
         self.staging = torch.empty_like(self.inputs[0])
+        self.out_exponent = None
         self.q0 = self._quantize(self.inputs[0])
 
     def _quantize(self, x):
@@ -591,21 +592,25 @@ def main() -> None:
     import flashim_b200
 
     workload = WORKLOADS[args.workload](device, rank, world)
-    for _ in range(args.warmup):
-        workload.step()
-    torch.cuda.synchronize()
-    flashim_b200.check_status(device)
-
+    # clocks are sampled from the warm-up to the end of the end-to-end region (short timed regions fall between samples)
     with ClockSampler(local) as sampler:
+        for _ in range(args.warmup):
+            workload.step()
+        torch.cuda.synchronize()
+        flashim_b200.check_status(device)
         ms = _timed(workload.step, args.steps, world, device)
-    flashim_b200.check_status(device)
-    units = _sum_over_ranks(workload.units_per_step(), world, device)
-    value = units * args.steps / (ms * 1e-3)
-
-    for _ in range(2):
-        workload.step_e2e()
-    e2e_ms = _timed(workload.step_e2e, args.steps, world, device)
-    flashim_b200.check_status(device)
+        flashim_b200.check_status(device)
+        units = _sum_over_ranks(workload.units_per_step(), world, device)
+        value = units * args.steps / (ms * 1e-3)
+        for _ in range(2):
+            workload.step_e2e()
+        e2e_ms = _timed(workload.step_e2e, args.steps, world, device)
+        flashim_b200.check_status(device)
+        # keep the device busy long enough for at least a few 200 ms samples
+        spin_until = time.perf_counter() + 0.7
+        while time.perf_counter() < spin_until:
+            workload.step()
+        torch.cuda.synchronize()
     h2d, d2h = workload.e2e_bytes()
 
     roofline = workload.roofline(args.steps) if rank == 0 else None

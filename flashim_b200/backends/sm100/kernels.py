@@ -58,7 +58,7 @@ def _ptr(t: Tensor | None) -> int | None:
 
 def _finish(code: int, what: str, device: torch.device) -> None:
     _native.check(code, what)
-    if _CHECK_EVERY_CALL:
+    if _CHECK_EVERY_CALL and not torch.cuda.is_current_stream_capturing():
         check_status(device)
 
 

@@ -94,6 +94,53 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Variants on a precomputed shared-memory address (the issue loops of the conv kernel keep them in registers).
+__device__ __forceinline__ bool mbar_try_addr(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// `heed_abort` = false: only this wait's own time limit ends it. Warps that meet at a named barrier afterwards use it, so
+// that all of them take the same decision (either the phase completes for all or it times out for all).
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                            bool heed_abort) {
+  const uint64_t start = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_addr(bar, parity)) return true;
+    if ((++spins & 31u) == 0u) {
+      if (heed_abort && *abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                               bool heed_abort = true) {
+  if (mbar_try_addr(bar, parity)) return true;
+  if (mbar_try_addr(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, code, heed_abort);
+}
+__device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_addr(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Barrier among `threads` threads of the CTA (a multiple of 32) on hardware barrier `id` (1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- TMA ---------------------------------------------------------------------------------------------------------
@@ -112,6 +159,38 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_addr(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_addr(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_addr(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Tiled store shared -> global (clipped at the tensor bounds), tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's committed store groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, `bytes` a multiple of 16.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
@@ -236,6 +315,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // GELU, erf form, in the operation order of torch's CPU kernel: x * 0.5 * (1 + erf(x * sqrt(1/2))).
 __device__ __forceinline__ float gelu_erf(float x) { return x * 0.5f * (1.0f + erff(x * 0.70710678118654752440f)); }
+
+// GELU through the complementary error function in the rational-exponential form of Abramowitz & Stegun 7.1.26
+// (|error of erf| <= 1.5e-7): gelu(x) = x/2 * (2 - c) for x >= 0 and x/2 * c for x < 0 with c = erfc(|x|/sqrt 2).
+// No branch, two MUFU operations. For every bf16 input with |x| < 3 the bf16-rounded result equals that of the erf form
+// above; beyond x < -4.5 (|gelu| < 2e-5) both forms are dominated by their own rounding.
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float z = fabsf(x) * 0.70710678118654752440f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float c = poly * t * exp2f(-(z * z) * 1.4426950408889634f);
+  const float half_x = 0.5f * x;
+  return x >= 0.0f ? half_x * (2.0f - c) : half_x * c;
+}
 
 constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2;
 __device__ __forceinline__ float activate(float x, int act) {

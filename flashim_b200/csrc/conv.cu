@@ -5,10 +5,14 @@
 // channels. Warp 0 is the TMA producer: per (tap, channel chunk) it loads the shifted activation patch (a 4-D box whose
 // out-of-image part TMA fills with zeros: the conv padding, no im2col buffer) and the weight tile into a ring of
 // swizzled K-major stages, plus the 512-byte scale tiles. Warp 1 issues tcgen05.mma from one lane, accumulating in
-// tensor memory; scale tiles go shared memory -> tensor memory with tcgen05.cp in front of the MMAs that use them.
-// Warps 2-5 are the epilogue: tcgen05.ld their 32 accumulator rows, apply bias / bf16 rounding / activation / residual
-// / requantisation in registers and store. Accumulators are double-buffered in tensor memory when 2 * BN columns fit,
-// so the epilogue of tile i overlaps the main loop of tile i + 1.
+// tensor memory; scale tiles go shared memory -> tensor memory with tcgen05.cp in front of the MMAs that use them, into
+// two alternating column sets so a copy never waits for the MMAs of the stage before. Warps 2-9 are the epilogue: two
+// warps per 32-lane quarter of tensor memory, each owning half of the BN columns. They tcgen05.ld 32 columns at a
+// time, apply bias / bf16 rounding / activation / residual / requantisation in registers, write the 32-column panel of
+// the tile into swizzled shared memory and hand it to a TMA store, which clips the ragged image edge. Accumulators are
+// double-buffered in tensor memory when two of them fit, so the epilogue of tile i overlaps the main loop of tile i + 1.
+// The producer and MMA loops keep stage addresses, descriptors and phase bits in registers: a single lane issues them
+// and every instruction there is on the critical path of the tensor pipe.
 //
 // Rounding points follow FlashIM's torch reference: flashim/ops/conv.py:174-206,309-342 and flashim/ops/gemm.py:58-98.
 #include "common.cuh"
@@ -17,17 +21,17 @@
 namespace fim {
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kTileM = 128;
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kSmemLimit = 226 * 1024;
 
 struct ConvParams {
-  int batch, height, width, cin, cout, out_h, out_w;
+  int cin, cout, out_h, out_w;
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
-  int block_k, k_chunks, stages;
+  int k_chunks, stages;
   // scales (MXFP8)
   const int8_t* act_exponent;     // static: [cin / 32]
   const uint8_t* act_scales;      // per pixel: swizzled tiles over rows = pixels
@@ -41,11 +45,10 @@ struct ConvParams {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   long long res_stride[4];
-  int res_channels, act, out_mode;
+  int res_channels, act, out_mode, out_elem;  // out_elem: bytes per output element
   const int8_t* out_exponent;
   uint8_t* out_scales;
   const float* out_scale;
-  void* out;
   int* status;
   int debug;  // timing experiments only: 1 = no activation loads, 2 = no weight loads, 4 = no output stores
 };
@@ -59,10 +62,12 @@ struct SharedControl {
   int abort_flag;
 };
 
-__device__ __forceinline__ uint32_t idesc_mxf8(int block_n, uint32_t a_id, uint32_t b_id) {
-  // E4M3 x E4M3 (format 0), both K-major, UE8M0 scales, M = 128, N = block_n
-  return (b_id << 4) | (static_cast<uint32_t>(block_n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24) |
-         (a_id << 29);
+__host__ __device__ constexpr int acc_stages(int bn) { return 2 * bn + 16 + 2 * (bn < 128 ? 4 : bn / 32) <= 512 ? 2 : 1; }
+__host__ __device__ constexpr int scale_tiles_b(int bn) { return bn <= 128 ? 1 : bn / 128; }
+
+__device__ __forceinline__ uint32_t idesc_mxf8(int block_n) {
+  // E4M3 x E4M3 (format 0), both K-major, UE8M0 scales, M = 128, N = block_n; scale ids are OR-ed in per MMA
+  return (static_cast<uint32_t>(block_n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24);
 }
 __device__ __forceinline__ uint32_t idesc_i8(int block_n) {
   // S32 accumulator (2), signed 8-bit A and B (1), both K-major, M = 128, N = block_n
@@ -70,22 +75,25 @@ __device__ __forceinline__ uint32_t idesc_i8(int block_n) {
          (static_cast<uint32_t>(kTileM >> 4) << 24);
 }
 
-// ---- epilogue on 32 consecutive output channels of one pixel -------------------------------------------------------
+// ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
+// Fills `w` with the output bytes of the chunk (32 * out_elem bytes, little end first).
 template <bool INT8>
 __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, size_t pixel, int b, int y,
-                                             int x, float a_scale) {
+                                             int x, bool valid, float a_scale, uint32_t (&w)[32]) {
+  if (INT8 && p.out_mode == FIM_OUT_INT32) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = raw[i];
+    return;
+  }
   float v[32];
   if (INT8) {
-    if (p.out_mode == FIM_OUT_INT32) {
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<int32_t*>(p.out) + pixel * p.cout + n);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] = make_uint4(raw[4 * i], raw[4 * i + 1], raw[4 * i + 2], raw[4 * i + 3]);
-      return;
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float scale = __fmul_rn(a_scale, __ldg(p.w_scale + n + i));
-      v[i] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i])), scale);
+    for (int i = 0; i < 32; i += 4) {
+      const float4 s = __ldg(reinterpret_cast<const float4*>(p.w_scale + n + i));
+      v[i] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i])), __fmul_rn(a_scale, s.x));
+      v[i + 1] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 1])), __fmul_rn(a_scale, s.y));
+      v[i + 2] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 2])), __fmul_rn(a_scale, s.z));
+      v[i + 3] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 3])), __fmul_rn(a_scale, s.w));
     }
   } else {
 #pragma unroll
@@ -95,8 +103,8 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
     const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 w = __ldg(bp + i);
-      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+      const uint4 q = __ldg(bp + i);
+      const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         v[8 * i + 2 * j] = __fadd_rn(v[8 * i + 2 * j], bf16_lo(ws[j]));
@@ -105,67 +113,63 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
     }
   }
   if (!INT8 && p.out_mode == FIM_OUT_F32) {
-    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + pixel * p.cout + n);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(v[i]);
     return;
   }
   const bool has_res = p.residual != nullptr;
   // one bf16 rounding, activation on the rounded value (ReLU waits for the residual when there is one)
+  if (p.act == kActGelu) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float h = bf16_round(v[i]);
-    if (p.act == kActGelu) h = bf16_round(gelu_erf(h));
-    if (p.act == kActRelu && !has_res) h = fmaxf(h, 0.0f);
-    v[i] = h;
+    for (int i = 0; i < 32; ++i) v[i] = bf16_round(gelu_fast(bf16_round(v[i])));
+  } else if (p.act == kActRelu && !has_res) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = fmaxf(bf16_round(v[i]), 0.0f);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]);
   }
   if (has_res) {
-    const __nv_bfloat16* rp = p.residual + b * p.res_stride[0] + y * p.res_stride[1] + x * p.res_stride[2];
     const int limit = p.res_channels - n;  // channels of this chunk present in the residual
-    const bool vec = p.res_stride[3] == 1 && limit >= 32 && ((reinterpret_cast<uintptr_t>(rp + n) & 15u) == 0);
-    if (vec) {
-      const uint4* r4 = reinterpret_cast<const uint4*>(rp + n);
+    if (valid && limit > 0) {
+      const __nv_bfloat16* rp = p.residual + b * p.res_stride[0] + y * p.res_stride[1] + x * p.res_stride[2];
+      const bool vec = p.res_stride[3] == 1 && limit >= 32 && ((reinterpret_cast<uintptr_t>(rp + n) & 15u) == 0);
+      if (vec) {
+        const uint4* r4 = reinterpret_cast<const uint4*>(rp + n);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 w = __ldg(r4 + i);
-        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        for (int i = 0; i < 4; ++i) {
+          const uint4 q = __ldg(r4 + i);
+          const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          v[8 * i + 2 * j] += bf16_lo(ws[j]);
-          v[8 * i + 2 * j + 1] += bf16_hi(ws[j]);
+          for (int j = 0; j < 4; ++j) {
+            v[8 * i + 2 * j] += bf16_lo(ws[j]);
+            v[8 * i + 2 * j + 1] += bf16_hi(ws[j]);
+          }
         }
-      }
-    } else {
+      } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (i < limit) v[i] += __bfloat162float(rp[(n + i) * p.res_stride[3]]);
+        for (int i = 0; i < 32; ++i) {
+          if (i < limit) v[i] += __bfloat162float(rp[(n + i) * p.res_stride[3]]);
+        }
       }
     }
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = bf16_round(p.act == kActRelu ? fmaxf(v[i], 0.0f) : v[i]);
   }
   if (p.out_mode == FIM_OUT_BF16) {
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + pixel * p.cout + n);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      dst[i] = make_uint4(pack_bf16(v[8 * i], v[8 * i + 1]), pack_bf16(v[8 * i + 2], v[8 * i + 3]),
-                          pack_bf16(v[8 * i + 4], v[8 * i + 5]), pack_bf16(v[8 * i + 6], v[8 * i + 7]));
-    }
+    for (int i = 0; i < 16; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
     return;
   }
   if (INT8) {  // FIM_OUT_INT8
     const float scale = __ldg(p.out_scale);
-    uint32_t q[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      uint32_t w = 0;
+      uint32_t q = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) w |= (static_cast<uint32_t>(int8_code(v[4 * i + k], scale)) & 0xFFu) << (8 * k);
-      q[i] = w;
+      for (int k = 0; k < 4; ++k) q |= (static_cast<uint32_t>(int8_code(v[4 * i + k], scale)) & 0xFFu) << (8 * k);
+      w[i] = q;
     }
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(p.out) + pixel * p.cout + n);
-    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
     return;
   }
   int e;
@@ -176,43 +180,63 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
 #pragma unroll
     for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
     e = e8m0_exponent(amax);
-    const int groups = p.cout >> 5;
-    p.out_scales[swizzled_scale_offset(pixel, n >> 5, (groups + 3) >> 2)] = static_cast<uint8_t>(e + 127);
+    if (valid) {
+      const int groups = p.cout >> 5;
+      p.out_scales[swizzled_scale_offset(pixel, n >> 5, (groups + 3) >> 2)] = static_cast<uint8_t>(e + 127);
+    }
   }
   const float inv = exp2_int(-e);
-  uint32_t q[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = e4m3x4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + pixel * p.cout + n);
-  dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-  dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+  for (int i = 0; i < 8; ++i) w[i] = e4m3x4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
 }
 
-template <bool INT8, int BN>
+// Write this row's 32 * elem bytes of a panel into swizzled shared memory (the layout a TMA store with swizzle mode
+// 32 * elem bytes reads): 16-byte slot i of row r lands in slot i ^ ((r * pitch / 128) mod slots).
+__device__ __forceinline__ void stage_row(uint32_t panel, int row, int elem, const uint32_t (&w)[32]) {
+  const uint32_t pitch = 32u * elem;           // 32, 64 or 128 bytes
+  const uint32_t slots = pitch >> 4;           // 2, 4 or 8
+  const uint32_t phase = ((static_cast<uint32_t>(row) * pitch) >> 7) & (slots - 1);
+  const uint32_t base = panel + row * pitch;
+#pragma unroll
+  for (uint32_t i = 0; i < 8; ++i) {
+    if (i < slots) {
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + ((i ^ phase) << 4)), "r"(w[4 * i]), "r"(w[4 * i + 1]),
+                   "r"(w[4 * i + 2]), "r"(w[4 * i + 3])
+                   : "memory");
+    }
+  }
+}
+
+template <bool INT8, int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map, const ConvParams p) {
-  constexpr int kAccStages = (2 * BN + 4 + (BN < 128 ? 4 : BN / 32)) <= static_cast<int>(kTmemColumns) ? 2 : 1;
-  constexpr int kScaleTilesB = BN <= 128 ? 1 : BN / 128;
-  constexpr uint32_t kSfaColumn = kAccStages * BN;
-  constexpr uint32_t kSfbColumn = kSfaColumn + 4;
+conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
+            const __grid_constant__ CUtensorMap out_map, const ConvParams p) {
+  constexpr int kAccStages = acc_stages(BN);
+  constexpr int kScaleTilesB = scale_tiles_b(BN);
+  constexpr int kKSteps = BK / 32;
+  constexpr uint32_t kABytes = kTileM * BK, kBBytes = BN * BK;
+  constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
+  constexpr uint32_t kSfaColumn = kAccStages * BN;       // two sets of 4 columns
+  constexpr uint32_t kSfbColumn = kSfaColumn + 8;        // two sets of kSfbColumns
+  constexpr int kChunksPerWarp = BN / 64;                // 32-column chunks each epilogue warp owns
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) SharedControl ctl;
 
-  // dynamic shared memory, 1024-byte aligned: [stages x A][stages x B][stages x scale tiles B][stages x scale tile A][static A tiles]
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023u) & ~static_cast<uintptr_t>(1023u));
-  const uint32_t a_bytes = kTileM * p.block_k;
-  const uint32_t b_bytes = BN * p.block_k;
-  uint8_t* smem_a = base;
-  uint8_t* smem_b = smem_a + static_cast<size_t>(p.stages) * a_bytes;
-  uint8_t* smem_sfb = smem_b + static_cast<size_t>(p.stages) * b_bytes;
-  uint8_t* smem_sfa = smem_sfb + static_cast<size_t>(p.stages) * kScaleTilesB * 512;
-  uint8_t* smem_sfa_static = smem_sfa + static_cast<size_t>(p.stages) * 512;
+  // dynamic shared memory, 1024-byte aligned:
+  // [stages x A][stages x B][4 output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles]
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t panel_bytes = 4096u * p.out_elem;
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = smem_a + p.stages * kABytes;
+  const uint32_t smem_out = smem_b + p.stages * kBBytes;
+  const uint32_t smem_sfb = smem_out + 4 * panel_bytes;
+  const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
+  const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dynamic_a = !INT8 && p.act_scales != nullptr;
   const int taps = p.kh * p.kw;
-  const int k_iters = taps * p.k_chunks;
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -222,11 +246,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl.tmem_full[s], 1);
-      mbar_init(&ctl.tmem_empty[s], 4);
+      mbar_init(&ctl.tmem_empty[s], 8);
     }
     mbar_fence_init();
     tma_prefetch_desc(&act_map);
     tma_prefetch_desc(&weight_map);
+    tma_prefetch_desc(&out_map);
   }
   if (warp == 1) {
     tmem_alloc(&ctl.tmem_base, kTmemColumns);
@@ -243,7 +268,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const uint32_t byte = idx < groups ? static_cast<uint32_t>(static_cast<int>(p.act_exponent[idx]) + 127) : 127u;
         word |= (byte & 0xFFu) << (8 * g);
       }
-      *reinterpret_cast<uint4*>(smem_sfa_static + t * 512 + lane * 16) = make_uint4(word, word, word, word);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem_sfa_static + t * 512 + lane * 16), "r"(word) : "memory");
     }
     fence_async_proxy();
   }
@@ -251,57 +276,60 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl.tmem_base;
+  const uint32_t full0 = smem_u32(&ctl.full[0]), empty0 = smem_u32(&ctl.empty[0]);
+  const uint32_t tfull0 = smem_u32(&ctl.tmem_full[0]), tempty0 = smem_u32(&ctl.tmem_empty[0]);
+  volatile int* abort_flag = &ctl.abort_flag;
 
   if (warp == 0) {
     // ===== TMA producer =====
     if (lane == 0) {
-      const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * p.block_k;
+      const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
       const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
-      const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? b_bytes : 0u) +
+      const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? kBBytes : 0u) +
                                 (INT8 ? 0u : kScaleTilesB * 512u + (dynamic_a ? 512u : 0u));
-      uint32_t it = 0;
+      uint32_t s = 0, phase = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x) {
         const int nt = tile % p.tiles_n;
-        int m = tile / p.tiles_n;
+        const int m_tile = tile / p.tiles_n;
+        int m = m_tile;
         const int tx = m % p.tiles_x; m /= p.tiles_x;
         const int ty = m % p.tiles_y;
         const int b = m / p.tiles_y;
-        const int x0 = tx * p.tile_w, y0 = ty * p.tile_h, n0 = nt * BN;
-        const int m_tile = tile / p.tiles_n;  // row tile of the per-pixel scale layout (flat 1x1 convs)
-        for (int tap = 0; tap < taps && alive; ++tap) {
-          const int ky = tap / p.kw, kx = tap - ky * p.kw;
-          for (int j = 0; j < p.k_chunks; ++j, ++it) {
-            const int s = it % p.stages;
-            if (!mbar_wait(&ctl.empty[s], ((it / p.stages) & 1) ^ 1, &ctl.abort_flag, p.status, kStatusWaitEmpty)) {
-              alive = false;
-              break;
-            }
-            if (tx_bytes != 0) {
-              mbar_expect_tx(&ctl.full[s], tx_bytes);
-            } else {
-              mbar_arrive(&ctl.full[s]);
-            }
-            if (load_a) {
-              tma_load_4d(smem_a + static_cast<size_t>(s) * a_bytes, &act_map, &ctl.full[s], j * p.block_k,
-                          x0 + kx * p.dil_w - p.pad_w, y0 + ky * p.dil_h - p.pad_h, b);
-            }
-            const int k0 = tap * p.cin + j * p.block_k;
-            if (load_b) tma_load_2d(smem_b + static_cast<size_t>(s) * b_bytes, &weight_map, &ctl.full[s], k0, n0);
-            if (!INT8) {
-              const int w_tile = (k0 >> 5) >> 2;
+        const int x0 = tx * p.tile_w - p.pad_w, y0 = ty * p.tile_h - p.pad_h, n0 = nt * BN;
+        const uint8_t* sfb_src[kScaleTilesB];
 #pragma unroll
-              for (int i = 0; i < kScaleTilesB; ++i) {
-                const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
-                bulk_load(smem_sfb + (static_cast<size_t>(s) * kScaleTilesB + i) * 512,
-                          p.weight_scales + (static_cast<size_t>(row_tile) * p.weight_scale_tiles + w_tile) * 512, 512,
-                          &ctl.full[s]);
+        for (int i = 0; i < kScaleTilesB; ++i) {
+          const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
+          sfb_src[i] = p.weight_scales + static_cast<size_t>(row_tile) * p.weight_scale_tiles * 512;
+        }
+        const uint8_t* sfa_src = dynamic_a ? p.act_scales + static_cast<size_t>(m_tile) * p.act_scale_tiles * 512 : nullptr;
+        int k0 = 0;  // offset along the weight's K axis
+        for (int ky = 0; ky < p.kh && alive; ++ky) {
+          for (int kx = 0; kx < p.kw && alive; ++kx) {
+            const int cx = x0 + kx * p.dil_w, cy = y0 + ky * p.dil_h;
+            for (int j = 0; j < p.k_chunks; ++j, k0 += BK) {
+              if (!mbar_wait_addr(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+                alive = false;
+                break;
               }
-              if (dynamic_a) {
-                const int a_tile = ((j * p.block_k) >> 5) >> 2;
-                bulk_load(smem_sfa + static_cast<size_t>(s) * 512,
-                          p.act_scales + (static_cast<size_t>(m_tile) * p.act_scale_tiles + a_tile) * 512, 512, &ctl.full[s]);
+              const uint32_t bar = full0 + 8 * s;
+              if (tx_bytes != 0) {
+                mbar_expect_tx_addr(bar, tx_bytes);
+              } else {
+                mbar_arrive_addr(bar);
               }
+              if (load_a) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
+              if (load_b) tma_load_2d_addr(smem_b + s * kBBytes, &weight_map, bar, k0, n0);
+              if (!INT8) {
+                const int w_tile = k0 >> 7;
+#pragma unroll
+                for (int i = 0; i < kScaleTilesB; ++i) {
+                  bulk_load_addr(smem_sfb + (s * kScaleTilesB + i) * 512, sfb_src[i] + static_cast<size_t>(w_tile) * 512, 512, bar);
+                }
+                if (dynamic_a) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
+              }
+              if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
             }
           }
         }
@@ -310,85 +338,116 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   } else if (warp == 1) {
     // ===== MMA issuer =====
     if (lane == 0) {
-      uint32_t it = 0, tile_it = 0;
+      const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
+      const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
+      const uint32_t idesc = INT8 ? idesc_i8(BN) : idesc_mxf8(BN);
+      const int k_iters = taps * p.k_chunks;
+      uint32_t s = 0, phase = 0, set = 0, tile_it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x, ++tile_it) {
-        const uint32_t acc = tile_it % kAccStages;
-        if (!mbar_wait(&ctl.tmem_empty[acc], ((tile_it / kAccStages) & 1) ^ 1, &ctl.abort_flag, p.status, kStatusWaitTmemEmpty)) {
-          break;
-        }
+        const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
+        const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
+        if (!mbar_wait_addr(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
-        for (int ki = 0; ki < k_iters; ++ki, ++it) {
-          const int s = it % p.stages;
-          if (!mbar_wait(&ctl.full[s], (it / p.stages) & 1, &ctl.abort_flag, p.status, kStatusWaitFull)) {
+        int j = 0;            // channel chunk within the tap
+        uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
+        for (int ki = 0; ki < k_iters; ++ki) {
+          if (!mbar_wait_addr(full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
             alive = false;
             break;
           }
           tc_fence_after();
-          const int tap = ki / p.k_chunks, j = ki - tap * p.k_chunks;
-          uint32_t a_id0 = 0, b_id0 = 0;
+          uint32_t a_id = 0;
+          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * set, sfb_tmem = tmem + kSfbColumn + kSfbColumns * set;
           if (!INT8) {
-            const int kb_w = (tap * p.cin + j * p.block_k) >> 5;
-            const int kb_a = (j * p.block_k) >> 5;
-            a_id0 = kb_a & 3, b_id0 = kb_w & 3;
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
-              tc_copy_scales(tmem + kSfbColumn + 4 * i, scale_desc(smem_u32(smem_sfb + (static_cast<size_t>(s) * kScaleTilesB + i) * 512)));
+              tc_copy_scales(sfb_tmem + 4 * i, sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4));
             }
-            const uint8_t* sfa = dynamic_a ? smem_sfa + static_cast<size_t>(s) * 512 : smem_sfa_static + (kb_a >> 2) * 512;
-            tc_copy_scales(tmem + kSfaColumn, scale_desc(smem_u32(sfa)));
+            const uint32_t kb_a = j * kKSteps;  // 32-channel block index of the activation chunk
+            if (BK != 128) a_id = kb_a & 3;
+            const uint32_t sfa_tile = dynamic_a ? s : (kb_a >> 2);
+            tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((sfa_tile * 512) >> 4));
           }
-          const uint64_t a_desc = kmajor_desc(smem_u32(smem_a + static_cast<size_t>(s) * a_bytes), p.block_k);
-          const uint64_t b_desc = kmajor_desc(smem_u32(smem_b + static_cast<size_t>(s) * b_bytes), p.block_k);
-          const int k_steps = p.block_k >> 5;
-          for (int k = 0; k < k_steps; ++k) {
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
+#pragma unroll
+          for (int k = 0; k < kKSteps; ++k) {
             const uint32_t accumulate = (ki > 0 || k > 0) ? 1u : 0u;
             if (INT8) {
-              tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_i8(BN), accumulate);
+              tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
             } else {
-              tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_mxf8(BN, a_id0 + k, b_id0 + k), tmem + kSfaColumn,
-                          tmem + kSfbColumn, accumulate);
+              tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc | ((a_id + k) << 29) | ((b_id + k) << 4), sfa_tmem,
+                          sfb_tmem, accumulate);
             }
           }
           tc_commit(&ctl.empty[s]);  // the stage is free once these MMAs have read it
+          if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
+          set ^= 1;
+          if (++j == p.k_chunks) j = 0;
+          if (BK != 128) b_id = (b_id + kKSteps) & 3;
         }
         if (alive) tc_commit(&ctl.tmem_full[acc]);
       }
     }
   } else {
-    // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 =====
+    // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one half of the BN columns =====
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its half
+    const uint32_t bar_id = 1 + half;
     const int row = quarter * 32 + lane;
     const int ry = row / p.tile_w, rx = row - ry * p.tile_w;
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
-    uint32_t tile_it = 0;
+    const uint32_t panels = smem_out + half * 2 * panel_bytes;
+    const bool store = !(p.debug & 4);
+    uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_it) {
       const int nt = tile % p.tiles_n;
       int m = tile / p.tiles_n;
       const int tx = m % p.tiles_x; m /= p.tiles_x;
       const int ty = m % p.tiles_y;
       const int b = m / p.tiles_y;
-      const int x = tx * p.tile_w + rx, y = ty * p.tile_h + ry, n0 = nt * BN;
+      const int x0 = tx * p.tile_w, y0 = ty * p.tile_h, n0 = nt * BN;
+      const int x = x0 + rx, y = y0 + ry;
       const bool valid = row_in_tile && x < p.out_w && y < p.out_h;
       const size_t pixel = (static_cast<size_t>(b) * p.out_h + y) * p.out_w + x;
-      const uint32_t acc = tile_it % kAccStages;
-      if (!mbar_wait(&ctl.tmem_full[acc], (tile_it / kAccStages) & 1, &ctl.abort_flag, p.status, kStatusWaitTmemFull)) break;
+      const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
+      const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
+      if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
       tc_fence_after();
-      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * (BN / 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= p.cout) break;  // warp-uniform
+      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
+        const int n = n0 + half * (BN / 2) + cc * 32;
         uint32_t raw[32];
-        tmem_load_32(lane_addr + c0, raw);
+        tmem_load_32(lane_addr + cc * 32, raw);
         tmem_load_wait();
-        if (valid && !(p.debug & 4)) finish_chunk<INT8>(p, raw, n0 + c0, pixel, b, y, x, a_scale);
+        if (cc == kChunksPerWarp - 1) {
+          // every column this warp owns is in registers: hand the accumulator back before the arithmetic
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
+        }
+        if (n >= p.cout) continue;  // uniform over the four warps of this half
+        uint32_t w[32];
+        finish_chunk<INT8>(p, raw, n, pixel, b, y, x, valid, a_scale, w);
+        const uint32_t panel = panels + (chunk_it & 1u) * panel_bytes;
+        ++chunk_it;
+        if (leader) bulk_wait_read<1>();  // the store that last read this panel has finished with it
+        named_barrier(bar_id, 128);
+        stage_row(panel, row, p.out_elem, w);
+        fence_async_proxy();
+        named_barrier(bar_id, 128);
+        if (leader && store) {
+          tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
+          bulk_commit();
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl.tmem_empty[acc]);
     }
+    if (leader) bulk_wait_read<0>();
   }
 
   if (ctl.abort_flag) {
@@ -415,9 +474,19 @@ struct Plan {
   int tiles_x, tiles_y, tiles_n, total_tiles;
   bool flat;
   int out_h, out_w;
+  size_t smem;
 };
 
-int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_flat, Plan* plan) {
+int out_elem_bytes(int out_mode) {
+  switch (out_mode) {
+    case FIM_OUT_BF16: return 2;
+    case FIM_OUT_F32:
+    case FIM_OUT_INT32: return 4;
+    default: return 1;
+  }
+}
+
+int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_flat, int out_elem, Plan* plan) {
   if (g.batch <= 0 || g.height <= 0 || g.width <= 0 || g.cin <= 0 || g.cout <= 0) return kBadArgument;
   if (g.cin % 32 || g.cout % 32) return kUnsupported;
   if (g.stride_h != 1 || g.stride_w != 1) return kUnsupported;
@@ -430,9 +499,13 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   Plan pl;
   pl.out_h = out_h, pl.out_w = out_w;
   pl.block_k = g.cin % 128 == 0 ? 128 : (g.cin % 64 == 0 ? 64 : 32);
-  int bn = g.cout <= 64 ? 64 : 128;
+  // Output-channel tile: 256 halves the activation re-reads of a wide layer; narrower layers keep two accumulators in
+  // tensor memory so the epilogue overlaps the next tile.
+  int bn = g.cout <= 64 ? 64 : (g.cout % 256 == 0 && g.kh * g.kw * g.cin >= 1024 ? 256 : 128);
   if (g_forced_block_n == 256 && g.cout > 128) bn = 256;
   if (g_forced_block_n == 128 && g.cout > 64) bn = 128;
+  if (g_forced_block_n == 64) bn = 64;
+  if (bn == 64 && g.cout > 64 && !int8) bn = 128;  // a 64-wide tile may only start at column 0 of its scale tile
   pl.block_n = bn;
   pl.flat = pointwise && allow_flat;
   if (pl.flat) {
@@ -459,31 +532,38 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   const long long total = static_cast<long long>(pl.tiles_x) * pl.tiles_y * (pl.flat ? 1 : g.batch) * pl.tiles_n;
   if (total > 0x7fffffffLL) return kUnsupported;
   pl.total_tiles = static_cast<int>(total);
-  const int scale_bytes = int8 ? 0 : ((bn <= 128 ? 1 : bn / 128) * 512 + 512);
-  const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_bytes;
-  pl.stages = kSmemBudget / stage_bytes;
+  // shared memory: alignment slack + 4 output panels + static activation-scale tiles + the stage ring
+  const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_tiles_b(bn) * 512 + 512;
+  const int fixed = 1024 + 4 * 4096 * out_elem + ((g.cin + 127) / 128) * 512;
+  pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
+  pl.smem = static_cast<size_t>(fixed) + static_cast<size_t>(pl.stages) * stage_bytes;
   const int sms = g_max_ctas > 0 && g_max_ctas < 148 ? g_max_ctas : 148;
   pl.ctas = pl.total_tiles < sms ? pl.total_tiles : sms;
   *plan = pl;
   return kOk;
 }
 
-template <bool INT8, int BN>
-int launch_conv(const CUtensorMap& act_map, const CUtensorMap& weight_map, const ConvParams& p, int ctas, cudaStream_t stream) {
-  const int scale_tiles_b = BN <= 128 ? 1 : BN / 128;
-  const size_t smem = 1024 + static_cast<size_t>(p.stages) * (kTileM * p.block_k + BN * p.block_k + scale_tiles_b * 512 + 512) +
-                      static_cast<size_t>((p.cin + 127) / 128) * 512;
+template <bool INT8, int BN, int BK>
+int launch_conv(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& out_map, const ConvParams& p,
+                const Plan& pl, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(conv_kernel<INT8, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    const cudaError_t e = cudaFuncSetAttribute(conv_kernel<INT8, BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  if (smem > 226 * 1024) return kUnsupported;
-  conv_kernel<INT8, BN><<<ctas, kThreads, smem, stream>>>(act_map, weight_map, p);
+  conv_kernel<INT8, BN, BK><<<pl.ctas, kThreads, pl.smem, stream>>>(act_map, weight_map, out_map, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <bool INT8, int BN>
+int launch_conv_k(const CUtensorMap& a, const CUtensorMap& w, const CUtensorMap& o, const ConvParams& p, const Plan& pl,
+                  cudaStream_t stream) {
+  if (pl.block_k == 128) return launch_conv<INT8, BN, 128>(a, w, o, p, pl, stream);
+  if (pl.block_k == 64) return launch_conv<INT8, BN, 64>(a, w, o, p, pl, stream);
+  return launch_conv<INT8, BN, 32>(a, w, o, p, pl, stream);
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
@@ -491,7 +571,10 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* act_scales, const void* weight,
              const void* weight_scales, const float* a_scale, const float* w_scale, const FimConvGeometry* g,
              const FimConvEpilogue* ep, void* out, int* status, void* stream) {
-  if (x == nullptr || weight == nullptr || g == nullptr || ep == nullptr || out == nullptr) return kBadArgument;
+  if (g == nullptr || ep == nullptr) return kBadArgument;
+  if (g->batch == 0 || g->height == 0 || g->width == 0) return kOk;
+  if (x == nullptr || weight == nullptr || out == nullptr) return kBadArgument;
+  if (ep->act < 0 || ep->act > 2 || ep->out_mode < 0 || ep->out_mode > 5) return kBadArgument;
   if (int8) {
     if (ep->out_mode != FIM_OUT_INT32 && (a_scale == nullptr || w_scale == nullptr)) return kBadArgument;
     if (ep->out_mode != FIM_OUT_BF16 && ep->out_mode != FIM_OUT_INT8 && ep->out_mode != FIM_OUT_INT32) return kBadArgument;
@@ -503,19 +586,18 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     if (ep->out_mode == FIM_OUT_E4M3_STATIC && ep->out_exponent == nullptr) return kBadArgument;
     if (ep->out_mode == FIM_OUT_E4M3_DYNAMIC && ep->out_scales == nullptr) return kBadArgument;
   }
-  if (ep->act < 0 || ep->act > 2 || ep->out_mode < 0 || ep->out_mode > 5) return kBadArgument;
   if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || (ep->bias && !aligned16(ep->bias)) ||
-      (weight_scales && !aligned16(weight_scales)) || (act_scales && !aligned16(act_scales))) {
+      (weight_scales && !aligned16(weight_scales)) || (act_scales && !aligned16(act_scales)) || (w_scale && !aligned16(w_scale))) {
     return kBadLayout;
   }
-  if (g->batch == 0 || g->height == 0 || g->width == 0) return kOk;
+  const int out_elem = out_elem_bytes(ep->out_mode);
 
   // a 1x1 conv is a plain GEMM over flattened pixels when the residual (if any) is dense NHWC
   bool allow_flat = true;
   Plan pl;
   {
     Plan probe;
-    const int rc0 = make_plan(*g, int8, act_scales != nullptr, true, &probe);
+    const int rc0 = make_plan(*g, int8, act_scales != nullptr, true, out_elem, &probe);
     if (rc0 != kOk) return rc0;
     if (probe.flat && ep->residual != nullptr) {
       const long long c = ep->res_stride[3], xs = ep->res_stride[2], ys = ep->res_stride[1], bs = ep->res_stride[0];
@@ -523,16 +605,16 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
       if (!dense) allow_flat = false;
     }
   }
-  const int rc = make_plan(*g, int8, act_scales != nullptr, allow_flat, &pl);
+  const int rc = make_plan(*g, int8, act_scales != nullptr, allow_flat, out_elem, &pl);
   if (rc != kOk) return rc;
 
   ConvParams p;
-  p.batch = g->batch, p.height = g->height, p.width = g->width, p.cin = g->cin, p.cout = g->cout;
+  p.cin = g->cin, p.cout = g->cout;
   p.out_h = pl.out_h, p.out_w = pl.out_w;
   p.kh = g->kh, p.kw = g->kw, p.pad_h = g->pad_h, p.pad_w = g->pad_w, p.dil_h = g->dil_h, p.dil_w = g->dil_w;
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
   p.total_tiles = pl.total_tiles;
-  p.block_k = pl.block_k, p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages;
+  p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages;
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;
@@ -544,47 +626,58 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.residual = static_cast<const __nv_bfloat16*>(ep->residual);
   for (int i = 0; i < 4; ++i) p.res_stride[i] = ep->res_stride[i];
   p.res_channels = ep->res_channels > 0 ? ep->res_channels : g->cout;
-  p.act = ep->act, p.out_mode = ep->out_mode;
+  p.act = ep->act, p.out_mode = ep->out_mode, p.out_elem = out_elem;
   p.out_exponent = ep->out_exponent;
   p.out_scales = static_cast<uint8_t*>(ep->out_scales);
   p.out_scale = ep->out_scale;
-  p.out = out;
   p.status = status;
   p.debug = g_debug_flags;
 
-  // tensor maps: activations [B, H, W, Cin] (flat: [1, 1, B*H*W, Cin]) and weights [Cout, K]
-  long long eff_b = g->batch, eff_h = g->height, eff_w = g->width;
+  // tensor maps: activations [B, H, W, Cin] and outputs [B, Ho, Wo, Cout * elem bytes] (a flat 1x1 conv sees one row of
+  // B*H*W pixels), weights [Cout, K]
+  long long in_b = g->batch, in_h = g->height, in_w = g->width, o_b = g->batch, o_h = pl.out_h, o_w = pl.out_w;
   if (pl.flat) {
-    eff_w = static_cast<long long>(g->batch) * g->height * g->width;
-    eff_h = 1, eff_b = 1;
-    p.batch = 1, p.height = 1, p.out_h = 1;
-    p.width = p.out_w = static_cast<int>(eff_w);
+    in_w = o_w = static_cast<long long>(g->batch) * g->height * g->width;
+    in_h = o_h = 1, in_b = o_b = 1;
+    p.out_h = 1, p.out_w = static_cast<int>(o_w);
     if (p.residual != nullptr) p.res_stride[0] = 0, p.res_stride[1] = 0;  // dense: the flat column index addresses it
   }
-  CUtensorMap act_map, weight_map;
-  const uint64_t adims[4] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(eff_w), static_cast<uint64_t>(eff_h),
-                             static_cast<uint64_t>(eff_b)};
-  const uint64_t astrides[3] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(eff_w) * g->cin,
-                                static_cast<uint64_t>(eff_h) * eff_w * g->cin};
-  const uint32_t abox[4] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.tile_w), static_cast<uint32_t>(pl.tile_h), 1};
-  int rcm = make_tensor_map(&act_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x, adims, astrides, abox, swizzle_for_bytes(pl.block_k));
-  if (rcm != kOk) return rcm;
-  const uint64_t k_total = static_cast<uint64_t>(g->kh) * g->kw * g->cin;
-  const uint64_t wdims[2] = {k_total, static_cast<uint64_t>(g->cout)};
-  const uint64_t wstrides[1] = {k_total};
-  const uint32_t wbox[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n)};
-  rcm = make_tensor_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, wdims, wstrides, wbox, swizzle_for_bytes(pl.block_k));
-  if (rcm != kOk) return rcm;
+  CUtensorMap act_map, weight_map, out_map;
+  {
+    const uint64_t dims[4] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w), static_cast<uint64_t>(in_h),
+                              static_cast<uint64_t>(in_b)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w) * g->cin,
+                                 static_cast<uint64_t>(in_h) * in_w * g->cin};
+    const uint32_t box[4] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.tile_w), static_cast<uint32_t>(pl.tile_h), 1};
+    const int rcm = make_tensor_map(&act_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x, dims, strides, box, swizzle_for_bytes(pl.block_k));
+    if (rcm != kOk) return rcm;
+  }
+  {
+    const uint64_t k_total = static_cast<uint64_t>(g->kh) * g->kw * g->cin;
+    const uint64_t dims[2] = {k_total, static_cast<uint64_t>(g->cout)};
+    const uint64_t strides[1] = {k_total};
+    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n)};
+    const int rcm = make_tensor_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, dims, strides, box, swizzle_for_bytes(pl.block_k));
+    if (rcm != kOk) return rcm;
+  }
+  {
+    const uint64_t row = static_cast<uint64_t>(g->cout) * out_elem;
+    const uint64_t dims[4] = {row, static_cast<uint64_t>(o_w), static_cast<uint64_t>(o_h), static_cast<uint64_t>(o_b)};
+    const uint64_t strides[3] = {row, static_cast<uint64_t>(o_w) * row, static_cast<uint64_t>(o_h) * o_w * row};
+    const uint32_t box[4] = {static_cast<uint32_t>(32 * out_elem), static_cast<uint32_t>(pl.tile_w), static_cast<uint32_t>(pl.tile_h), 1};
+    const int rcm = make_tensor_map(&out_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, out, dims, strides, box, swizzle_for_bytes(32 * out_elem));
+    if (rcm != kOk) return rcm;
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int8) {
-    if (pl.block_n == 64) return launch_conv<true, 64>(act_map, weight_map, p, pl.ctas, s);
-    if (pl.block_n == 128) return launch_conv<true, 128>(act_map, weight_map, p, pl.ctas, s);
-    return launch_conv<true, 256>(act_map, weight_map, p, pl.ctas, s);
+    if (pl.block_n == 64) return launch_conv_k<true, 64>(act_map, weight_map, out_map, p, pl, s);
+    if (pl.block_n == 128) return launch_conv_k<true, 128>(act_map, weight_map, out_map, p, pl, s);
+    return launch_conv_k<true, 256>(act_map, weight_map, out_map, p, pl, s);
   }
-  if (pl.block_n == 64) return launch_conv<false, 64>(act_map, weight_map, p, pl.ctas, s);
-  if (pl.block_n == 128) return launch_conv<false, 128>(act_map, weight_map, p, pl.ctas, s);
-  return launch_conv<false, 256>(act_map, weight_map, p, pl.ctas, s);
+  if (pl.block_n == 64) return launch_conv_k<false, 64>(act_map, weight_map, out_map, p, pl, s);
+  if (pl.block_n == 128) return launch_conv_k<false, 128>(act_map, weight_map, out_map, p, pl, s);
+  return launch_conv_k<false, 256>(act_map, weight_map, out_map, p, pl, s);
 }
 
 }  // namespace
@@ -608,7 +701,7 @@ extern "C" int fim_int8_conv2d(const void* x, const void* weight, const float* a
 extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]) {
   if (geometry == nullptr || plan == nullptr) return kBadArgument;
   Plan pl;
-  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, &pl);
+  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, &pl);
   if (rc != kOk) return rc;
   plan[0] = pl.tile_h, plan[1] = pl.tile_w, plan[2] = pl.block_n, plan[3] = pl.block_k, plan[4] = pl.stages, plan[5] = pl.ctas;
   return kOk;
