@@ -272,22 +272,31 @@ __device__ __forceinline__ uint64_t scale_desc(uint32_t smem_addr) {
 
 // ---- number formats ------------------------------------------------------------------------------------------------
 
-// Unbiased E8M0 exponent of a block with maximum magnitude `amax`: the fp32 expression ceil(log2(amax / 448)) clamped
-// to [-127, 127], -127 for amax == 0. The result only depends on which side of an integer the fp32 logarithm falls;
-// log2f decides that except within 1e-3 of an integer, where the double-precision logarithm rounded to fp32 is used
-// (it reproduces the fp32 rounding of k + epsilon to k for values a few ulp above 448 * 2**k).
+// Unbiased E8M0 exponent of a block with maximum magnitude `amax` (>= 0): the reference's fp32 expression
+// clamp(ceil(log2(amax / 448)), -127, 127), -127 for amax == 0, evaluated without floating point. With
+// amax = m * 2**E (1 <= m < 2) the value is E - 8 when m <= 1.75 and E - 7 above, except that the fp32 logarithm of a
+// ratio a few ulp above one rounds back to the integer E - 8: the reference keeps E - 8 for mantissas up to `slack` ulp
+// above 1.75, where slack (0, 2, 4, 9, 20, 39) only depends on the binade of |E - 8|, i.e. on the ulp of the fp32 number
+// E - 8 + epsilon. The thresholds were read off the reference expression for every exponent and the rule reproduces it
+// on all boundary cases (tests compare the bytes).
 __device__ __forceinline__ int e8m0_exponent(float amax) {
-  if (amax == 0.0f) return -127;
-  const float v = __fdiv_rn(amax, 448.0f);
-  float l = log2f(v);
-  const float frac = l - floorf(l);
-  if (!(frac > 1e-3f && frac < 1.0f - 1e-3f)) l = static_cast<float>(log2(static_cast<double>(v)));
-  const float c = fminf(fmaxf(ceilf(l), -127.0f), 127.0f);
-  return static_cast<int>(c);
+  const uint32_t bits = __float_as_uint(amax);
+  if (bits == 0u) return -127;
+  const int E = static_cast<int>(bits >> 23) - 127;
+  if (E == 128) return 127;  // inf / nan
+  const int k = E - 8;
+  const int m = k >= 0 ? k : -k - 1;
+  const int binade = min(5, max(0, 30 - __clz(m)));
+  const uint32_t slack = static_cast<uint32_t>(0x271409040200ull >> (8 * binade)) & 0xFFu;
+  const uint32_t threshold = 0x600000u + slack + (E == -119 ? 1u : 0u);
+  const int e = (bits & 0x7FFFFFu) > threshold ? k + 1 : k;
+  return min(127, max(-127, e));
 }
 
 // 2**e for e in [-127, 127], exact (2**-127 is a subnormal).
-__device__ __forceinline__ float exp2_int(int e) { return scalbnf(1.0f, e); }
+__device__ __forceinline__ float exp2_int(int e) {
+  return __uint_as_float(e == -127 ? 0x00400000u : static_cast<uint32_t>(e + 127) << 23);
+}
 
 // Two fp32 -> two E4M3 bytes (round to nearest even, saturating to +-448); `lo` lands in the low byte.
 __device__ __forceinline__ uint16_t e4m3x2(float lo, float hi) {
@@ -316,6 +325,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // GELU, erf form, in the operation order of torch's CPU kernel: x * 0.5 * (1 + erf(x * sqrt(1/2))).
 __device__ __forceinline__ float gelu_erf(float x) { return x * 0.5f * (1.0f + erff(x * 0.70710678118654752440f)); }
 
+// ---- packed fp32 pairs (one issue slot for two lanes' worth of fp32 work) -------------------------------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// bf16x2 word -> its two values as a packed fp32 pair (low half first)
+__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t w) { return pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u)); }
+
 // GELU through the complementary error function in the rational-exponential form of Abramowitz & Stegun 7.1.26
 // (|error of erf| <= 1.5e-7): gelu(x) = x/2 * (2 - c) for x >= 0 and x/2 * c for x < 0 with c = erfc(|x|/sqrt 2).
 // No branch, two MUFU operations. For every bf16 input with |x| < 3 the bf16-rounded result equals that of the erf form
@@ -330,6 +364,26 @@ __device__ __forceinline__ float gelu_fast(float x) {
   const float c = poly * t * exp2f(-(z * z) * 1.4426950408889634f);
   const float half_x = 0.5f * x;
   return x >= 0.0f ? half_x * (2.0f - c) : half_x * c;
+}
+// The same on a packed pair.
+__device__ __forceinline__ uint64_t gelu_fast2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t z = mul2(pack2(fabsf(x0), fabsf(x1)), pack2(0.70710678118654752440f, 0.70710678118654752440f));
+  float d0, d1;
+  unpack2(fma2(pack2(0.3275911f, 0.3275911f), z, pack2(1.0f, 1.0f)), d0, d1);
+  const uint64_t t = pack2(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+  uint64_t poly = fma2(pack2(1.061405429f, 1.061405429f), t, pack2(-1.453152027f, -1.453152027f));
+  poly = fma2(poly, t, pack2(1.421413741f, 1.421413741f));
+  poly = fma2(poly, t, pack2(-0.284496736f, -0.284496736f));
+  poly = fma2(poly, t, pack2(0.254829592f, 0.254829592f));
+  float a0, a1;
+  unpack2(mul2(mul2(z, z), pack2(-1.4426950408889634f, -1.4426950408889634f)), a0, a1);
+  const uint64_t c = mul2(mul2(poly, t), pack2(exp2f(a0), exp2f(a1)));
+  float c0, c1;
+  unpack2(c, c0, c1);
+  const uint64_t half_x = mul2(x2, pack2(0.5f, 0.5f));
+  return mul2(half_x, pack2(x0 >= 0.0f ? 2.0f - c0 : c0, x1 >= 0.0f ? 2.0f - c1 : c1));
 }
 
 constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2;

@@ -50,7 +50,7 @@ struct ConvParams {
   uint8_t* out_scales;
   const float* out_scale;
   int* status;
-  int debug;  // timing experiments only: 1 = no activation loads, 2 = no weight loads, 4 = no output stores
+  int debug;  // timing experiments only: 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
 
 struct SharedControl {
@@ -62,7 +62,10 @@ struct SharedControl {
   int abort_flag;
 };
 
-__host__ __device__ constexpr int acc_stages(int bn) { return 2 * bn + 16 + 2 * (bn < 128 ? 4 : bn / 32) <= 512 ? 2 : 1; }
+constexpr int kMaxStaticScaleTiles = 16;  // input channels / 128 whose activation scales stay resident in tensor memory
+__host__ __device__ constexpr int acc_stages(int bn) {
+  return 2 * bn + 4 * kMaxStaticScaleTiles + 2 * (bn < 128 ? 4 : bn / 32) <= 512 ? 2 : 1;
+}
 __host__ __device__ constexpr int scale_tiles_b(int bn) { return bn <= 128 ? 1 : bn / 128; }
 
 __device__ __forceinline__ uint32_t idesc_mxf8(int block_n) {
@@ -216,8 +219,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   constexpr int kKSteps = BK / 32;
   constexpr uint32_t kABytes = kTileM * BK, kBBytes = BN * BK;
   constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
-  constexpr uint32_t kSfaColumn = kAccStages * BN;       // two sets of 4 columns
-  constexpr uint32_t kSfbColumn = kSfaColumn + 8;        // two sets of kSfbColumns
+  constexpr uint32_t kSfbColumn = kAccStages * BN;                // two sets of kSfbColumns
+  constexpr uint32_t kSfaColumn = kSfbColumn + 2 * kSfbColumns;   // static scales: 4 columns per 128 input channels, copied
+                                                                  // once; per-pixel scales: two sets of 4 columns
   constexpr int kChunksPerWarp = BN / 64;                // 32-column chunks each epilogue warp owns
 
   extern __shared__ uint8_t smem_dyn[];
@@ -342,6 +346,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
       const uint32_t idesc = INT8 ? idesc_i8(BN) : idesc_mxf8(BN);
       const int k_iters = taps * p.k_chunks;
+      const bool copy_scales = !INT8 && !(p.debug & 8);
+      if (!INT8 && !dynamic_a) {
+        // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
+        const int tiles = (p.cin + 127) / 128;
+        for (int t = 0; t < tiles; ++t) tc_copy_scales(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+      }
       uint32_t s = 0, phase = 0, set = 0, tile_it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x, ++tile_it) {
@@ -359,16 +369,16 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           }
           tc_fence_after();
           uint32_t a_id = 0;
-          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * set, sfb_tmem = tmem + kSfbColumn + kSfbColumns * set;
-          if (!INT8) {
+          const uint32_t kb_a = j * kKSteps;  // 32-channel block index of the activation chunk
+          if (BK != 128) a_id = kb_a & 3;
+          const uint32_t sfb_tmem = tmem + kSfbColumn + kSfbColumns * set;
+          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * (dynamic_a ? set : (kb_a >> 2));
+          if (copy_scales) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
               tc_copy_scales(sfb_tmem + 4 * i, sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4));
             }
-            const uint32_t kb_a = j * kKSteps;  // 32-channel block index of the activation chunk
-            if (BK != 128) a_id = kb_a & 3;
-            const uint32_t sfa_tile = dynamic_a ? s : (kb_a >> 2);
-            tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((sfa_tile * 512) >> 4));
+            if (dynamic_a) tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
           }
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
@@ -419,31 +429,38 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * (BN / 2);
-#pragma unroll 1
-      for (int cc = 0; cc < kChunksPerWarp; ++cc) {
-        const int n = n0 + half * (BN / 2) + cc * 32;
-        uint32_t raw[32];
-        tmem_load_32(lane_addr + cc * 32, raw);
+      // Drain two 32-column chunks at a time into registers (ten warps share a register file quarter three deep, which
+      // caps a thread at 168 registers) and hand the accumulator back as soon as the last chunk is read, before its
+      // arithmetic.
+      constexpr int kGroup = kChunksPerWarp < 2 ? 1 : 2;
+#pragma unroll
+      for (int g = 0; g < kChunksPerWarp; g += kGroup) {
+        uint32_t raw[kGroup][32];
+#pragma unroll
+        for (int i = 0; i < kGroup; ++i) tmem_load_32(lane_addr + (g + i) * 32, raw[i]);
         tmem_load_wait();
-        if (cc == kChunksPerWarp - 1) {
-          // every column this warp owns is in registers: hand the accumulator back before the arithmetic
+        if (g + kGroup >= kChunksPerWarp) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
         }
-        if (n >= p.cout) continue;  // uniform over the four warps of this half
-        uint32_t w[32];
-        finish_chunk<INT8>(p, raw, n, pixel, b, y, x, valid, a_scale, w);
-        const uint32_t panel = panels + (chunk_it & 1u) * panel_bytes;
-        ++chunk_it;
-        if (leader) bulk_wait_read<1>();  // the store that last read this panel has finished with it
-        named_barrier(bar_id, 128);
-        stage_row(panel, row, p.out_elem, w);
-        fence_async_proxy();
-        named_barrier(bar_id, 128);
-        if (leader && store) {
-          tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
-          bulk_commit();
+#pragma unroll
+        for (int i = 0; i < kGroup; ++i) {
+          const int n = n0 + half * (BN / 2) + (g + i) * 32;
+          if (n >= p.cout) continue;  // uniform over the four warps of this half
+          uint32_t w[32];
+          finish_chunk<INT8>(p, raw[i], n, pixel, b, y, x, valid, a_scale, w);
+          const uint32_t panel = panels + (chunk_it & 1u) * panel_bytes;
+          ++chunk_it;
+          if (leader) bulk_wait_read<1>();  // the store that last read this panel has finished with it
+          named_barrier(bar_id, 128);
+          stage_row(panel, row, p.out_elem, w);
+          fence_async_proxy();
+          named_barrier(bar_id, 128);
+          if (leader && store) {
+            tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
+            bulk_commit();
+          }
         }
       }
     }
@@ -496,6 +513,7 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   if (out_h <= 0 || out_w <= 0) return kBadArgument;
   const bool pointwise = g.kh == 1 && g.kw == 1 && g.pad_h == 0 && g.pad_w == 0;
   if (per_pixel && !(pointwise && allow_flat)) return kUnsupported;
+  if (!int8 && !per_pixel && (g.cin + 127) / 128 > kMaxStaticScaleTiles) return kUnsupported;
   Plan pl;
   pl.out_h = out_h, pl.out_w = out_w;
   pl.block_k = g.cin % 128 == 0 ? 128 : (g.cin % 64 == 0 ? 64 : 32);

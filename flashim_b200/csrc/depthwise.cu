@@ -4,9 +4,11 @@
 //
 // Layout of the work. A CTA owns 64 channels x (4 * warps) columns x `tile_rows` rows of one image. Input rows
 // (with their 2-pixel halo, zero-filled outside the image by TMA) stream through a ring of single-row stages in
-// shared memory; a lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 x 2 weights and five rows
-// of partial sums in registers, and finishes one output row per input row. A 32-channel MX block is 16 adjacent
-// lanes, reduced with shuffles.
+// shared memory; a lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 weight pairs and five rows
+// of partial sums in registers as packed fp32 pairs (fma.rn.f32x2: both channels in one issue slot), and finishes one
+// output row per input row. The kernel is bound by the fp32 pipe (25 FMAs per element), not by HBM alone, so the issue
+// slots beside the FMAs are what is budgeted: one 32-bit shared-memory load per input word, packed bias / GELU math, one
+// redux per 32-channel MX block (16 adjacent lanes).
 #include "common.cuh"
 #include "flashim_sm100.h"
 
@@ -16,7 +18,7 @@ namespace {
 constexpr int kChannels = 64;  // per CTA: one 128-byte line per pixel
 constexpr int kCols = 4;       // output columns per lane
 constexpr int kStages = 8;     // single-row stages in the ring
-constexpr int kMaxWarps = 10;
+constexpr int kMinWarps = 4, kMaxWarps = 8;
 
 enum { kOutBf16 = 0, kOutMx = 1, kOutInt8 = 2 };
 
@@ -32,24 +34,35 @@ struct DwParams {
   int* status;
 };
 
+__device__ __forceinline__ uint64_t activate2(uint64_t v, int act) {
+  if (act == kActGelu) return gelu_fast2(v);
+  if (act == kActRelu) {
+    float lo, hi;
+    unpack2(v, lo, hi);
+    return pack2(fmaxf(lo, 0.0f), fmaxf(hi, 0.0f));
+  }
+  return v;
+}
+
 template <int MODE>
-__device__ __forceinline__ void emit_row(const DwParams& p, const float (&acc)[kCols][2], const float2 bias, int b, int y,
-                                         int x0, int c, bool lane_active, float int8_scale) {
+__device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, int b, int y, int x0,
+                                         int c, bool lane_active, float int8_scale) {
   const int groups = p.channels >> 5;
+  const size_t row_pixel = (static_cast<size_t>(b) * p.height + y) * p.width;
 #pragma unroll
   for (int j = 0; j < kCols; ++j) {
     const int x = x0 + j;
-    const bool store = lane_active && x < p.width;  // warp-uniform in x; shuffles below run for every lane
-    const size_t pixel = (static_cast<size_t>(b) * p.height + y) * p.width + x;
-    float lo = activate(acc[j][0] + bias.x, p.act);
-    float hi = activate(acc[j][1] + bias.y, p.act);
+    const bool store = lane_active && x < p.width;  // x is warp-uniform; the reductions below run in every lane
+    const size_t pixel = row_pixel + x;
+    float lo, hi;
+    unpack2(activate2(add2(acc[j], bias2), p.act), lo, hi);
     if (MODE == kOutBf16) {
       if (store) reinterpret_cast<uint32_t*>(p.out)[(pixel * p.channels + c) >> 1] = pack_bf16(lo, hi);
     } else if (MODE == kOutMx) {
-      float amax = lane_active ? fmaxf(fabsf(lo), fabsf(hi)) : 0.0f;
-#pragma unroll
-      for (int m = 1; m < 16; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-      const int e = e8m0_exponent(amax);
+      // non-negative floats order like their bit patterns: one integer redux per 16-lane block
+      const uint32_t mine = lane_active ? __float_as_uint(fmaxf(fabsf(lo), fabsf(hi))) : 0u;
+      const uint32_t mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+      const int e = e8m0_exponent(__uint_as_float(__reduce_max_sync(mask, mine)));
       const float inv = exp2_int(-e);
       if (store) {
         reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] = e4m3x2(lo * inv, hi * inv);
@@ -70,7 +83,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const float (&acc)[k
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
+__global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
@@ -79,8 +92,7 @@ __global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_cons
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_cols = warps * kCols;
-  const int row_pixels = tile_cols + 4;
-  const uint32_t row_bytes = row_pixels * kChannels * 2;
+  const uint32_t row_bytes = (tile_cols + 4) * kChannels * 2;
 
   // tile decode: x fastest, then y, channel tile, batch
   int t = blockIdx.x;
@@ -104,10 +116,11 @@ __global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_cons
   }
   __syncthreads();
 
+  const uint32_t smem0 = smem_u32(smem_raw), full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
   auto issue_row = [&](int r) {  // input row r of this tile -> stage r % kStages
     const int s = r % kStages;
-    mbar_expect_tx(&full_bar[s], row_bytes);
-    tma_load_4d(smem_raw + static_cast<size_t>(s) * row_bytes, &in_map, &full_bar[s], c_base, x_base - 2, y_base - 2 + r, b);
+    mbar_expect_tx_addr(full0 + 8 * s, row_bytes);
+    tma_load_4d_addr(smem0 + s * row_bytes, &in_map, full0 + 8 * s, c_base, x_base - 2, y_base - 2 + r, b);
   };
   if (threadIdx.x == 0) {
     for (int r = 0; r < min(kStages - 1, rows_in); ++r) issue_row(r);
@@ -115,22 +128,22 @@ __global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_cons
 
   const int c = c_base + 2 * lane;
   const bool lane_active = c < p.channels;
-  float2 w[25];
+  uint64_t w[25];
 #pragma unroll
   for (int k = 0; k < 25; ++k) {
-    const uint32_t word = lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u;
-    w[k] = make_float2(bf16_lo(word), bf16_hi(word));
+    w[k] = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
   }
-  const float2 bias = lane_active ? make_float2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : make_float2(0.f, 0.f);
+  const uint64_t bias2 = lane_active ? pack2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : pack2(0.f, 0.f);
   const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
 
-  float acc[5][kCols][2];
+  uint64_t acc[5][kCols];
 #pragma unroll
   for (int s = 0; s < 5; ++s)
 #pragma unroll
-    for (int j = 0; j < kCols; ++j) acc[s][j][0] = acc[s][j][1] = 0.0f;
+    for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // two +0.0f
 
   const int x0 = x_base + warp * kCols;
+  const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
   bool alive = true;
   for (int r0 = 0; r0 < rows_in && alive; r0 += 5) {
 #pragma unroll
@@ -141,48 +154,45 @@ __global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_cons
       if (threadIdx.x == 0 && r + kStages - 1 < rows_in) {
         if (r >= 1) {
           const int back = r - 1;
-          if (!mbar_wait(&empty_bar[back % kStages], (back / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
-            alive = false;
-          }
+          alive = mbar_wait_addr(empty0 + 8 * (back % kStages), (back / kStages) & 1, &abort_flag, p.status, kStatusWaitRows);
         }
         if (alive) issue_row(r + kStages - 1);
       }
-      alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;  // warp 0 learns of its lane 0 giving up
+      if (warp == 0) alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;  // warp 0 learns of its lane 0 giving up
       if (!alive) break;
       const int s = r % kStages;
-      if (!mbar_wait(&full_bar[s], (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
+      if (!mbar_wait_addr(full0 + 8 * s, (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
         alive = false;
         break;
       }
-      const uint32_t* row = reinterpret_cast<const uint32_t*>(smem_raw + static_cast<size_t>(s) * row_bytes) +
-                            (warp * kCols) * (kChannels / 2) + lane;
-      float in[kCols + 4][2];
+      uint64_t in[kCols + 4];
 #pragma unroll
       for (int j = 0; j < kCols + 4; ++j) {
-        const uint32_t word = row[j * (kChannels / 2)];
-        in[j][0] = bf16_lo(word);
-        in[j][1] = bf16_hi(word);
+        uint32_t word;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(word) : "r"(lane_smem + s * row_bytes + j * (kChannels * 2)));
+        in[j] = bf16x2_to_f32x2(word);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      if (lane == 0) mbar_arrive_addr(empty0 + 8 * s);
 #pragma unroll
       for (int ky = 0; ky < 5; ++ky) {
-        const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
+        const int oy = r - ky;  // output row of this tile that tap row ky of input row r feeds
+        if (oy < 0 || oy >= rows_out) continue;  // uniform: rows above / below the tile get no arithmetic
+        const int slot = (ph - ky + 5) % 5;
 #pragma unroll
         for (int kx = 0; kx < 5; ++kx) {
 #pragma unroll
-          for (int j = 0; j < kCols; ++j) {
-            acc[slot][j][0] = fmaf(in[j + kx][0], w[ky * 5 + kx].x, acc[slot][j][0]);
-            acc[slot][j][1] = fmaf(in[j + kx][1], w[ky * 5 + kx].y, acc[slot][j][1]);
-          }
+          for (int j = 0; j < kCols; ++j) acc[slot][j] = fma2(in[j + kx], w[ky * 5 + kx], acc[slot][j]);
         }
       }
       // output row r - 4 has now received all five input rows
       const int done = (ph + 1) % 5;
       const int oy = r - 4;
-      if (oy >= 0 && oy < rows_out) emit_row<MODE>(p, acc[done], bias, b, y_base + oy, x0, c, lane_active, int8_scale);
+      if (oy >= 0) {
+        emit_row<MODE>(p, acc[done], bias2, b, y_base + oy, x0, c, lane_active, int8_scale);
 #pragma unroll
-      for (int j = 0; j < kCols; ++j) acc[done][j][0] = acc[done][j][1] = 0.0f;
+        for (int j = 0; j < kCols; ++j) acc[done][j] = 0ull;
+      }
     }
   }
   if (!alive) {
@@ -194,12 +204,13 @@ __global__ void __launch_bounds__(32 * kMaxWarps) dw5x5_kernel(const __grid_cons
 }
 
 int pick_warps(int width) {
-  int best = 8;
+  // fewest idle columns in the last tile of a row; on ties the narrower CTA (more CTAs per SM, better latency hiding)
+  int best = kMinWarps;
   double best_eff = 0.0;
-  for (int w = 5; w <= kMaxWarps; ++w) {
+  for (int w = kMinWarps; w <= kMaxWarps; ++w) {
     const int cols = w * kCols;
     const double eff = static_cast<double>(width) / (static_cast<double>(ceil_div(width, cols)) * cols);
-    if (eff > best_eff + 1e-9 || (eff > best_eff - 1e-9 && w >= best)) {
+    if (eff > best_eff + 1e-9) {
       best_eff = eff;
       best = w;
     }
@@ -208,12 +219,13 @@ int pick_warps(int width) {
 }
 
 int pick_tile_rows(int height, long long tiles_per_row_band) {
-  // Rows per CTA: tall enough that the 4 halo rows cost little, short enough that the grid fills 148 SMs several times.
+  // Rows per CTA: tall enough that the 4 halo rows (loaded, not computed on) cost little, short enough that the grid
+  // fills the 148 SMs several times over at 3-4 resident CTAs each.
   const int candidates[] = {64, 50, 40, 32, 25, 20, 16, 10, 8};
   for (int rows : candidates) {
     if (rows > height && rows != 8) continue;
     const long long ctas = tiles_per_row_band * ceil_div(height, rows);
-    if (ctas >= 148LL * 6) return rows;
+    if (ctas >= 148LL * 16) return rows;
   }
   return height < 8 ? height : 8;
 }
@@ -256,12 +268,6 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   if (rc != kOk) return rc;
 
   const size_t smem = static_cast<size_t>(kStages) * (tile_cols + 4) * kChannels * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(dw5x5_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
   dw5x5_kernel<MODE><<<static_cast<unsigned>(ctas), warps * 32, smem, static_cast<cudaStream_t>(stream)>>>(map, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -278,13 +284,13 @@ extern "C" int fim_dw5x5_bf16(const void* value, const void* weight, const float
 
 extern "C" int fim_dw5x5_mxfp8(const void* value, const void* weight, const float* bias, void* out, void* scales, int swizzled,
                                int batch, int height, int width, int channels, int act, int* status, void* stream) {
-  if (scales == nullptr) return kBadArgument;
+  if (scales == nullptr && batch > 0 && height > 0 && width > 0) return kBadArgument;
   return launch<kOutMx>(value, weight, bias, out, scales, nullptr, swizzled, batch, height, width, channels, act, status, stream);
 }
 
 extern "C" int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias, const float* scale, void* out,
                                    int batch, int height, int width, int channels, int* status, void* stream) {
-  if (scale == nullptr) return kBadArgument;
+  if (scale == nullptr && batch > 0 && height > 0 && width > 0) return kBadArgument;
   return launch<kOutInt8>(value, weight, bias, out, nullptr, scale, 0, batch, height, width, channels, kActRelu, status, stream);
 }
 

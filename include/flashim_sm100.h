@@ -137,7 +137,7 @@ int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scale
 
 /* Tuning and measurement hooks for the following conv launches of this process (all 0 = automatic / off):
  * `block_n` forces the output-channel tile (64 / 128 / 256); `max_ctas` caps the persistent grid; `debug_flags` is for
- * timing experiments only and makes results invalid (1: skip activation loads, 2: skip weight loads, 4: skip stores). */
+ * timing experiments only and makes results invalid (1: skip activation loads, 2: skip weight loads, 4: skip stores, 8: skip scale copies). */
 void fim_conv_tune(int block_n, int max_ctas, int debug_flags);
 
 #ifdef __cplusplus
