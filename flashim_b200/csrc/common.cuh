@@ -354,36 +354,41 @@ __device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t w) { return pack2(_
 // (|error of erf| <= 1.5e-7): gelu(x) = x/2 * (2 - c) for x >= 0 and x/2 * c for x < 0 with c = erfc(|x|/sqrt 2).
 // No branch, two MUFU operations. For every bf16 input with |x| < 3 the bf16-rounded result equals that of the erf form
 // above; beyond x < -4.5 (|gelu| < 2e-5) both forms are dominated by their own rounding.
-__device__ __forceinline__ float gelu_fast(float x) {
-  const float z = fabsf(x) * 0.70710678118654752440f;
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float c = poly * t * exp2f(-(z * z) * 1.4426950408889634f);
-  const float half_x = 0.5f * x;
-  return x >= 0.0f ? half_x * (2.0f - c) : half_x * c;
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
-// The same on a packed pair.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// On a packed pair, arranged for issue slots: 0.5 x + 0.5 |x| (1 - c) with c = erfc(|x| / sqrt 2) avoids the
+// sign select, and the two MUFU operations per lane take their operands straight from the halves of the pair.
 __device__ __forceinline__ uint64_t gelu_fast2(uint64_t x2) {
   float x0, x1;
   unpack2(x2, x0, x1);
-  const uint64_t z = mul2(pack2(fabsf(x0), fabsf(x1)), pack2(0.70710678118654752440f, 0.70710678118654752440f));
+  const uint64_t ax = pack2(fabsf(x0), fabsf(x1));
   float d0, d1;
-  unpack2(fma2(pack2(0.3275911f, 0.3275911f), z, pack2(1.0f, 1.0f)), d0, d1);
-  const uint64_t t = pack2(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+  unpack2(fma2(pack2(0.23164190f, 0.23164190f), ax, pack2(1.0f, 1.0f)), d0, d1);  // 1 + 0.3275911 |x| / sqrt 2
+  const uint64_t t = pack2(rcp_approx(d0), rcp_approx(d1));
   uint64_t poly = fma2(pack2(1.061405429f, 1.061405429f), t, pack2(-1.453152027f, -1.453152027f));
   poly = fma2(poly, t, pack2(1.421413741f, 1.421413741f));
   poly = fma2(poly, t, pack2(-0.284496736f, -0.284496736f));
   poly = fma2(poly, t, pack2(0.254829592f, 0.254829592f));
   float a0, a1;
-  unpack2(mul2(mul2(z, z), pack2(-1.4426950408889634f, -1.4426950408889634f)), a0, a1);
-  const uint64_t c = mul2(mul2(poly, t), pack2(exp2f(a0), exp2f(a1)));
-  float c0, c1;
-  unpack2(c, c0, c1);
-  const uint64_t half_x = mul2(x2, pack2(0.5f, 0.5f));
-  return mul2(half_x, pack2(x0 >= 0.0f ? 2.0f - c0 : c0, x1 >= 0.0f ? 2.0f - c1 : c1));
+  unpack2(mul2(mul2(x2, x2), pack2(-0.72134752044448170f, -0.72134752044448170f)), a0, a1);  // -x^2 / 2 * log2(e)
+  const uint64_t c = mul2(mul2(poly, t), pack2(ex2_approx(a0), ex2_approx(a1)));
+  const uint64_t one_minus_c = fma2(c, pack2(-1.0f, -1.0f), pack2(1.0f, 1.0f));
+  const uint64_t half = pack2(0.5f, 0.5f);
+  return fma2(mul2(ax, half), one_minus_c, mul2(x2, half));
+}
+
+__device__ __forceinline__ float gelu_fast(float x) {
+  float lo, hi;
+  unpack2(gelu_fast2(pack2(x, x)), lo, hi);
+  return lo;
 }
 
 constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2;

@@ -32,6 +32,7 @@ struct ConvParams {
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
   int k_chunks, stages;
+  int panels_per_half;  // output panels each half of the epilogue rotates through (2 or 4)
   // scales (MXFP8)
   const int8_t* act_exponent;     // static: [cin / 32]
   const uint8_t* act_scales;      // per pixel: swizzled tiles over rows = pixels
@@ -124,7 +125,11 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
   // one bf16 rounding, activation on the rounded value (ReLU waits for the residual when there is one)
   if (p.act == kActGelu) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = bf16_round(gelu_fast(bf16_round(v[i])));
+    for (int i = 0; i < 32; i += 2) {
+      float g0, g1;
+      unpack2(gelu_fast2(pack2(bf16_round(v[i]), bf16_round(v[i + 1]))), g0, g1);
+      v[i] = bf16_round(g0), v[i + 1] = bf16_round(g1);
+    }
   } else if (p.act == kActRelu && !has_res) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = fmaxf(bf16_round(v[i]), 0.0f);
@@ -228,13 +233,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   __shared__ __align__(8) SharedControl ctl;
 
   // dynamic shared memory, 1024-byte aligned:
-  // [stages x A][stages x B][4 output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles]
+  // [stages x A][stages x B][4 or 8 output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles]
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t panel_bytes = 4096u * p.out_elem;
   const uint32_t smem_a = base;
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + p.stages * kBBytes;
-  const uint32_t smem_sfb = smem_out + 4 * panel_bytes;
+  const uint32_t smem_sfb = smem_out + 2 * p.panels_per_half * panel_bytes;
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
 
@@ -411,7 +416,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     const int ry = row / p.tile_w, rx = row - ry * p.tile_w;
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
-    const uint32_t panels = smem_out + half * 2 * panel_bytes;
+    const uint32_t panels = smem_out + half * p.panels_per_half * panel_bytes;
     const bool store = !(p.debug & 4);
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_it) {
@@ -450,9 +455,15 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           if (n >= p.cout) continue;  // uniform over the four warps of this half
           uint32_t w[32];
           finish_chunk<INT8>(p, raw[i], n, pixel, b, y, x, valid, a_scale, w);
-          const uint32_t panel = panels + (chunk_it & 1u) * panel_bytes;
+          const uint32_t panel = panels + (chunk_it & (p.panels_per_half - 1)) * panel_bytes;
           ++chunk_it;
-          if (leader) bulk_wait_read<1>();  // the store that last read this panel has finished with it
+          if (leader) {  // the store that last read this panel has finished with it
+            if (p.panels_per_half == 4) {
+              bulk_wait_read<3>();
+            } else {
+              bulk_wait_read<1>();
+            }
+          }
           named_barrier(bar_id, 128);
           stage_row(panel, row, p.out_elem, w);
           fence_async_proxy();
@@ -487,7 +498,7 @@ int g_max_ctas = 0;
 int g_debug_flags = 0;
 
 struct Plan {
-  int tile_h, tile_w, block_n, block_k, stages, ctas;
+  int tile_h, tile_w, block_n, block_k, stages, ctas, panels_per_half;
   int tiles_x, tiles_y, tiles_n, total_tiles;
   bool flat;
   int out_h, out_w;
@@ -550,9 +561,12 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   const long long total = static_cast<long long>(pl.tiles_x) * pl.tiles_y * (pl.flat ? 1 : g.batch) * pl.tiles_n;
   if (total > 0x7fffffffLL) return kUnsupported;
   pl.total_tiles = static_cast<int>(total);
-  // shared memory: alignment slack + 4 output panels + static activation-scale tiles + the stage ring
+  // shared memory: alignment slack + output panels + static activation-scale tiles + the stage ring. A layer with few
+  // K iterations per tile is bound by its stores: it gets more panels in flight; a long main loop gets the stages.
+  const int k_iters = g.kh * g.kw * (g.cin / pl.block_k);
+  pl.panels_per_half = (k_iters <= 4 && out_elem <= 2) ? 4 : 2;
   const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_tiles_b(bn) * 512 + 512;
-  const int fixed = 1024 + 4 * 4096 * out_elem + ((g.cin + 127) / 128) * 512;
+  const int fixed = 1024 + 2 * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
@@ -632,7 +646,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.kh = g->kh, p.kw = g->kw, p.pad_h = g->pad_h, p.pad_w = g->pad_w, p.dil_h = g->dil_h, p.dil_w = g->dil_w;
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
   p.total_tiles = pl.total_tiles;
-  p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages;
+  p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages, p.panels_per_half = pl.panels_per_half;
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;

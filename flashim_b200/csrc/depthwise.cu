@@ -44,38 +44,71 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v, int act) {
   return v;
 }
 
+// Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's four pixels. Kept out of
+// line: it is reached from the five unrolled phases of the row loop, and inlining it five times made the kernel
+// instruction-cache bound.
 template <int MODE>
-__device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, int b, int y, int x0,
-                                         int c, bool lane_active, float int8_scale) {
+__device__ __noinline__ void emit_row(const DwParams& p, uint64_t a0, uint64_t a1, uint64_t a2, uint64_t a3, uint64_t bias2, int b,
+                                      int y, int x0, int c, bool lane_active, float int8_scale) {
+  const uint64_t acc[kCols] = {a0, a1, a2, a3};
   const int groups = p.channels >> 5;
   const size_t row_pixel = (static_cast<size_t>(b) * p.height + y) * p.width;
+  float lo[kCols], hi[kCols];
 #pragma unroll
-  for (int j = 0; j < kCols; ++j) {
-    const int x = x0 + j;
-    const bool store = lane_active && x < p.width;  // x is warp-uniform; the reductions below run in every lane
-    const size_t pixel = row_pixel + x;
-    float lo, hi;
-    unpack2(activate2(add2(acc[j], bias2), p.act), lo, hi);
-    if (MODE == kOutBf16) {
-      if (store) reinterpret_cast<uint32_t*>(p.out)[(pixel * p.channels + c) >> 1] = pack_bf16(lo, hi);
-    } else if (MODE == kOutMx) {
-      // non-negative floats order like their bit patterns: one integer redux per 16-lane block
-      const uint32_t mine = lane_active ? __float_as_uint(fmaxf(fabsf(lo), fabsf(hi))) : 0u;
-      const uint32_t mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
-      const int e = e8m0_exponent(__uint_as_float(__reduce_max_sync(mask, mine)));
+  for (int j = 0; j < kCols; ++j) unpack2(activate2(add2(acc[j], bias2), p.act), lo[j], hi[j]);
+  if (MODE == kOutBf16) {
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) {
+      if (lane_active && x0 + j < p.width) {
+        reinterpret_cast<uint32_t*>(p.out)[((row_pixel + x0 + j) * p.channels + c) >> 1] = pack_bf16(lo[j], hi[j]);
+      }
+    }
+  } else if (MODE == kOutMx) {
+    // amax of each pixel over the 16 lanes of its 32-channel block by a transposing butterfly: after the exchanges lane
+    // l holds the block maximum of pixel l & 3 (5 shuffles instead of 16), computes that pixel's exponent once, and
+    // the four exponents are read back with one shuffle each.
+    float m[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) m[j] = lane_active ? fmaxf(fabsf(lo[j]), fabsf(hi[j])) : 0.0f;
+    const int lane = threadIdx.x & 31;
+    {
+      const bool odd = lane & 1;  // even lanes keep pixels 0, 1 and odd lanes pixels 2, 3
+      const float s0 = __shfl_xor_sync(0xffffffffu, odd ? m[0] : m[2], 1);
+      const float s1 = __shfl_xor_sync(0xffffffffu, odd ? m[1] : m[3], 1);
+      m[0] = fmaxf(odd ? m[2] : m[0], s0);
+      m[1] = fmaxf(odd ? m[3] : m[1], s1);
+    }
+    {
+      const bool up = lane & 2;  // then bit 1 of the lane picks the second of the pair
+      const float s0 = __shfl_xor_sync(0xffffffffu, up ? m[0] : m[1], 2);
+      m[0] = fmaxf(up ? m[1] : m[0], s0);
+    }
+    m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 4));
+    m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 8));
+    // lane holds pixel ((lane & 1) << 1) | ((lane >> 1) & 1)
+    const int mine = e8m0_exponent(m[0]);
+    const int half = lane & 16;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) {
+      const int src = half | ((j >> 1) & 1) | ((j & 1) << 1);
+      const int e = __shfl_sync(0xffffffffu, mine, src);
       const float inv = exp2_int(-e);
-      if (store) {
-        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] = e4m3x2(lo * inv, hi * inv);
-        if ((threadIdx.x & 15) == 0) {
+      const size_t pixel = row_pixel + x0 + j;
+      if (lane_active && x0 + j < p.width) {
+        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] = e4m3x2(lo[j] * inv, hi[j] * inv);
+        if ((lane & 15) == 0) {
           const int g = c >> 5;
           const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
           p.scales[at] = static_cast<uint8_t>(e + 127);
         }
       }
-    } else {
-      const int qlo = int8_code(bf16_round(lo), int8_scale), qhi = int8_code(bf16_round(hi), int8_scale);
-      if (store) {
-        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] =
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) {
+      const int qlo = int8_code(bf16_round(lo[j]), int8_scale), qhi = int8_code(bf16_round(hi[j]), int8_scale);
+      if (lane_active && x0 + j < p.width) {
+        reinterpret_cast<uint16_t*>(p.out)[((row_pixel + x0 + j) * p.channels + c) >> 1] =
             static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
       }
     }
@@ -174,13 +207,14 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_c
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_addr(empty0 + 8 * s);
+      // 100 packed FMAs in one basic block: tap column outermost, so consecutive instructions belong to 20 different
+      // accumulators and nothing waits on the FMA latency. Rows above / below the tile accumulate too (into sums that
+      // are dropped): a branch per tap row would split the block.
 #pragma unroll
-      for (int ky = 0; ky < 5; ++ky) {
-        const int oy = r - ky;  // output row of this tile that tap row ky of input row r feeds
-        if (oy < 0 || oy >= rows_out) continue;  // uniform: rows above / below the tile get no arithmetic
-        const int slot = (ph - ky + 5) % 5;
+      for (int kx = 0; kx < 5; ++kx) {
 #pragma unroll
-        for (int kx = 0; kx < 5; ++kx) {
+        for (int ky = 0; ky < 5; ++ky) {
+          const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
 #pragma unroll
           for (int j = 0; j < kCols; ++j) acc[slot][j] = fma2(in[j + kx], w[ky * 5 + kx], acc[slot][j]);
         }
@@ -189,18 +223,19 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_c
       const int done = (ph + 1) % 5;
       const int oy = r - 4;
       if (oy >= 0) {
-        emit_row<MODE>(p, acc[done], bias2, b, y_base + oy, x0, c, lane_active, int8_scale);
-#pragma unroll
-        for (int j = 0; j < kCols; ++j) acc[done][j] = 0ull;
+        emit_row<MODE>(p, acc[done][0], acc[done][1], acc[done][2], acc[done][3], bias2, b, y_base + oy, x0, c, lane_active,
+                       int8_scale);
       }
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[done][j] = 0ull;
     }
   }
   if (!alive) {
     // Give copies that are still in flight time to land before the shared memory is released.
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
   }
-  __syncthreads();
 }
 
 int pick_warps(int width) {
@@ -225,7 +260,7 @@ int pick_tile_rows(int height, long long tiles_per_row_band) {
   for (int rows : candidates) {
     if (rows > height && rows != 8) continue;
     const long long ctas = tiles_per_row_band * ceil_div(height, rows);
-    if (ctas >= 148LL * 16) return rows;
+    if (ctas >= 148LL * 3 * 3) return rows;  // three waves of three resident CTAs per SM
   }
   return height < 8 ? height : 8;
 }
