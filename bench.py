@@ -359,7 +359,9 @@ class StackWorkload(Workload):
         from flashim_b200.refiner import LEVELS
 
         self.model = flashim_b200.load("refiner-stack", "fp8", device=device)
-        per_rank = self.PAIRS // world + (1 if rank < self.PAIRS % world else 0)
+        from flashim_b200.sharding import shard_pairs
+
+        _, per_rank = shard_pairs(self.PAIRS, rank, world)
         self.pairs = per_rank
         images = 2 * per_rank
         g = torch.Generator().manual_seed(4 + rank)
@@ -487,58 +489,19 @@ def _cpu_conv_sample(h, c, k, budget_s):
 # ---- driver ------------------------------------------------------------------------------------------------------------------
 
 
-def _dist_setup(gpus: int):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        import torch.distributed as dist
-
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return rank, world, local
-
-
-def _barrier(world: int):
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-    torch.cuda.synchronize()
-
-
-def _max_over_ranks(value: float, world: int, device) -> float:
-    if world == 1:
-        return value
-    import torch.distributed as dist
-
-    t = torch.tensor([value], device=device, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def _sum_over_ranks(value: float, world: int, device) -> float:
-    if world == 1:
-        return value
-    import torch.distributed as dist
-
-    t = torch.tensor([value], device=device, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
-    return float(t.item())
-
-
-def _timed(fn, steps: int, world: int, device) -> float:
+def _timed(fn, steps: int, ranks) -> float:
     """Device time of `steps` calls in ms: CUDA events on the current stream, barrier + synchronise on both sides, max over ranks."""
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    _barrier(world)
+    ranks.barrier()
+    torch.cuda.synchronize()
     start.record()
     for _ in range(steps):
         fn()
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end)
-    _barrier(world)
-    return _max_over_ranks(ms, world, device)
+    ranks.barrier()
+    return ranks.max(ms)
 
 
 def run_reference(args) -> None:
@@ -586,7 +549,10 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the sm_100a kernels have no CPU path")
 
-    rank, world, local = _dist_setup(args.gpus)
+    from flashim_b200.sharding import Ranks
+
+    ranks = Ranks.from_env("nccl")
+    rank, world, local = ranks.rank, ranks.world, ranks.local_rank
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     import flashim_b200
@@ -598,13 +564,13 @@ def main() -> None:
             workload.step()
         torch.cuda.synchronize()
         flashim_b200.check_status(device)
-        ms = _timed(workload.step, args.steps, world, device)
+        ms = _timed(workload.step, args.steps, ranks)
         flashim_b200.check_status(device)
-        units = _sum_over_ranks(workload.units_per_step(), world, device)
+        units = ranks.sum(workload.units_per_step())
         value = units * args.steps / (ms * 1e-3)
         for _ in range(2):
             workload.step_e2e()
-        e2e_ms = _timed(workload.step_e2e, args.steps, world, device)
+        e2e_ms = _timed(workload.step_e2e, args.steps, ranks)
         flashim_b200.check_status(device)
         # keep the device busy long enough for at least a few 200 ms samples
         spin_until = time.perf_counter() + 0.7
@@ -629,10 +595,7 @@ def main() -> None:
             "clocks": sampler.report,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.destroy_process_group()
+    ranks.close()
 
 
 if __name__ == "__main__":

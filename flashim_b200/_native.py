@@ -70,6 +70,7 @@ SIGNATURES: dict[str, tuple] = {
     "fim_int8_conv2d": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_conv_plan": (_I, [ctypes.POINTER(ConvGeometry), _I, _I, ctypes.POINTER(ctypes.c_int * 6)]),
     "fim_conv_tune": (None, [_I, _I, _I]),
+    "fim_dw_tune": (None, [_I]),
 }
 
 

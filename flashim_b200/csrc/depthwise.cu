@@ -18,7 +18,7 @@ namespace {
 constexpr int kChannels = 64;  // per CTA: one 128-byte line per pixel
 constexpr int kCols = 4;       // output columns per lane
 constexpr int kStages = 8;     // single-row stages in the ring
-constexpr int kMinWarps = 4, kMaxWarps = 8;
+constexpr int kMinWarps = 4, kMaxWarps = 5;  // compute warps per CTA (plus one producer warp)
 
 enum { kOutBf16 = 0, kOutMx = 1, kOutInt8 = 2 };
 
@@ -32,11 +32,13 @@ struct DwParams {
   int tile_rows, tiles_x, tiles_y, channel_tiles;
   int act, swizzled;
   int* status;
+  int debug;  // timing experiments only: 1 = no FMAs, 2 = no epilogue, 4 = no loads and no waits for them
 };
 
-__device__ __forceinline__ uint64_t activate2(uint64_t v, int act) {
-  if (act == kActGelu) return gelu_fast2(v);
-  if (act == kActRelu) {
+template <int ACT>
+__device__ __forceinline__ uint64_t activate2(uint64_t v) {
+  if (ACT == kActGelu) return gelu_fast2(v);
+  if (ACT == kActRelu) {
     float lo, hi;
     unpack2(v, lo, hi);
     return pack2(fmaxf(lo, 0.0f), fmaxf(hi, 0.0f));
@@ -44,29 +46,24 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v, int act) {
   return v;
 }
 
-// Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's four pixels. Kept out of
-// line: it is reached from the five unrolled phases of the row loop, and inlining it five times made the kernel
-// instruction-cache bound.
-template <int MODE>
-__device__ __noinline__ void emit_row(const DwParams& p, uint64_t a0, uint64_t a1, uint64_t a2, uint64_t a3, uint64_t bias2, int b,
-                                      int y, int x0, int c, bool lane_active, float int8_scale) {
-  const uint64_t acc[kCols] = {a0, a1, a2, a3};
-  const int groups = p.channels >> 5;
-  const size_t row_pixel = (static_cast<size_t>(b) * p.height + y) * p.width;
+// Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's four pixels. It is
+// inlined next to the FMA block of the following input row, with which it shares no data, so the two interleave.
+template <int MODE, int ACT>
+__device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, size_t row_pixel,
+                                         int x0, int c, bool lane_active, float int8_scale) {
   float lo[kCols], hi[kCols];
 #pragma unroll
-  for (int j = 0; j < kCols; ++j) unpack2(activate2(add2(acc[j], bias2), p.act), lo[j], hi[j]);
+  for (int j = 0; j < kCols; ++j) unpack2(activate2<ACT>(add2(acc[j], bias2)), lo[j], hi[j]);
   if (MODE == kOutBf16) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
-      if (lane_active && x0 + j < p.width) {
-        reinterpret_cast<uint32_t*>(p.out)[((row_pixel + x0 + j) * p.channels + c) >> 1] = pack_bf16(lo[j], hi[j]);
-      }
+      if (lane_active && x0 + j < p.width) out[static_cast<size_t>(j) * (p.channels >> 1)] = pack_bf16(lo[j], hi[j]);
     }
   } else if (MODE == kOutMx) {
     // amax of each pixel over the 16 lanes of its 32-channel block by a transposing butterfly: after the exchanges lane
-    // l holds the block maximum of pixel l & 3 (5 shuffles instead of 16), computes that pixel's exponent once, and
-    // the four exponents are read back with one shuffle each.
+    // l holds the block maximum of one pixel (5 shuffles instead of 16), computes that pixel's exponent once, and the
+    // four exponents are read back with one shuffle each.
     float m[kCols];
 #pragma unroll
     for (int j = 0; j < kCols; ++j) m[j] = lane_active ? fmaxf(fabsf(lo[j]), fabsf(hi[j])) : 0.0f;
@@ -85,18 +82,19 @@ __device__ __noinline__ void emit_row(const DwParams& p, uint64_t a0, uint64_t a
     }
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 4));
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 8));
-    // lane holds pixel ((lane & 1) << 1) | ((lane >> 1) & 1)
+    // this lane now holds pixel ((lane & 1) << 1) | ((lane >> 1) & 1) of its half-warp
     const int mine = e8m0_exponent(m[0]);
     const int half = lane & 16;
+    const int groups = p.channels >> 5;
+    uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
-      const int src = half | ((j >> 1) & 1) | ((j & 1) << 1);
-      const int e = __shfl_sync(0xffffffffu, mine, src);
+      const int e = __shfl_sync(0xffffffffu, mine, half | ((j >> 1) & 1) | ((j & 1) << 1));
       const float inv = exp2_int(-e);
-      const size_t pixel = row_pixel + x0 + j;
       if (lane_active && x0 + j < p.width) {
-        reinterpret_cast<uint16_t*>(p.out)[(pixel * p.channels + c) >> 1] = e4m3x2(lo[j] * inv, hi[j] * inv);
+        out[static_cast<size_t>(j) * (p.channels >> 1)] = e4m3x2(lo[j] * inv, hi[j] * inv);
         if ((lane & 15) == 0) {
+          const size_t pixel = row_pixel + x0 + j;
           const int g = c >> 5;
           const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
           p.scales[at] = static_cast<uint8_t>(e + 127);
@@ -104,25 +102,33 @@ __device__ __noinline__ void emit_row(const DwParams& p, uint64_t a0, uint64_t a
       }
     }
   } else {
+    uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
       const int qlo = int8_code(bf16_round(lo[j]), int8_scale), qhi = int8_code(bf16_round(hi[j]), int8_scale);
       if (lane_active && x0 + j < p.width) {
-        reinterpret_cast<uint16_t*>(p.out)[((row_pixel + x0 + j) * p.channels + c) >> 1] =
-            static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
+        out[static_cast<size_t>(j) * (p.channels >> 1)] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
       }
     }
   }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
+__device__ __forceinline__ uint64_t lds64(uint32_t addr) {
+  uint64_t v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+  return v;
+}
+
+// Thread layout: `warps` compute warps (warp w owns columns 4w .. 4w+3 of the tile) and one producer warp whose lane 0
+// streams input rows into the ring. Shared memory: [kStages rows][25 x 32 weight pairs as packed fp32].
+template <int MODE, int ACT, bool WREG, bool PROBE>
+__global__ void __launch_bounds__(32 * (kMaxWarps + 1), 2) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ int abort_flag;
 
-  const int warps = blockDim.x >> 5;
+  const int warps = (blockDim.x >> 5) - 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_cols = warps * kCols;
   const uint32_t row_bytes = (tile_cols + 4) * kChannels * 2;
@@ -136,6 +142,12 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_c
   const int x_base = tx * tile_cols, y_base = ty * p.tile_rows, c_base = ct * kChannels;
   const int rows_out = min(p.tile_rows, p.height - y_base);
   const int rows_in = rows_out + 4;
+  const bool loads = !(PROBE && (p.debug & 4));
+
+  const uint32_t smem0 = smem_u32(smem_raw), full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+  const uint32_t wsm = smem0 + kStages * row_bytes;
+  const int c = c_base + 2 * lane;
+  const bool lane_active = c < p.channels;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -147,96 +159,120 @@ __global__ void __launch_bounds__(32 * kMaxWarps, 2) dw5x5_kernel(const __grid_c
     fence_async_proxy();
     tma_prefetch_desc(&in_map);
   }
-  __syncthreads();
-
-  const uint32_t smem0 = smem_u32(smem_raw), full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-  auto issue_row = [&](int r) {  // input row r of this tile -> stage r % kStages
-    const int s = r % kStages;
-    mbar_expect_tx_addr(full0 + 8 * s, row_bytes);
-    tma_load_4d_addr(smem0 + s * row_bytes, &in_map, full0 + 8 * s, c_base, x_base - 2, y_base - 2 + r, b);
-  };
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < min(kStages - 1, rows_in); ++r) issue_row(r);
-  }
-
-  const int c = c_base + 2 * lane;
-  const bool lane_active = c < p.channels;
-  uint64_t w[25];
-#pragma unroll
-  for (int k = 0; k < 25; ++k) {
-    w[k] = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
-  }
-  const uint64_t bias2 = lane_active ? pack2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : pack2(0.f, 0.f);
-  const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
-
-  uint64_t acc[5][kCols];
-#pragma unroll
-  for (int s = 0; s < 5; ++s)
-#pragma unroll
-    for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // two +0.0f
-
-  const int x0 = x_base + warp * kCols;
-  const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
-  bool alive = true;
-  for (int r0 = 0; r0 < rows_in && alive; r0 += 5) {
-#pragma unroll
-    for (int ph = 0; ph < 5; ++ph) {
-      const int r = r0 + ph;
-      if (r >= rows_in) break;
-      // refill the stage that every warp released one row ago with the row kStages - 1 ahead
-      if (threadIdx.x == 0 && r + kStages - 1 < rows_in) {
-        if (r >= 1) {
-          const int back = r - 1;
-          alive = mbar_wait_addr(empty0 + 8 * (back % kStages), (back / kStages) & 1, &abort_flag, p.status, kStatusWaitRows);
-        }
-        if (alive) issue_row(r + kStages - 1);
-      }
-      if (warp == 0) alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;  // warp 0 learns of its lane 0 giving up
-      if (!alive) break;
-      const int s = r % kStages;
-      if (!mbar_wait_addr(full0 + 8 * s, (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) {
-        alive = false;
-        break;
-      }
-      uint64_t in[kCols + 4];
-#pragma unroll
-      for (int j = 0; j < kCols + 4; ++j) {
-        uint32_t word;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(word) : "r"(lane_smem + s * row_bytes + j * (kChannels * 2)));
-        in[j] = bf16x2_to_f32x2(word);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive_addr(empty0 + 8 * s);
-      // 100 packed FMAs in one basic block: tap column outermost, so consecutive instructions belong to 20 different
-      // accumulators and nothing waits on the FMA latency. Rows above / below the tile accumulate too (into sums that
-      // are dropped): a branch per tap row would split the block.
-#pragma unroll
-      for (int kx = 0; kx < 5; ++kx) {
-#pragma unroll
-        for (int ky = 0; ky < 5; ++ky) {
-          const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
-#pragma unroll
-          for (int j = 0; j < kCols; ++j) acc[slot][j] = fma2(in[j + kx], w[ky * 5 + kx], acc[slot][j]);
-        }
-      }
-      // output row r - 4 has now received all five input rows
-      const int done = (ph + 1) % 5;
-      const int oy = r - 4;
-      if (oy >= 0) {
-        emit_row<MODE>(p, acc[done][0], acc[done][1], acc[done][2], acc[done][3], bias2, b, y_base + oy, x0, c, lane_active,
-                       int8_scale);
-      }
-#pragma unroll
-      for (int j = 0; j < kCols; ++j) acc[done][j] = 0ull;
+  if (warp == 0 && !WREG) {
+    // the 25 weight pairs of this lane's channels, widened to fp32 once per CTA
+    for (int k = 0; k < 25; ++k) {
+      const uint64_t w2 = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
+      asm volatile("st.shared.b64 [%0], %1;" ::"r"(wsm + (k * 32 + lane) * 8), "l"(w2) : "memory");
     }
   }
-  if (!alive) {
-    // Give copies that are still in flight time to land before the shared memory is released.
+  __syncthreads();
+
+  if (warp == warps) {
+    // ===== producer: one input row per stage, kStages rows ahead of the consumers =====
+    if (lane == 0 && loads) {
+      for (int r = 0; r < rows_in; ++r) {
+        const int s = r % kStages;
+        if (r >= kStages && !mbar_wait_addr(empty0 + 8 * s, ((r / kStages) - 1) & 1, &abort_flag, p.status, kStatusWaitRows)) break;
+        mbar_expect_tx_addr(full0 + 8 * s, row_bytes);
+        tma_load_4d_addr(smem0 + s * row_bytes, &in_map, full0 + 8 * s, c_base, x_base - 2, y_base - 2 + r, b);
+      }
+    }
+  } else {
+    // ===== consumers =====
+    const uint64_t bias2 = lane_active ? pack2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : pack2(0.f, 0.f);
+    const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
+    const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
+    const uint32_t lane_w = wsm + lane * 8;
+    const int x0 = x_base + warp * kCols;
+    const size_t image_pixel = static_cast<size_t>(b) * p.height * p.width;
+
+    uint64_t wreg[WREG ? 25 : 1];
+    if (WREG) {
+#pragma unroll
+      for (int k = 0; k < 25; ++k) {
+        wreg[k] = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
+      }
+    }
+    uint64_t acc[5][kCols];
+#pragma unroll
+    for (int s = 0; s < 5; ++s)
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // two +0.0f
+    uint64_t fin[kCols];   // the row completed by the previous input row, emitted beside this row's FMAs
+    int fin_y = -1;
+    uint32_t raw[kCols + 4];  // bf16x2 words of the next input row
+
+    auto fetch = [&](int r) -> bool {  // wait for input row r and read this lane's words of it
+      const int s = r % kStages;
+      if (loads && !mbar_wait_addr(full0 + 8 * s, (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) return false;
+#pragma unroll
+      for (int j = 0; j < kCols + 4; ++j) {
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw[j]) : "r"(lane_smem + s * row_bytes + j * (kChannels * 2)));
+      }
+      return true;
+    };
+
+    bool alive = fetch(0);
+    for (int r0 = 0; r0 < rows_in && alive; r0 += 5) {
+#pragma unroll
+      for (int ph = 0; ph < 5; ++ph) {
+        const int r = r0 + ph;
+        if (r >= rows_in) break;
+        uint64_t in[kCols + 4];
+#pragma unroll
+        for (int j = 0; j < kCols + 4; ++j) in[j] = bf16x2_to_f32x2(raw[j]);
+        // the words of row r are in registers: release its stage, then start on row r + 1
+        __syncwarp();
+        if (lane == 0 && loads) mbar_arrive_addr(empty0 + 8 * (r % kStages));
+        if (r + 1 < rows_in && !fetch(r + 1)) {
+          alive = false;
+          break;
+        }
+        if (fin_y >= 0 && !(PROBE && (p.debug & 2))) {
+          emit_row<MODE, ACT>(p, fin, bias2, image_pixel + static_cast<size_t>(fin_y) * p.width, x0, c, lane_active, int8_scale);
+        }
+        if (!(PROBE && (p.debug & 1))) {
+          // 100 packed FMAs in one basic block: tap column outermost, so consecutive instructions belong to 20 different
+          // accumulators and nothing waits on the FMA latency. Rows above / below the tile accumulate too (into sums that
+          // are dropped): a branch per tap row would split the block. Weights come from shared memory per use.
+#pragma unroll
+          for (int kx = 0; kx < 5; ++kx) {
+#pragma unroll
+            for (int ky = 0; ky < 5; ++ky) {
+              const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
+              const uint64_t w2 = WREG ? wreg[ky * 5 + kx] : lds64(lane_w + (ky * 5 + kx) * 256);
+#pragma unroll
+              for (int j = 0; j < kCols; ++j) acc[slot][j] = fma2(in[j + kx], w2, acc[slot][j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) acc[ph][j] = in[j] ^ in[j + 4];  // keep the loads alive
+        }
+        // output row r - 4 has now received all five input rows
+        const int done = (ph + 1) % 5;
+        fin_y = r - 4 >= 0 ? y_base + r - 4 : -1;
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) {
+          fin[j] = acc[done][j];
+          acc[done][j] = 0ull;
+        }
+      }
+    }
+    if (alive && fin_y >= 0 && !(PROBE && (p.debug & 2))) {
+      emit_row<MODE, ACT>(p, fin, bias2, image_pixel + static_cast<size_t>(fin_y) * p.width, x0, c, lane_active, int8_scale);
+    }
+  }
+  if (abort_flag) {
+    // a wait ran out: give copies that are still in flight time to land before the shared memory is released
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
 }
+
+int g_dw_debug = 0;
 
 int pick_warps(int width) {
   // fewest idle columns in the last tile of a row; on ties the narrower CTA (more CTAs per SM, better latency hiding)
@@ -289,7 +325,7 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   p.channel_tiles = ceil_div(channels, kChannels);
   p.tile_rows = pick_tile_rows(height, static_cast<long long>(p.tiles_x) * p.channel_tiles * batch);
   p.tiles_y = ceil_div(height, p.tile_rows);
-  p.act = act, p.swizzled = swizzled, p.status = status;
+  p.act = act, p.swizzled = swizzled, p.status = status, p.debug = g_dw_debug;
   const long long ctas = static_cast<long long>(p.tiles_x) * p.tiles_y * p.channel_tiles * batch;
   if (ctas > 0x7fffffffLL) return kUnsupported;
 
@@ -302,8 +338,19 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != kOk) return rc;
 
-  const size_t smem = static_cast<size_t>(kStages) * (tile_cols + 4) * kChannels * 2;
-  dw5x5_kernel<MODE><<<static_cast<unsigned>(ctas), warps * 32, smem, static_cast<cudaStream_t>(stream)>>>(map, p);
+  const size_t smem = static_cast<size_t>(kStages) * (tile_cols + 4) * kChannels * 2 + 25 * 32 * 8;
+  const unsigned grid = static_cast<unsigned>(ctas), block = (warps + 1) * 32;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g_dw_debug != 0) {  // measurement hooks: a separate instantiation, so the production kernel carries no flag tests
+    if (act == kActGelu) dw5x5_kernel<MODE, kActGelu, true, true><<<grid, block, smem, s>>>(map, p);
+    else dw5x5_kernel<MODE, kActRelu, true, true><<<grid, block, smem, s>>>(map, p);
+  } else if (act == kActGelu) {
+    dw5x5_kernel<MODE, kActGelu, true, false><<<grid, block, smem, s>>>(map, p);
+  } else if (act == kActRelu) {
+    dw5x5_kernel<MODE, kActRelu, true, false><<<grid, block, smem, s>>>(map, p);
+  } else {
+    dw5x5_kernel<MODE, kActNone, true, false><<<grid, block, smem, s>>>(map, p);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -328,5 +375,7 @@ extern "C" int fim_dw5x5_relu_int8(const void* value, const void* weight, const 
   if (scale == nullptr && batch > 0 && height > 0 && width > 0) return kBadArgument;
   return launch<kOutInt8>(value, weight, bias, out, nullptr, scale, 0, batch, height, width, channels, kActRelu, status, stream);
 }
+
+extern "C" void fim_dw_tune(int debug_flags) { g_dw_debug = debug_flags; }
 
 extern "C" int fim_abi_version(void) { return FIM_ABI_VERSION; }

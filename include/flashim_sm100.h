@@ -95,6 +95,10 @@ int fim_dw5x5_mxfp8(const void* value, const void* weight, const float* bias, vo
 int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias, const float* scale, void* out, int batch,
                         int height, int width, int channels, int* status, void* stream);
 
+/* Measurement hook for the following depthwise launches of this process (0 = off); results are invalid when set:
+ * 1: skip the FMAs, 2: skip the epilogue, 4: skip the loads and the waits for them. */
+void fim_dw_tune(int debug_flags);
+
 /* ---- implicit-GEMM conv2d on tcgen05 tensor cores ----------------------------------------------------------- */
 
 typedef struct FimConvGeometry {
