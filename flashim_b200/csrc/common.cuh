@@ -350,6 +350,24 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 // bf16x2 word -> its two values as a packed fp32 pair (low half first)
 __device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t w) { return pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u)); }
 
+// ---- bf16x2 words (two bf16 values in one register; one instruction for both) ---------------------------------------
+__device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// magnitude max(|a|, |b|) per half; the sign bit of each half is the xor of the operands' signs (mask it off)
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // GELU through the complementary error function in the rational-exponential form of Abramowitz & Stegun 7.1.26
 // (|error of erf| <= 1.5e-7): gelu(x) = x/2 * (2 - c) for x >= 0 and x/2 * c for x < 0 with c = erfc(|x|/sqrt 2).
 // No branch, two MUFU operations. For every bf16 input with |x| < 3 the bf16-rounded result equals that of the erf form

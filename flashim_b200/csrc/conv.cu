@@ -21,7 +21,7 @@
 namespace fim {
 namespace {
 
-constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+constexpr int kThreads = 576;  // producer warp, MMA warp, 16 epilogue warps
 constexpr int kTileM = 128;
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kMaxStages = 8;
@@ -32,7 +32,7 @@ struct ConvParams {
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
   int k_chunks, stages;
-  int panels_per_half;  // output panels each half of the epilogue rotates through (2 or 4)
+  int panels_per_half;  // output panels each column group of the epilogue rotates through (1 or 2)
   // scales (MXFP8)
   const int8_t* act_exponent;     // static: [cin / 32]
   const uint8_t* act_scales;      // per pixel: swizzled tiles over rows = pixels
@@ -65,7 +65,7 @@ struct SharedControl {
 
 constexpr int kMaxStaticScaleTiles = 16;  // input channels / 128 whose activation scales stay resident in tensor memory
 __host__ __device__ constexpr int acc_stages(int bn) {
-  return 2 * bn + 4 * kMaxStaticScaleTiles + 2 * (bn < 128 ? 4 : bn / 32) <= 512 ? 2 : 1;
+  return 2 * bn + 4 * kMaxStaticScaleTiles + kMaxStages * (bn < 128 ? 4 : bn / 32) <= 512 ? 2 : 1;
 }
 __host__ __device__ constexpr int scale_tiles_b(int bn) { return bn <= 128 ? 1 : bn / 128; }
 
@@ -80,62 +80,88 @@ __device__ __forceinline__ uint32_t idesc_i8(int block_n) {
 }
 
 // ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
-// Fills `w` with the output bytes of the chunk (32 * out_elem bytes, little end first).
+// Fills `w` with the output bytes of the chunk (32 * out_elem bytes, little end first). The block-scaled path works on
+// packed pairs throughout: fp32 pairs (one issue slot for two channels) up to the bf16 rounding, bf16x2 words after it
+// (residual add, ReLU and the block maximum are single bf16x2 instructions; a bf16 add of two bf16 values rounds once,
+// like the reference's fp32 add followed by a bf16 rounding, because the fp32 sum of two 8-bit significands is exact
+// whenever it can matter). `bias_at` is the shared-memory address of this chunk's 32 fp32 bias values.
+__device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_t& b0, uint64_t& b1) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(bias_at + i * 16));
+}
+
+// bf16x2 words r[16] -> E4M3 codes of value * 2**-e, four per output word
+__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[32]) {
+  const float inv = exp2_int(-e);
+  const uint64_t inv2 = pack2(inv, inv);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float a, b, c, d;
+    unpack2(mul2(bf16x2_to_f32x2(r[2 * i]), inv2), a, b);
+    unpack2(mul2(bf16x2_to_f32x2(r[2 * i + 1]), inv2), c, d);
+    w[i] = e4m3x4(a, b, c, d);
+  }
+}
+
 template <bool INT8>
-__device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, size_t pixel, int b, int y,
-                                             int x, bool valid, float a_scale, uint32_t (&w)[32]) {
+__device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, size_t pixel,
+                                             int b, int y, int x, bool valid, float a_scale, uint32_t (&w)[32]) {
   if (INT8 && p.out_mode == FIM_OUT_INT32) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = raw[i];
     return;
   }
-  float v[32];
+  // ---- fp32 value + bias, as packed pairs ----
+  uint64_t v2[16];
   if (INT8) {
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       const float4 s = __ldg(reinterpret_cast<const float4*>(p.w_scale + n + i));
-      v[i] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i])), __fmul_rn(a_scale, s.x));
-      v[i + 1] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 1])), __fmul_rn(a_scale, s.y));
-      v[i + 2] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 2])), __fmul_rn(a_scale, s.z));
-      v[i + 3] = __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 3])), __fmul_rn(a_scale, s.w));
+      v2[i / 2] = pack2(__fmul_rn(__int2float_rn(static_cast<int>(raw[i])), __fmul_rn(a_scale, s.x)),
+                        __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 1])), __fmul_rn(a_scale, s.y)));
+      v2[i / 2 + 1] = pack2(__fmul_rn(__int2float_rn(static_cast<int>(raw[i + 2])), __fmul_rn(a_scale, s.z)),
+                            __fmul_rn(__int2float_rn(static_cast<int>(raw[i + 3])), __fmul_rn(a_scale, s.w)));
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+    for (int i = 0; i < 16; ++i) v2[i] = pack2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
   }
   if (p.bias != nullptr) {
-    const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 q = __ldg(bp + i);
-      const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[8 * i + 2 * j] = __fadd_rn(v[8 * i + 2 * j], bf16_lo(ws[j]));
-        v[8 * i + 2 * j + 1] = __fadd_rn(v[8 * i + 2 * j + 1], bf16_hi(ws[j]));
-      }
+    for (int i = 0; i < 8; ++i) {
+      uint64_t b0, b1;
+      load_bias_pairs(bias_at, i, b0, b1);
+      v2[2 * i] = add2(v2[2 * i], b0);
+      v2[2 * i + 1] = add2(v2[2 * i + 1], b1);
     }
   }
   if (!INT8 && p.out_mode == FIM_OUT_F32) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(v[i]);
+    for (int i = 0; i < 16; ++i) {
+      float lo, hi;
+      unpack2(v2[i], lo, hi);
+      w[2 * i] = __float_as_uint(lo), w[2 * i + 1] = __float_as_uint(hi);
+    }
     return;
   }
+  // ---- one bf16 rounding; activation on the rounded value (ReLU waits for the residual when there is one) ----
   const bool has_res = p.residual != nullptr;
-  // one bf16 rounding, activation on the rounded value (ReLU waits for the residual when there is one)
+  uint32_t r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float lo, hi;
+    unpack2(v2[i], lo, hi);
+    r[i] = pack_bf16(lo, hi);
+  }
   if (p.act == kActGelu) {
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float g0, g1;
-      unpack2(gelu_fast2(pack2(bf16_round(v[i]), bf16_round(v[i + 1]))), g0, g1);
-      v[i] = bf16_round(g0), v[i + 1] = bf16_round(g1);
+    for (int i = 0; i < 16; ++i) {
+      float lo, hi;
+      unpack2(gelu_fast2(bf16x2_to_f32x2(r[i])), lo, hi);
+      r[i] = pack_bf16(lo, hi);
     }
   } else if (p.act == kActRelu && !has_res) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = fmaxf(bf16_round(v[i]), 0.0f);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]);
+    for (int i = 0; i < 16; ++i) r[i] = bf16x2_max(r[i], 0u);
   }
   if (has_res) {
     const int limit = p.res_channels - n;  // channels of this chunk present in the residual
@@ -147,36 +173,39 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint4 q = __ldg(r4 + i);
-          const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            v[8 * i + 2 * j] += bf16_lo(ws[j]);
-            v[8 * i + 2 * j + 1] += bf16_hi(ws[j]);
-          }
+          r[4 * i] = bf16x2_add(r[4 * i], q.x);
+          r[4 * i + 1] = bf16x2_add(r[4 * i + 1], q.y);
+          r[4 * i + 2] = bf16x2_add(r[4 * i + 2], q.z);
+          r[4 * i + 3] = bf16x2_add(r[4 * i + 3], q.w);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i < limit) v[i] += __bfloat162float(rp[(n + i) * p.res_stride[3]]);
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t lo = 2 * i < limit ? __bfloat16_as_ushort(rp[(n + 2 * i) * p.res_stride[3]]) : 0u;
+          const uint32_t hi = 2 * i + 1 < limit ? __bfloat16_as_ushort(rp[(n + 2 * i + 1) * p.res_stride[3]]) : 0u;
+          r[i] = bf16x2_add(r[i], lo | (hi << 16));
         }
       }
     }
+    if (p.act == kActRelu) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = bf16_round(p.act == kActRelu ? fmaxf(v[i], 0.0f) : v[i]);
+      for (int i = 0; i < 16; ++i) r[i] = bf16x2_max(r[i], 0u);
+    }
   }
   if (p.out_mode == FIM_OUT_BF16) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+    for (int i = 0; i < 16; ++i) w[i] = r[i];
     return;
   }
   if (INT8) {  // FIM_OUT_INT8
     const float scale = __ldg(p.out_scale);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      uint32_t q = 0;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) q |= (static_cast<uint32_t>(int8_code(v[4 * i + k], scale)) & 0xFFu) << (8 * k);
-      w[i] = q;
+      const uint32_t q0 = static_cast<uint32_t>(int8_code(bf16_lo(r[2 * i]), scale)) & 0xFFu;
+      const uint32_t q1 = static_cast<uint32_t>(int8_code(bf16_hi(r[2 * i]), scale)) & 0xFFu;
+      const uint32_t q2 = static_cast<uint32_t>(int8_code(bf16_lo(r[2 * i + 1]), scale)) & 0xFFu;
+      const uint32_t q3 = static_cast<uint32_t>(int8_code(bf16_hi(r[2 * i + 1]), scale)) & 0xFFu;
+      w[i] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
     }
     return;
   }
@@ -184,18 +213,22 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
   if (p.out_mode == FIM_OUT_E4M3_STATIC) {
     e = static_cast<int>(__ldg(p.out_exponent + (n >> 5)));
   } else {
-    float amax = 0.0f;
+    // block maximum of |value| on bf16x2 words: max.xorsign.abs keeps the larger magnitude in both halves (signs are
+    // masked off at the end); a bf16 magnitude shifted left by 16 is the same number in fp32
+    uint32_t m[8];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    e = e8m0_exponent(amax);
+    for (int i = 0; i < 8; ++i) m[i] = bf16x2_absmax(r[2 * i], r[2 * i + 1]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[i] = bf16x2_absmax(m[2 * i], m[2 * i + 1]);
+    m[0] = bf16x2_absmax(bf16x2_absmax(m[0], m[1]), bf16x2_absmax(m[2], m[3]));
+    const uint32_t top = max(m[0] & 0x7FFFu, (m[0] >> 16) & 0x7FFFu);
+    e = e8m0_exponent(__uint_as_float(top << 16));
     if (valid) {
       const int groups = p.cout >> 5;
       p.out_scales[swizzled_scale_offset(pixel, n >> 5, (groups + 3) >> 2)] = static_cast<uint8_t>(e + 127);
     }
   }
-  const float inv = exp2_int(-e);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) w[i] = e4m3x4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+  scale_to_e4m3(r, e, w);
 }
 
 // Write this row's 32 * elem bytes of a panel into swizzled shared memory (the layout a TMA store with swizzle mode
@@ -224,24 +257,26 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   constexpr int kKSteps = BK / 32;
   constexpr uint32_t kABytes = kTileM * BK, kBBytes = BN * BK;
   constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
-  constexpr uint32_t kSfbColumn = kAccStages * BN;                // two sets of kSfbColumns
-  constexpr uint32_t kSfaColumn = kSfbColumn + 2 * kSfbColumns;   // static scales: 4 columns per 128 input channels, copied
-                                                                  // once; per-pixel scales: two sets of 4 columns
-  constexpr int kChunksPerWarp = BN / 64;                // 32-column chunks each epilogue warp owns
+  constexpr uint32_t kSfbColumn = kAccStages * BN;                        // one set of kSfbColumns per stage
+  constexpr uint32_t kSfaColumn = kSfbColumn + kMaxStages * kSfbColumns;  // static scales: 4 columns per 128 input channels,
+                                                                          // copied once; per-pixel scales: 4 columns per stage
+  constexpr int kEpiGroups = BN >= 128 ? 4 : 2;          // column groups of the epilogue, four warps (one per lane quarter) each
+  constexpr int kChunksPerWarp = BN / (32 * kEpiGroups); // 32-column chunks each epilogue warp owns
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) SharedControl ctl;
 
   // dynamic shared memory, 1024-byte aligned:
-  // [stages x A][stages x B][4 or 8 output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles]
+  // [stages x A][stages x B][output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles][bias]
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t panel_bytes = 4096u * p.out_elem;
   const uint32_t smem_a = base;
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + p.stages * kBBytes;
-  const uint32_t smem_sfb = smem_out + 2 * p.panels_per_half * panel_bytes;
+  const uint32_t smem_sfb = smem_out + 4 * p.panels_per_half * panel_bytes;
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
+  const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dynamic_a = !INT8 && p.act_scales != nullptr;
@@ -255,7 +290,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl.tmem_full[s], 1);
-      mbar_init(&ctl.tmem_empty[s], 8);
+      mbar_init(&ctl.tmem_empty[s], 4 * kEpiGroups);
     }
     mbar_fence_init();
     tma_prefetch_desc(&act_map);
@@ -280,6 +315,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem_sfa_static + t * 512 + lane * 16), "r"(word) : "memory");
     }
     fence_async_proxy();
+  }
+  if (p.bias != nullptr) {
+    // the bias widened to fp32 once per CTA (zero for the columns a ragged last tile pads)
+    for (int i = threadIdx.x; i < p.tiles_n * BN; i += kThreads) {
+      const float value = i < p.cout ? __bfloat162float(p.bias[i]) : 0.0f;
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias + i * 4), "f"(value) : "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -357,7 +399,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int tiles = (p.cin + 127) / 128;
         for (int t = 0; t < tiles; ++t) tc_copy_scales(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
       }
-      uint32_t s = 0, phase = 0, set = 0, tile_it = 0;
+      uint32_t s = 0, phase = 0, tile_it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x, ++tile_it) {
         const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
@@ -376,8 +418,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           uint32_t a_id = 0;
           const uint32_t kb_a = j * kKSteps;  // 32-channel block index of the activation chunk
           if (BK != 128) a_id = kb_a & 3;
-          const uint32_t sfb_tmem = tmem + kSfbColumn + kSfbColumns * set;
-          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * (dynamic_a ? set : (kb_a >> 2));
+          // scale tiles of this stage: shared memory -> the stage's own tensor-memory columns, in front of its MMAs (the
+          // tensor pipe runs both in issue order; a column set is rewritten only after the MMAs that read it, a whole
+          // ring of stages earlier)
+          const uint32_t sfb_tmem = tmem + kSfbColumn + kSfbColumns * s;
+          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * (dynamic_a ? s : (kb_a >> 2));
           if (copy_scales) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
@@ -399,7 +444,6 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           }
           tc_commit(&ctl.empty[s]);  // the stage is free once these MMAs have read it
           if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
-          set ^= 1;
           if (++j == p.k_chunks) j = 0;
           if (BK != 128) b_id = (b_id + kKSteps) & 3;
         }
@@ -407,17 +451,19 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       }
     }
   } else {
-    // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one half of the BN columns =====
+    // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one column group of the tile =====
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its half
-    const uint32_t bar_id = 1 + half;
+    const int group = (warp - 2) >> 2;
+    if (group < kEpiGroups) {
+    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its group
+    const uint32_t bar_id = 1 + group;
     const int row = quarter * 32 + lane;
     const int ry = row / p.tile_w, rx = row - ry * p.tile_w;
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
-    const uint32_t panels = smem_out + half * p.panels_per_half * panel_bytes;
+    const uint32_t panels = smem_out + group * p.panels_per_half * panel_bytes;
     const bool store = !(p.debug & 4);
+    constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_it) {
       const int nt = tile % p.tiles_n;
@@ -433,11 +479,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
       if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
       tc_fence_after();
-      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * (BN / 2);
+      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
       // Drain two 32-column chunks at a time into registers (ten warps share a register file quarter three deep, which
       // caps a thread at 168 registers) and hand the accumulator back as soon as the last chunk is read, before its
       // arithmetic.
-      constexpr int kGroup = kChunksPerWarp < 2 ? 1 : 2;
+      constexpr int kGroup = 1;
 #pragma unroll
       for (int g = 0; g < kChunksPerWarp; g += kGroup) {
         uint32_t raw[kGroup][32];
@@ -451,17 +497,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
 #pragma unroll
         for (int i = 0; i < kGroup; ++i) {
-          const int n = n0 + half * (BN / 2) + (g + i) * 32;
-          if (n >= p.cout) continue;  // uniform over the four warps of this half
+          const int n = n0 + group * kGroupColumns + (g + i) * 32;
+          if (n >= p.cout) continue;  // uniform over the four warps of this group
           uint32_t w[32];
-          finish_chunk<INT8>(p, raw[i], n, pixel, b, y, x, valid, a_scale, w);
+          finish_chunk<INT8>(p, raw[i], n, smem_bias + static_cast<uint32_t>(n) * 4u, pixel, b, y, x, valid, a_scale, w);
           const uint32_t panel = panels + (chunk_it & (p.panels_per_half - 1)) * panel_bytes;
           ++chunk_it;
           if (leader) {  // the store that last read this panel has finished with it
-            if (p.panels_per_half == 4) {
-              bulk_wait_read<3>();
-            } else {
+            if (p.panels_per_half == 2) {
               bulk_wait_read<1>();
+            } else {
+              bulk_wait_read<0>();
             }
           }
           named_barrier(bar_id, 128);
@@ -476,6 +522,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       }
     }
     if (leader) bulk_wait_read<0>();
+    }
   }
 
   if (ctl.abort_flag) {
@@ -564,9 +611,12 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   // shared memory: alignment slack + output panels + static activation-scale tiles + the stage ring. A layer with few
   // K iterations per tile is bound by its stores: it gets more panels in flight; a long main loop gets the stages.
   const int k_iters = g.kh * g.kw * (g.cin / pl.block_k);
-  pl.panels_per_half = (k_iters <= 4 && out_elem <= 2) ? 4 : 2;
+  pl.panels_per_half = out_elem == 4 ? 1 : 2;  // 16 KB panels of a 4-byte output: one per column group
+  (void)k_iters;
   const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_tiles_b(bn) * 512 + 512;
-  const int fixed = 1024 + 2 * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512;
+  const int bias_bytes = pl.tiles_n * bn * 4;
+  if (bias_bytes > 32 * 1024) return kUnsupported;
+  const int fixed = 1024 + 4 * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;

@@ -2,22 +2,25 @@
 // static INT8. Arithmetic follows FlashIM's torch reference (flashim/ops/conv.py:30-61): bf16 inputs and weights,
 // fp32 FMA chain ordered (ky, kx) from zero, bias added last.
 //
-// Layout of the work. A CTA owns 64 channels x (4 * warps) columns x `tile_rows` rows of one image. Input rows
-// (with their 2-pixel halo, zero-filled outside the image by TMA) stream through a ring of single-row stages in
-// shared memory; a lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 weight pairs and five rows
-// of partial sums in registers as packed fp32 pairs (fma.rn.f32x2: both channels in one issue slot), and finishes one
-// output row per input row. The kernel is bound by the fp32 pipe (25 FMAs per element), not by HBM alone, so the issue
-// slots beside the FMAs are what is budgeted: one 32-bit shared-memory load per input word, packed bias / GELU math, one
-// redux per 32-channel MX block (16 adjacent lanes).
+// Layout of the work. A CTA owns 64 channels x (4 * warps) columns x `tile_rows` rows of one image. Input rows (with
+// their 2-pixel halo, zero-filled outside the image by TMA) arrive five at a time in a ring of shared-memory chunks; a
+// lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 weight pairs and five rows of partial sums in
+// registers as packed fp32 pairs (fma.rn.f32x2: both channels in one issue slot), and finishes one output row per input
+// row. The kernel is bound by the fp32 pipe (25 FMAs per element = 100 packed FMAs per lane and row), so everything
+// beside the FMAs is budgeted in issue slots: the five rows of a chunk are one straight-line block (accumulator slots,
+// shared-memory offsets and weights are all compile-time), barriers are touched once per chunk, a fresh accumulator
+// starts with a multiply instead of being zeroed, and the MX block maximum over 16 lanes is a transposing butterfly
+// whose owner lanes compute exponent and scale once per pixel.
 #include "common.cuh"
 #include "flashim_sm100.h"
 
 namespace fim {
 namespace {
 
-constexpr int kChannels = 64;  // per CTA: one 128-byte line per pixel
-constexpr int kCols = 4;       // output columns per lane
-constexpr int kStages = 8;     // single-row stages in the ring
+constexpr int kChannels = 64;    // per CTA: one 128-byte line per pixel
+constexpr int kCols = 4;         // output columns per lane
+constexpr int kChunkRows = 5;    // input rows per ring chunk = accumulator slots
+constexpr int kStages = 3;       // chunks in the ring
 constexpr int kMinWarps = 4, kMaxWarps = 5;  // compute warps per CTA (plus one producer warp)
 
 enum { kOutBf16 = 0, kOutMx = 1, kOutInt8 = 2 };
@@ -29,7 +32,7 @@ struct DwParams {
   uint8_t* scales;
   const float* scale;  // INT8
   int batch, height, width, channels;
-  int tile_rows, tiles_x, tiles_y, channel_tiles;
+  int tile_rows, tiles_x, tiles_y, channel_tiles, total_tiles;  // tile_rows + 4 is a multiple of kChunkRows
   int act, swizzled;
   int* status;
   int debug;  // timing experiments only: 1 = no FMAs, 2 = no epilogue, 4 = no loads and no waits for them
@@ -46,27 +49,35 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v) {
   return v;
 }
 
-// Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's four pixels. It is
-// inlined next to the FMA block of the following input row, with which it shares no data, so the two interleave.
+// Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's four pixels.
+// `out_row` points at this lane's channel pair of pixel (row, x0) in units of output pairs; `pixel0` is that pixel's
+// index in the batch; `cols_ok` has bit j set when column x0 + j exists (0 for a lane without channels).
 template <int MODE, int ACT>
-__device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, size_t row_pixel,
-                                         int x0, int c, bool lane_active, float int8_scale) {
-  float lo[kCols], hi[kCols];
+__device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, void* out_row,
+                                         size_t pixel0, int c, uint32_t cols_ok, float int8_scale) {
+  const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
+  uint64_t v[kCols];
 #pragma unroll
-  for (int j = 0; j < kCols; ++j) unpack2(activate2<ACT>(add2(acc[j], bias2)), lo[j], hi[j]);
+  for (int j = 0; j < kCols; ++j) v[j] = activate2<ACT>(add2(acc[j], bias2));
   if (MODE == kOutBf16) {
-    uint32_t* out = reinterpret_cast<uint32_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
+    uint32_t* out = static_cast<uint32_t*>(out_row);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
-      if (lane_active && x0 + j < p.width) out[static_cast<size_t>(j) * (p.channels >> 1)] = pack_bf16(lo[j], hi[j]);
+      float lo, hi;
+      unpack2(v[j], lo, hi);
+      if (cols_ok & (1u << j)) out[j * pair_stride] = pack_bf16(lo, hi);
     }
   } else if (MODE == kOutMx) {
     // amax of each pixel over the 16 lanes of its 32-channel block by a transposing butterfly: after the exchanges lane
-    // l holds the block maximum of one pixel (5 shuffles instead of 16), computes that pixel's exponent once, and the
-    // four exponents are read back with one shuffle each.
+    // l holds the block maximum of pixel ((l & 1) << 1) | ((l >> 1) & 1); lanes 0-3 of each half-warp are the owners
+    // of one pixel each: they compute its exponent, store the scale byte and hand 2**-e back with one shuffle per pixel.
     float m[kCols];
 #pragma unroll
-    for (int j = 0; j < kCols; ++j) m[j] = lane_active ? fmaxf(fabsf(lo[j]), fabsf(hi[j])) : 0.0f;
+    for (int j = 0; j < kCols; ++j) {
+      float lo, hi;
+      unpack2(v[j], lo, hi);
+      m[j] = fmaxf(fabsf(lo), fabsf(hi));
+    }
     const int lane = threadIdx.x & 31;
     {
       const bool odd = lane & 1;  // even lanes keep pixels 0, 1 and odd lanes pixels 2, 3
@@ -82,186 +93,215 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     }
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 4));
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 8));
-    // this lane now holds pixel ((lane & 1) << 1) | ((lane >> 1) & 1) of its half-warp
-    const int mine = e8m0_exponent(m[0]);
+    const int e = e8m0_exponent(m[0]);
+    const float inv_mine = exp2_int(-e);
+    const int mine = ((lane & 1) << 1) | ((lane >> 1) & 1);  // the pixel this lane holds
+    if ((lane & 12) == 0 && ((cols_ok >> mine) & 1u)) {
+      const size_t pixel = pixel0 + mine;
+      const int groups = p.channels >> 5;
+      const int g = c >> 5;
+      const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
+      p.scales[at] = static_cast<uint8_t>(e + 127);
+    }
     const int half = lane & 16;
-    const int groups = p.channels >> 5;
-    uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
+    uint16_t* out = static_cast<uint16_t*>(out_row);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
-      const int e = __shfl_sync(0xffffffffu, mine, half | ((j >> 1) & 1) | ((j & 1) << 1));
-      const float inv = exp2_int(-e);
-      if (lane_active && x0 + j < p.width) {
-        out[static_cast<size_t>(j) * (p.channels >> 1)] = e4m3x2(lo[j] * inv, hi[j] * inv);
-        if ((lane & 15) == 0) {
-          const size_t pixel = row_pixel + x0 + j;
-          const int g = c >> 5;
-          const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
-          p.scales[at] = static_cast<uint8_t>(e + 127);
-        }
-      }
+      const float inv = __shfl_sync(0xffffffffu, inv_mine, half | ((j >> 1) & 1) | ((j & 1) << 1));
+      float lo, hi;
+      unpack2(mul2(v[j], pack2(inv, inv)), lo, hi);
+      if (cols_ok & (1u << j)) out[j * pair_stride] = e4m3x2(lo, hi);
     }
   } else {
-    uint16_t* out = reinterpret_cast<uint16_t*>(p.out) + (((row_pixel + x0) * p.channels + c) >> 1);
+    uint16_t* out = static_cast<uint16_t*>(out_row);
 #pragma unroll
     for (int j = 0; j < kCols; ++j) {
-      const int qlo = int8_code(bf16_round(lo[j]), int8_scale), qhi = int8_code(bf16_round(hi[j]), int8_scale);
-      if (lane_active && x0 + j < p.width) {
-        out[static_cast<size_t>(j) * (p.channels >> 1)] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
-      }
+      float lo, hi;
+      unpack2(v[j], lo, hi);
+      const int qlo = int8_code(bf16_round(lo), int8_scale), qhi = int8_code(bf16_round(hi), int8_scale);
+      if (cols_ok & (1u << j)) out[j * pair_stride] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
     }
   }
 }
 
-__device__ __forceinline__ uint64_t lds64(uint32_t addr) {
-  uint64_t v;
-  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 
-// Thread layout: `warps` compute warps (warp w owns columns 4w .. 4w+3 of the tile) and one producer warp whose lane 0
-// streams input rows into the ring. Shared memory: [kStages rows][25 x 32 weight pairs as packed fp32].
-template <int MODE, int ACT, bool WREG, bool PROBE>
-__global__ void __launch_bounds__(32 * (kMaxWarps + 1), 2) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
+// Thread layout: WARPS compute warps (warp w owns columns 4w .. 4w+3 of the tile) and one producer warp whose lane 0
+// streams chunks of five input rows into the ring.
+template <int MODE, int ACT, int WARPS, bool PROBE>
+__global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
+  constexpr int kTileCols = WARPS * kCols;
+  constexpr uint32_t kRowBytes = (kTileCols + 4) * kChannels * 2;
+  constexpr uint32_t kChunkBytes = kChunkRows * kRowBytes;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ int abort_flag;
 
-  const int warps = (blockDim.x >> 5) - 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_cols = warps * kCols;
-  const uint32_t row_bytes = (tile_cols + 4) * kChannels * 2;
 
-  // tile decode: x fastest, then y, channel tile, batch
-  int t = blockIdx.x;
-  const int tx = t % p.tiles_x; t /= p.tiles_x;
-  const int ty = t % p.tiles_y; t /= p.tiles_y;
-  const int ct = t % p.channel_tiles;
-  const int b = t / p.channel_tiles;
-  const int x_base = tx * tile_cols, y_base = ty * p.tile_rows, c_base = ct * kChannels;
-  const int rows_out = min(p.tile_rows, p.height - y_base);
-  const int rows_in = rows_out + 4;
+  // Persistent CTAs: this one owns the contiguous tile range [t_begin, t_end) (x fastest, then y, channel tile, batch),
+  // so the chunk ring keeps flowing from one tile into the next and neighbouring tiles (shared halo columns, same
+  // weights) follow each other on the same SM.
+  const int t_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * p.total_tiles / gridDim.x);
+  const int t_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.total_tiles / gridDim.x);
+  const int chunks = (p.tile_rows + 4) / kChunkRows;
+  const int total_chunks = (t_end - t_begin) * chunks;
   const bool loads = !(PROBE && (p.debug & 4));
 
   const uint32_t smem0 = smem_u32(smem_raw), full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-  const uint32_t wsm = smem0 + kStages * row_bytes;
-  const int c = c_base + 2 * lane;
-  const bool lane_active = c < p.channels;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], warps);
+      mbar_init(&empty_bar[s], WARPS);
     }
     mbar_fence_init();
     fence_async_proxy();
     tma_prefetch_desc(&in_map);
   }
-  if (warp == 0 && !WREG) {
-    // the 25 weight pairs of this lane's channels, widened to fp32 once per CTA
-    for (int k = 0; k < 25; ++k) {
-      const uint64_t w2 = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
-      asm volatile("st.shared.b64 [%0], %1;" ::"r"(wsm + (k * 32 + lane) * 8), "l"(w2) : "memory");
-    }
-  }
   __syncthreads();
 
-  if (warp == warps) {
-    // ===== producer: one input row per stage, kStages rows ahead of the consumers =====
+  if (warp == WARPS) {
+    // ===== producer: five input rows per chunk, kStages chunks ahead of the consumers =====
     if (lane == 0 && loads) {
-      for (int r = 0; r < rows_in; ++r) {
-        const int s = r % kStages;
-        if (r >= kStages && !mbar_wait_addr(empty0 + 8 * s, ((r / kStages) - 1) & 1, &abort_flag, p.status, kStatusWaitRows)) break;
-        mbar_expect_tx_addr(full0 + 8 * s, row_bytes);
-        tma_load_4d_addr(smem0 + s * row_bytes, &in_map, full0 + 8 * s, c_base, x_base - 2, y_base - 2 + r, b);
+      uint32_t s = 0, phase = 0;
+      int n = 0;
+      bool stop = false;
+      for (int tile = t_begin; tile < t_end && !stop; ++tile) {
+        int t = tile;
+        const int tx = t % p.tiles_x; t /= p.tiles_x;
+        const int ty = t % p.tiles_y; t /= p.tiles_y;
+        const int ct = t % p.channel_tiles;
+        const int b = t / p.channel_tiles;
+        for (int g = 0; g < chunks; ++g, ++n) {
+          if (n >= kStages && !mbar_wait_addr(empty0 + 8 * s, phase ^ 1, &abort_flag, p.status, kStatusWaitRows)) {
+            stop = true;
+            break;
+          }
+          mbar_expect_tx_addr(full0 + 8 * s, kChunkBytes);
+          tma_load_4d_addr(smem0 + s * kChunkBytes, &in_map, full0 + 8 * s, ct * kChannels, tx * kTileCols - 2,
+                           ty * p.tile_rows - 2 + g * kChunkRows, b);
+          if (++s == kStages) s = 0, phase ^= 1;
+        }
       }
     }
-  } else {
+  } else if (total_chunks > 0) {
     // ===== consumers =====
-    const uint64_t bias2 = lane_active ? pack2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : pack2(0.f, 0.f);
     const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
     const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
-    const uint32_t lane_w = wsm + lane * 8;
-    const int x0 = x_base + warp * kCols;
-    const size_t image_pixel = static_cast<size_t>(b) * p.height * p.width;
+    constexpr int kOutBytes = MODE == kOutBf16 ? 4 : 2;  // per channel pair
+    const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
+    const size_t row_pairs = static_cast<size_t>(p.width) * pair_stride;
 
-    uint64_t wreg[WREG ? 25 : 1];
-    if (WREG) {
+    // per-tile state, set when a tile's first chunk starts
+    uint64_t wreg[25];
+    uint64_t bias2 = 0ull;
+    int c = 0, last_ct = -1, y_base = 0, y_out = 0;
+    uint32_t cols_ok = 0;
+    size_t pixel0 = 0;
+    uint8_t* out_row = nullptr;
 #pragma unroll
-      for (int k = 0; k < 25; ++k) {
-        wreg[k] = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
-      }
+    for (int k = 0; k < 25; ++k) wreg[k] = 0ull;
+    uint64_t acc[kChunkRows][kCols];
+#pragma unroll
+    for (int s = 0; s < kChunkRows; ++s)
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // a slot is read for real only after its first multiply
+
+    uint32_t s = 0, phase = 0;
+    uint32_t raw[kCols + 4];  // bf16x2 words of the input row about to be used
+    bool ok = !loads || mbar_wait_addr(full0, 0, &abort_flag, p.status, kStatusWaitRows);
+    bool alive = __all_sync(0xffffffffu, ok);
+    if (alive) {
+#pragma unroll
+      for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + j * (kChannels * 2));
     }
-    uint64_t acc[5][kCols];
+    int tile = t_begin, g = 0;
+    for (int n = 0; n < total_chunks && alive; ++n) {
+      if (g == 0) {
+        int t = tile;
+        const int tx = t % p.tiles_x; t /= p.tiles_x;
+        const int ty = t % p.tiles_y; t /= p.tiles_y;
+        const int ct = t % p.channel_tiles;
+        const int b = t / p.channel_tiles;
+        c = ct * kChannels + 2 * lane;
+        const bool lane_active = c < p.channels;
+        if (ct != last_ct) {  // uniform: a new channel tile brings new weights and bias
+          last_ct = ct;
 #pragma unroll
-    for (int s = 0; s < 5; ++s)
+          for (int k = 0; k < 25; ++k) {
+            wreg[k] = bf16x2_to_f32x2(lane_active ? __ldg(p.weight + ((static_cast<size_t>(k) * p.channels + c) >> 1)) : 0u);
+          }
+          bias2 = lane_active ? pack2(__ldg(p.bias + c), __ldg(p.bias + c + 1)) : pack2(0.f, 0.f);
+        }
+        const int x0 = tx * kTileCols + warp * kCols;
+        cols_ok = 0;
 #pragma unroll
-      for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // two +0.0f
-    uint64_t fin[kCols];   // the row completed by the previous input row, emitted beside this row's FMAs
-    int fin_y = -1;
-    uint32_t raw[kCols + 4];  // bf16x2 words of the next input row
-
-    auto fetch = [&](int r) -> bool {  // wait for input row r and read this lane's words of it
-      const int s = r % kStages;
-      if (loads && !mbar_wait_addr(full0 + 8 * s, (r / kStages) & 1, &abort_flag, p.status, kStatusWaitRows)) return false;
-#pragma unroll
-      for (int j = 0; j < kCols + 4; ++j) {
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw[j]) : "r"(lane_smem + s * row_bytes + j * (kChannels * 2)));
+        for (int j = 0; j < kCols; ++j) cols_ok |= (lane_active && x0 + j < p.width) ? (1u << j) : 0u;
+        y_base = ty * p.tile_rows;
+        y_out = y_base - 4;  // where the tile's first input row would "finish": four rows above the tile
+        pixel0 = (static_cast<size_t>(b) * p.height + y_base) * p.width + x0;  // of output row y_base, advanced per emitted row
+        out_row = static_cast<uint8_t*>(p.out) + (pixel0 * pair_stride + (c >> 1)) * kOutBytes;
       }
-      return true;
-    };
-
-    bool alive = fetch(0);
-    for (int r0 = 0; r0 < rows_in && alive; r0 += 5) {
+      const uint32_t chunk = lane_smem + s * kChunkBytes;
+      const uint32_t s_next = s + 1 == kStages ? 0u : s + 1;
+      const uint32_t phase_next = s + 1 == kStages ? phase ^ 1u : phase;
 #pragma unroll
-      for (int ph = 0; ph < 5; ++ph) {
-        const int r = r0 + ph;
-        if (r >= rows_in) break;
+      for (int ph = 0; ph < kChunkRows; ++ph) {
         uint64_t in[kCols + 4];
 #pragma unroll
         for (int j = 0; j < kCols + 4; ++j) in[j] = bf16x2_to_f32x2(raw[j]);
-        // the words of row r are in registers: release its stage, then start on row r + 1
-        __syncwarp();
-        if (lane == 0 && loads) mbar_arrive_addr(empty0 + 8 * (r % kStages));
-        if (r + 1 < rows_in && !fetch(r + 1)) {
-          alive = false;
-          break;
-        }
-        if (fin_y >= 0 && !(PROBE && (p.debug & 2))) {
-          emit_row<MODE, ACT>(p, fin, bias2, image_pixel + static_cast<size_t>(fin_y) * p.width, x0, c, lane_active, int8_scale);
+        // fetch the next input row while this one is in the FMAs
+        if (ph + 1 < kChunkRows) {
+#pragma unroll
+          for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(chunk + (ph + 1) * kRowBytes + j * (kChannels * 2));
+        } else {
+          // every word of this chunk is in registers: hand it back, then take the first row of the next chunk (which
+          // may already belong to the next tile)
+          __syncwarp();
+          if (lane == 0 && loads) mbar_arrive_addr(empty0 + 8 * s);
+          if (n + 1 < total_chunks) {
+            ok = !loads || mbar_wait_addr(full0 + 8 * s_next, phase_next, &abort_flag, p.status, kStatusWaitRows);
+            alive = __all_sync(0xffffffffu, ok);
+#pragma unroll
+            for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + s_next * kChunkBytes + j * (kChannels * 2));
+          }
         }
         if (!(PROBE && (p.debug & 1))) {
-          // 100 packed FMAs in one basic block: tap column outermost, so consecutive instructions belong to 20 different
-          // accumulators and nothing waits on the FMA latency. Rows above / below the tile accumulate too (into sums that
-          // are dropped): a branch per tap row would split the block. Weights come from shared memory per use.
+          // 100 packed FMAs: input row r = 5 g + ph feeds tap row ky of the output row in slot (ph - ky) mod 5. Tap column
+          // outermost, so neighbouring instructions belong to 20 different accumulators and nothing waits on the FMA
+          // latency. Tap row 0 opens a new output row: its first term is a plain product (0 + a*b == a*b).
 #pragma unroll
           for (int kx = 0; kx < 5; ++kx) {
 #pragma unroll
             for (int ky = 0; ky < 5; ++ky) {
-              const int slot = (ph - ky + 5) % 5;  // output row r - ky of this tile
-              const uint64_t w2 = WREG ? wreg[ky * 5 + kx] : lds64(lane_w + (ky * 5 + kx) * 256);
+              const int slot = (ph - ky + 5) % 5;
 #pragma unroll
-              for (int j = 0; j < kCols; ++j) acc[slot][j] = fma2(in[j + kx], w2, acc[slot][j]);
+              for (int j = 0; j < kCols; ++j) {
+                acc[slot][j] = (ky == 0 && kx == 0) ? mul2(in[j], wreg[0]) : fma2(in[j + kx], wreg[ky * 5 + kx], acc[slot][j]);
+              }
             }
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < kCols; ++j) acc[ph][j] = in[j] ^ in[j + 4];  // keep the loads alive
+          for (int j = 0; j < kCols; ++j) acc[(ph + 1) % 5][j] = in[j] ^ in[j + 4];  // keep the loads alive
         }
-        // output row r - 4 has now received all five input rows
-        const int done = (ph + 1) % 5;
-        fin_y = r - 4 >= 0 ? y_base + r - 4 : -1;
-#pragma unroll
-        for (int j = 0; j < kCols; ++j) {
-          fin[j] = acc[done][j];
-          acc[done][j] = 0ull;
+        // the output row in slot (ph + 1) mod 5 has now received all five input rows
+        if (y_out >= y_base && y_out < p.height && !(PROBE && (p.debug & 2))) {
+          emit_row<MODE, ACT>(p, acc[(ph + 1) % 5], bias2, out_row, pixel0, c, cols_ok, int8_scale);
+          pixel0 += p.width;
+          out_row += row_pairs * kOutBytes;
         }
+        ++y_out;
       }
-    }
-    if (alive && fin_y >= 0 && !(PROBE && (p.debug & 2))) {
-      emit_row<MODE, ACT>(p, fin, bias2, image_pixel + static_cast<size_t>(fin_y) * p.width, x0, c, lane_active, int8_scale);
+      s = s_next, phase = phase_next;
+      if (++g == chunks) g = 0, ++tile;
     }
   }
   if (abort_flag) {
@@ -275,7 +315,7 @@ __global__ void __launch_bounds__(32 * (kMaxWarps + 1), 2) dw5x5_kernel(const __
 int g_dw_debug = 0;
 
 int pick_warps(int width) {
-  // fewest idle columns in the last tile of a row; on ties the narrower CTA (more CTAs per SM, better latency hiding)
+  // fewest idle columns in the last tile of a row; on ties the narrower CTA
   int best = kMinWarps;
   double best_eff = 0.0;
   for (int w = kMinWarps; w <= kMaxWarps; ++w) {
@@ -290,15 +330,55 @@ int pick_warps(int width) {
 }
 
 int pick_tile_rows(int height, long long tiles_per_row_band) {
-  // Rows per CTA: tall enough that the 4 halo rows (loaded, not computed on) cost little, short enough that the grid
-  // fills the 148 SMs several times over at 3-4 resident CTAs each.
-  const int candidates[] = {64, 50, 40, 32, 25, 20, 16, 10, 8};
-  for (int rows : candidates) {
-    if (rows > height && rows != 8) continue;
-    const long long ctas = tiles_per_row_band * ceil_div(height, rows);
-    if (ctas >= 148LL * 3 * 3) return rows;  // three waves of three resident CTAs per SM
+  // Rows per CTA (+ 4 halo rows = a whole number of chunks). A tile costs tile_rows + 4 rows of FMAs, so tall tiles waste
+  // less on the halo and on rows past the image's last; short tiles fill the 148 SMs (two CTAs each) more evenly. The
+  // cost below is FMA rows per row band, stretched by half of the idle fraction of the last wave.
+  int best = 6;
+  double best_cost = 1e30;
+  for (int rows = 6; rows <= 61; rows += kChunkRows) {
+    const long long tiles_y = ceil_div(height, rows);
+    const double waves = static_cast<double>(tiles_per_row_band * tiles_y) / (148.0 * 2.0);
+    const double whole = waves <= 1.0 ? 1.0 : static_cast<double>(static_cast<long long>(waves + 0.999999));
+    const double stretch = waves <= 1.0 ? 1.0 : 1.0 + 0.5 * (whole / waves - 1.0);
+    const double cost = static_cast<double>(tiles_y) * (rows + 4) * stretch;
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = rows;
+    }
   }
-  return height < 8 ? height : 8;
+  return best;
+}
+
+template <int MODE, int WARPS>
+cudaError_t launch_kernel(const CUtensorMap& map, const DwParams& p, int act, unsigned grid, cudaStream_t s) {
+  constexpr unsigned kBlock = (WARPS + 1) * 32;
+  constexpr size_t kSmem = static_cast<size_t>(kStages) * kChunkRows * (WARPS * kCols + 4) * kChannels * 2;
+  static bool configured = false;
+  if (!configured) {
+    // every instantiation gets the opt-in limit once (some chunk rings exceed the 48 KB default)
+    cudaError_t e = cudaSuccess;
+    auto set = [&](auto kernel) {
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
+    };
+    set(dw5x5_kernel<MODE, kActNone, WARPS, false>);
+    set(dw5x5_kernel<MODE, kActRelu, WARPS, false>);
+    set(dw5x5_kernel<MODE, kActGelu, WARPS, false>);
+    set(dw5x5_kernel<MODE, kActRelu, WARPS, true>);
+    set(dw5x5_kernel<MODE, kActGelu, WARPS, true>);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  if (g_dw_debug != 0) {  // measurement hooks: a separate instantiation, so the production kernel carries no flag tests
+    if (act == kActGelu) dw5x5_kernel<MODE, kActGelu, WARPS, true><<<grid, kBlock, kSmem, s>>>(map, p);
+    else dw5x5_kernel<MODE, kActRelu, WARPS, true><<<grid, kBlock, kSmem, s>>>(map, p);
+  } else if (act == kActGelu) {
+    dw5x5_kernel<MODE, kActGelu, WARPS, false><<<grid, kBlock, kSmem, s>>>(map, p);
+  } else if (act == kActRelu) {
+    dw5x5_kernel<MODE, kActRelu, WARPS, false><<<grid, kBlock, kSmem, s>>>(map, p);
+  } else {
+    dw5x5_kernel<MODE, kActNone, WARPS, false><<<grid, kBlock, kSmem, s>>>(map, p);
+  }
+  return cudaGetLastError();
 }
 
 template <int MODE>
@@ -328,30 +408,21 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   p.act = act, p.swizzled = swizzled, p.status = status, p.debug = g_dw_debug;
   const long long ctas = static_cast<long long>(p.tiles_x) * p.tiles_y * p.channel_tiles * batch;
   if (ctas > 0x7fffffffLL) return kUnsupported;
+  p.total_tiles = static_cast<int>(ctas);
 
   CUtensorMap map;
   const uint64_t dims[4] = {static_cast<uint64_t>(channels), static_cast<uint64_t>(width), static_cast<uint64_t>(height),
                             static_cast<uint64_t>(batch)};
   const uint64_t strides[3] = {static_cast<uint64_t>(channels) * 2, static_cast<uint64_t>(width) * channels * 2,
                                static_cast<uint64_t>(height) * width * channels * 2};
-  const uint32_t box[4] = {kChannels, static_cast<uint32_t>(tile_cols + 4), 1, 1};
+  const uint32_t box[4] = {kChannels, static_cast<uint32_t>(tile_cols + 4), kChunkRows, 1};
   const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != kOk) return rc;
 
-  const size_t smem = static_cast<size_t>(kStages) * (tile_cols + 4) * kChannels * 2 + 25 * 32 * 8;
-  const unsigned grid = static_cast<unsigned>(ctas), block = (warps + 1) * 32;
+  const unsigned grid = static_cast<unsigned>(ctas < 148LL * 2 ? ctas : 148LL * 2);  // two persistent CTAs per SM
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (g_dw_debug != 0) {  // measurement hooks: a separate instantiation, so the production kernel carries no flag tests
-    if (act == kActGelu) dw5x5_kernel<MODE, kActGelu, true, true><<<grid, block, smem, s>>>(map, p);
-    else dw5x5_kernel<MODE, kActRelu, true, true><<<grid, block, smem, s>>>(map, p);
-  } else if (act == kActGelu) {
-    dw5x5_kernel<MODE, kActGelu, true, false><<<grid, block, smem, s>>>(map, p);
-  } else if (act == kActRelu) {
-    dw5x5_kernel<MODE, kActRelu, true, false><<<grid, block, smem, s>>>(map, p);
-  } else {
-    dw5x5_kernel<MODE, kActNone, true, false><<<grid, block, smem, s>>>(map, p);
-  }
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t e = warps == 4 ? launch_kernel<MODE, 4>(map, p, act, grid, s) : launch_kernel<MODE, 5>(map, p, act, grid, s);
+  return static_cast<int>(e);
 }
 
 }  // namespace

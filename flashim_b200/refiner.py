@@ -20,6 +20,7 @@ import torch
 from torch import Tensor, nn
 
 from flashim_b200 import ops
+from flashim_b200.backends.sm100.kernels import check_status
 from flashim_b200.build import EAGER, BuildContext, EngineSpec, ModelSpec
 from flashim_b200.config import RunConfig
 from flashim_b200.quant.tensor import QuantizedWeight, padded_channels, swizzle_scales
@@ -120,13 +121,19 @@ def _load(config: RunConfig) -> nn.Module:
 
 
 def _graph_setup(model: nn.Module, ctx: BuildContext) -> None:
-    """``cuda-graph`` engine: capture one forward per input-shape signature and replay it (the launch-bound small
-    levels gain; shapes must repeat). After flashim/engines/cuda_graph.py:19-63."""
+    """``cuda-graph`` engine: capture one forward per input-shape signature and replay it (shapes must repeat). The 17
+    launches per level and chunk cost more on the host than on the GPU once the kernels are fast; a replay has no host
+    cost. ``model.static_inputs(pyramid)`` returns the graph's own input buffers for that signature: a caller that
+    writes its inputs there (e.g. the host-to-device copy) and passes them back skips the staging copy.
+    After flashim/engines/cuda_graph.py:19-63."""
     eager_forward = model.forward
     graphs: dict = {}
 
-    def forward(pyramid):
-        key = tuple((tuple(t.shape), t.dtype) for t in pyramid)
+    def signature(pyramid):
+        return tuple((tuple(t.shape), t.dtype) for t in pyramid)
+
+    def entry_for(pyramid):
+        key = signature(pyramid)
         entry = graphs.get(key)
         if entry is None:
             static_in = [t.clone() for t in pyramid]
@@ -136,17 +143,90 @@ def _graph_setup(model: nn.Module, ctx: BuildContext) -> None:
                 for _ in range(2):
                     eager_forward(static_in)
             torch.cuda.current_stream().wait_stream(stream)
+            check_status(static_in[0].device)  # kernels inside a capture cannot be checked; the warm-up runs of the same shapes can
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_out = eager_forward(static_in)
             entry = graphs[key] = (graph, static_in, static_out)
-        graph, static_in, static_out = entry
+        return entry
+
+    def forward(pyramid):
+        graph, static_in, static_out = entry_for(pyramid)
         for dst, src in zip(static_in, pyramid):
-            dst.copy_(src)
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src)
         graph.replay()
         return static_out
 
+    # ---- host-to-host streaming: per-chunk graphs in two slots, copies on their own streams ----
+    chunk_graphs: dict = {}
+    streams: dict = {}
+
+    def chunk_entry(index: int, level, shape, dtype, device, slot: int):
+        key = (index, tuple(shape), dtype, slot)
+        entry = chunk_graphs.get(key)
+        if entry is None:
+            static_in = torch.zeros(shape, dtype=dtype, device=device)
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side), torch.inference_mode():
+                for _ in range(2):
+                    level(static_in)
+            torch.cuda.current_stream(device).wait_stream(side)
+            check_status(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph), torch.inference_mode():
+                static_out = level(static_in)
+            entry = chunk_graphs[key] = (graph, static_in, static_out)
+        return entry
+
+    def forward_host(host_pyramid, host_outputs):
+        """Pinned host pyramid -> pinned host head outputs. Chunk ``i + 1`` crosses PCIe while chunk ``i`` computes and
+        chunk ``i - 1`` returns: a copy-in stream, the compute stream and a copy-out stream, two buffer slots per level,
+        ordered by events only (no host synchronisation until the end)."""
+        device = next(model.parameters(), next(model.buffers())).device
+        compute = torch.cuda.current_stream(device)
+        if device not in streams:
+            streams[device] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        copy_in, copy_out = streams[device]
+        copy_in.wait_stream(compute)
+        copy_out.wait_stream(compute)
+        in_free: dict = {}   # (level, slot) -> event: the graph that read this input buffer has run
+        out_free: dict = {}  # (level, slot) -> event: the copy-out of this output buffer has finished
+        step = 0
+        for index, (level, src, dst) in enumerate(zip(model.levels, host_pyramid, host_outputs)):
+            for start in range(0, src.shape[0], model.chunk):
+                part = src[start: start + model.chunk]
+                slot = step & 1
+                step += 1
+                graph, static_in, static_out = chunk_entry(index, level, part.shape, part.dtype, device, slot)
+                key = (index, tuple(part.shape), slot)
+                with torch.cuda.stream(copy_in):
+                    if key in in_free:
+                        copy_in.wait_event(in_free[key])
+                    static_in.copy_(part, non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(copy_in)
+                compute.wait_event(arrived)
+                if key in out_free:
+                    compute.wait_event(out_free[key])
+                graph.replay()
+                done = torch.cuda.Event()
+                done.record(compute)
+                in_free[key] = done
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(done)
+                    dst[start: start + part.shape[0]].copy_(static_out, non_blocking=True)
+                    returned = torch.cuda.Event()
+                    returned.record(copy_out)
+                out_free[key] = returned
+        compute.wait_stream(copy_out)
+        compute.synchronize()
+        return host_outputs
+
     model.forward = forward
+    model.static_inputs = lambda pyramid: entry_for(pyramid)[1]
+    model.forward_host = forward_host
 
 
 def _validate(config: RunConfig) -> None:

@@ -9,7 +9,7 @@ import torch
 
 reference = os.environ.get("FLASHIM_REFERENCE", "/root/reference")
 if os.path.isdir(os.path.join(reference, "flashim")) and reference not in sys.path:
-    sys.path.insert(0, reference)
+    sys.path.append(reference)  # behind this repository, whose `tests` package must keep winning
 flashim = pytest.importorskip("flashim")
 
 

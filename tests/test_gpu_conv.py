@@ -5,7 +5,7 @@ import torch
 import torch.nn.functional as F
 
 import oracle
-from tests.conftest import DEV, bf16_ulp_distance, code_mismatch, rel_l2, same_bytes, to_dev
+from fim_testlib import DEV, bf16_ulp_distance, code_mismatch, rel_l2, same_bytes, to_dev
 
 pytestmark = pytest.mark.gpu
 E4M3, BF16 = torch.float8_e4m3fn, torch.bfloat16

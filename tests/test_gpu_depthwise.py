@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from tests.conftest import DEV, bf16_ulp_distance, code_mismatch, same_bytes, to_dev
+from fim_testlib import DEV, bf16_ulp_distance, code_mismatch, same_bytes, to_dev
 
 pytestmark = pytest.mark.gpu
 E4M3, BF16 = torch.float8_e4m3fn, torch.bfloat16

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import oracle
-from tests.conftest import DEV, same_bytes, to_dev
+from fim_testlib import DEV, same_bytes, to_dev
 
 pytestmark = pytest.mark.gpu
 E4M3, BF16 = torch.float8_e4m3fn, torch.bfloat16

@@ -9,7 +9,7 @@ import torch
 import torch.nn.functional as F
 
 import oracle
-from tests.conftest import same_bytes
+from fim_testlib import same_bytes
 
 E4M3 = torch.float8_e4m3fn
 BF16 = torch.bfloat16
