@@ -293,6 +293,24 @@ __device__ __forceinline__ int e8m0_exponent(float amax) {
   return min(127, max(-127, e));
 }
 
+// The same value on the bits of a non-negative amax, arranged for issue slots: away from the narrow mantissa window where
+// the reference's logarithm rounds back (40 ulp above 1.75) the answer is E - 8 + (mantissa > 1.75), clamped; inside
+// the window (and for inf / nan) the full rule decides. The branch is taken about once in 200000 blocks.
+__device__ __forceinline__ int e8m0_exponent_bits(uint32_t bits) {
+  const uint32_t mantissa = bits & 0x7FFFFFu;
+  const int biased = static_cast<int>(bits >> 23);
+  int e = biased - 135 + (mantissa > 0x600000u ? 1 : 0);
+  if ((mantissa - 0x600001u) < 40u || biased == 255) e = e8m0_exponent(__uint_as_float(bits));
+  return min(127, max(-127, e));
+}
+
+// max over the lanes named in `mask` (every one of which executes this with the same mask)
+__device__ __forceinline__ uint32_t redux_max(uint32_t value, uint32_t mask) {
+  uint32_t r;
+  asm volatile("redux.sync.max.u32 %0, %1, %2;" : "=r"(r) : "r"(value), "r"(mask));
+  return r;
+}
+
 // 2**e for e in [-127, 127], exact (2**-127 is a subnormal).
 __device__ __forceinline__ float exp2_int(int e) {
   return __uint_as_float(e == -127 ? 0x00400000u : static_cast<uint32_t>(e + 127) << 23);
