@@ -222,7 +222,7 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
     for (int i = 0; i < 4; ++i) m[i] = bf16x2_absmax(m[2 * i], m[2 * i + 1]);
     m[0] = bf16x2_absmax(bf16x2_absmax(m[0], m[1]), bf16x2_absmax(m[2], m[3]));
     const uint32_t top = max(m[0] & 0x7FFFu, (m[0] >> 16) & 0x7FFFu);
-    e = e8m0_exponent(__uint_as_float(top << 16));
+    e = e8m0_exponent_bits(top << 16);
     if (valid) {
       const int groups = p.cout >> 5;
       p.out_scales[swizzled_scale_offset(pixel, n >> 5, (groups + 3) >> 2)] = static_cast<uint8_t>(e + 127);
@@ -477,6 +477,15 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const size_t pixel = (static_cast<size_t>(b) * p.out_h + y) * p.out_w + x;
       const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
       const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
+      if (p.residual != nullptr && valid && p.res_stride[3] == 1) {
+        // ask for this row's residual line in L2 before the wait for the accumulator, so that the loads in the epilogue
+        // do not pay the DRAM latency (a prefetch holds no registers)
+        const int n_first = n0 + group * kGroupColumns;
+        if (n_first < p.res_channels) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + b * p.res_stride[0] + y * p.res_stride[1] + x * p.res_stride[2] +
+                                                          n_first));
+        }
+      }
       if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;

@@ -2,8 +2,9 @@
 // static INT8. Arithmetic follows FlashIM's torch reference (flashim/ops/conv.py:30-61): bf16 inputs and weights,
 // fp32 FMA chain ordered (ky, kx) from zero, bias added last.
 //
-// Layout of the work. A CTA owns 64 channels x (4 * warps) columns x `tile_rows` rows of one image. Input rows (with
-// their 2-pixel halo, zero-filled outside the image by TMA) arrive five at a time in a ring of shared-memory chunks; a
+// Layout of the work. A CTA works on strips of 64 channels x (4 * warps) columns of one image, five output rows (a unit)
+// at a time; the persistent CTAs split the sequence of all units evenly. Input rows (with their 2-pixel halo, zero-filled
+// outside the image by TMA) arrive five at a time in a ring of shared-memory chunks; a
 // lane owns one bf16x2 channel pair and four adjacent columns, keeps the 25 weight pairs and five rows of partial sums in
 // registers as packed fp32 pairs (fma.rn.f32x2: both channels in one issue slot), and finishes one output row per input
 // row. The kernel is bound by the fp32 pipe (25 FMAs per element = 100 packed FMAs per lane and row), so everything
@@ -20,7 +21,7 @@ namespace {
 constexpr int kChannels = 64;    // per CTA: one 128-byte line per pixel
 constexpr int kCols = 4;         // output columns per lane
 constexpr int kChunkRows = 5;    // input rows per ring chunk = accumulator slots
-constexpr int kStages = 3;       // chunks in the ring
+constexpr int kStages = 5;       // chunks in the ring: the producer runs up to 20 rows ahead (a chunk takes ~2 us to arrive)
 constexpr int kMinWarps = 4, kMaxWarps = 5;  // compute warps per CTA (plus one producer warp)
 
 enum { kOutBf16 = 0, kOutMx = 1, kOutInt8 = 2 };
@@ -32,7 +33,8 @@ struct DwParams {
   uint8_t* scales;
   const float* scale;  // INT8
   int batch, height, width, channels;
-  int tile_rows, tiles_x, tiles_y, channel_tiles, total_tiles;  // tile_rows + 4 is a multiple of kChunkRows
+  int tiles_x, channel_tiles;  // a strip = (image, 64-channel tile, column tile), all rows of the image
+  int strip_chunks, total_units;  // 5-row output chunks per strip; work units = strips * strip_chunks
   int act, swizzled;
   int* status;
   int debug;  // timing experiments only: 1 = no FMAs, 2 = no epilogue, 4 = no loads and no waits for them
@@ -93,7 +95,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     }
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 4));
     m[0] = fmaxf(m[0], __shfl_xor_sync(0xffffffffu, m[0], 8));
-    const int e = e8m0_exponent(m[0]);
+    const int e = e8m0_exponent_bits(__float_as_uint(m[0]));
     const float inv_mine = exp2_int(-e);
     const int mine = ((lane & 1) << 1) | ((lane >> 1) & 1);  // the pixel this lane holds
     if ((lane & 12) == 0 && ((cols_ok >> mine) & 1u)) {
@@ -144,13 +146,12 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // Persistent CTAs: this one owns the contiguous tile range [t_begin, t_end) (x fastest, then y, channel tile, batch),
-  // so the chunk ring keeps flowing from one tile into the next and neighbouring tiles (shared halo columns, same
-  // weights) follow each other on the same SM.
-  const int t_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * p.total_tiles / gridDim.x);
-  const int t_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.total_tiles / gridDim.x);
-  const int chunks = (p.tile_rows + 4) / kChunkRows;
-  const int total_chunks = (t_end - t_begin) * chunks;
+  // Persistent CTAs over work units of five output rows. A strip is one (image, channel tile, column tile) over all rows;
+  // the units of all strips form one sequence, of which this CTA owns the contiguous range [u_begin, u_end): an equal
+  // share to within one unit, cut into spans where it crosses a strip. A span of `len` units reads len + 1 input chunks
+  // (its rows plus the halo above and below), so the chunk ring flows on from span to span without draining.
+  const int u_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * p.total_units / gridDim.x);
+  const int u_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.total_units / gridDim.x);
   const bool loads = !(PROBE && (p.debug & 4));
 
   const uint32_t smem0 = smem_u32(smem_raw), full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
@@ -173,25 +174,27 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
       uint32_t s = 0, phase = 0;
       int n = 0;
       bool stop = false;
-      for (int tile = t_begin; tile < t_end && !stop; ++tile) {
-        int t = tile;
+      for (int u = u_begin; u < u_end && !stop;) {
+        const int strip = u / p.strip_chunks, k0 = u - strip * p.strip_chunks;
+        const int len = min(p.strip_chunks - k0, u_end - u);
+        u += len;
+        int t = strip;
         const int tx = t % p.tiles_x; t /= p.tiles_x;
-        const int ty = t % p.tiles_y; t /= p.tiles_y;
         const int ct = t % p.channel_tiles;
         const int b = t / p.channel_tiles;
-        for (int g = 0; g < chunks; ++g, ++n) {
+        for (int g = 0; g <= len; ++g, ++n) {
           if (n >= kStages && !mbar_wait_addr(empty0 + 8 * s, phase ^ 1, &abort_flag, p.status, kStatusWaitRows)) {
             stop = true;
             break;
           }
           mbar_expect_tx_addr(full0 + 8 * s, kChunkBytes);
           tma_load_4d_addr(smem0 + s * kChunkBytes, &in_map, full0 + 8 * s, ct * kChannels, tx * kTileCols - 2,
-                           ty * p.tile_rows - 2 + g * kChunkRows, b);
+                           (k0 + g) * kChunkRows - 2, b);
           if (++s == kStages) s = 0, phase ^= 1;
         }
       }
     }
-  } else if (total_chunks > 0) {
+  } else if (u_end > u_begin) {
     // ===== consumers =====
     const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
     const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
@@ -199,10 +202,10 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
     const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
     const size_t row_pairs = static_cast<size_t>(p.width) * pair_stride;
 
-    // per-tile state, set when a tile's first chunk starts
+    // per-span state
     uint64_t wreg[25];
     uint64_t bias2 = 0ull;
-    int c = 0, last_ct = -1, y_base = 0, y_out = 0;
+    int c = 0, last_ct = -1, y_base = 0, y_end = 0, y_out = 0;
     uint32_t cols_ok = 0;
     size_t pixel0 = 0;
     uint8_t* out_row = nullptr;
@@ -214,6 +217,12 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // a slot is read for real only after its first multiply
 
+    uint64_t fin[kCols];  // the output row completed by the previous input row, with where it goes (mask 0: nowhere)
+    uint32_t fin_mask = 0;
+    uint8_t* fin_out = nullptr;
+    size_t fin_pixel = 0;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) fin[j] = 0ull;
     uint32_t s = 0, phase = 0;
     uint32_t raw[kCols + 4];  // bf16x2 words of the input row about to be used
     bool ok = !loads || mbar_wait_addr(full0, 0, &abort_flag, p.status, kStatusWaitRows);
@@ -222,12 +231,13 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + j * (kChannels * 2));
     }
-    int tile = t_begin, g = 0;
-    for (int n = 0; n < total_chunks && alive; ++n) {
-      if (g == 0) {
-        int t = tile;
+    for (int u = u_begin; u < u_end && alive;) {
+      const int strip = u / p.strip_chunks, k0 = u - strip * p.strip_chunks;
+      const int len = min(p.strip_chunks - k0, u_end - u);
+      u += len;
+      {
+        int t = strip;
         const int tx = t % p.tiles_x; t /= p.tiles_x;
-        const int ty = t % p.tiles_y; t /= p.tiles_y;
         const int ct = t % p.channel_tiles;
         const int b = t / p.channel_tiles;
         c = ct * kChannels + 2 * lane;
@@ -244,11 +254,14 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
         cols_ok = 0;
 #pragma unroll
         for (int j = 0; j < kCols; ++j) cols_ok |= (lane_active && x0 + j < p.width) ? (1u << j) : 0u;
-        y_base = ty * p.tile_rows;
-        y_out = y_base - 4;  // where the tile's first input row would "finish": four rows above the tile
+        y_base = k0 * kChunkRows;
+        y_end = min(y_base + len * kChunkRows, p.height);
+        y_out = y_base - 4;  // where the span's first input row would "finish": four rows above the span
         pixel0 = (static_cast<size_t>(b) * p.height + y_base) * p.width + x0;  // of output row y_base, advanced per emitted row
         out_row = static_cast<uint8_t*>(p.out) + (pixel0 * pair_stride + (c >> 1)) * kOutBytes;
       }
+      for (int g = 0; g <= len && alive; ++g) {
+        const bool more = g < len || u < u_end;  // another chunk follows, in this span or the next
       const uint32_t chunk = lane_smem + s * kChunkBytes;
       const uint32_t s_next = s + 1 == kStages ? 0u : s + 1;
       const uint32_t phase_next = s + 1 == kStages ? phase ^ 1u : phase;
@@ -266,13 +279,14 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
           // may already belong to the next tile)
           __syncwarp();
           if (lane == 0 && loads) mbar_arrive_addr(empty0 + 8 * s);
-          if (n + 1 < total_chunks) {
+          if (more) {
             ok = !loads || mbar_wait_addr(full0 + 8 * s_next, phase_next, &abort_flag, p.status, kStatusWaitRows);
             alive = __all_sync(0xffffffffu, ok);
 #pragma unroll
             for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + s_next * kChunkBytes + j * (kChannels * 2));
           }
         }
+        if (!(PROBE && (p.debug & 2))) emit_row<MODE, ACT>(p, fin, bias2, fin_out, fin_pixel, c, fin_mask, int8_scale);
         if (!(PROBE && (p.debug & 1))) {
           // 100 packed FMAs: input row r = 5 g + ph feeds tap row ky of the output row in slot (ph - ky) mod 5. Tap column
           // outermost, so neighbouring instructions belong to 20 different accumulators and nothing waits on the FMA
@@ -292,16 +306,23 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 #pragma unroll
           for (int j = 0; j < kCols; ++j) acc[(ph + 1) % 5][j] = in[j] ^ in[j + 4];  // keep the loads alive
         }
-        // the output row in slot (ph + 1) mod 5 has now received all five input rows
-        if (y_out >= y_base && y_out < p.height && !(PROBE && (p.debug & 2))) {
-          emit_row<MODE, ACT>(p, acc[(ph + 1) % 5], bias2, out_row, pixel0, c, cols_ok, int8_scale);
-          pixel0 += p.width;
-          out_row += row_pairs * kOutBytes;
+        // The output row in slot (ph + 1) mod 5 has now received all five input rows. It is finished (bias, activation,
+        // stores) beside the FMAs of the next input row: no branch separates the two, so they interleave, and a row that
+        // lies outside the span simply has an empty store mask.
+        {
+          const bool valid = y_out >= y_base && y_out < y_end;
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) fin[j] = acc[(ph + 1) % 5][j];
+          fin_mask = valid ? cols_ok : 0u;
+          fin_out = out_row;
+          fin_pixel = pixel0;
+          pixel0 += valid ? static_cast<size_t>(p.width) : 0;
+          out_row += valid ? row_pairs * kOutBytes : 0;
         }
         ++y_out;
       }
       s = s_next, phase = phase_next;
-      if (++g == chunks) g = 0, ++tile;
+      }
     }
   }
   if (abort_flag) {
@@ -315,35 +336,18 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 int g_dw_debug = 0;
 
 int pick_warps(int width) {
-  // fewest idle columns in the last tile of a row; on ties the narrower CTA
+  // Four compute warps put one on each of the SM's four schedulers (two with the second resident CTA); a fifth would
+  // double up on one scheduler while the others idle a sixth of the time, so five only wins when its 20 columns fit the
+  // image width much better than 16 do.
   int best = kMinWarps;
   double best_eff = 0.0;
   for (int w = kMinWarps; w <= kMaxWarps; ++w) {
     const int cols = w * kCols;
-    const double eff = static_cast<double>(width) / (static_cast<double>(ceil_div(width, cols)) * cols);
+    const double balance = w == 4 ? 1.0 : 5.0 / 6.0;
+    const double eff = balance * static_cast<double>(width) / (static_cast<double>(ceil_div(width, cols)) * cols);
     if (eff > best_eff + 1e-9) {
       best_eff = eff;
       best = w;
-    }
-  }
-  return best;
-}
-
-int pick_tile_rows(int height, long long tiles_per_row_band) {
-  // Rows per CTA (+ 4 halo rows = a whole number of chunks). A tile costs tile_rows + 4 rows of FMAs, so tall tiles waste
-  // less on the halo and on rows past the image's last; short tiles fill the 148 SMs (two CTAs each) more evenly. The
-  // cost below is FMA rows per row band, stretched by half of the idle fraction of the last wave.
-  int best = 6;
-  double best_cost = 1e30;
-  for (int rows = 6; rows <= 61; rows += kChunkRows) {
-    const long long tiles_y = ceil_div(height, rows);
-    const double waves = static_cast<double>(tiles_per_row_band * tiles_y) / (148.0 * 2.0);
-    const double whole = waves <= 1.0 ? 1.0 : static_cast<double>(static_cast<long long>(waves + 0.999999));
-    const double stretch = waves <= 1.0 ? 1.0 : 1.0 + 0.5 * (whole / waves - 1.0);
-    const double cost = static_cast<double>(tiles_y) * (rows + 4) * stretch;
-    if (cost < best_cost - 1e-9) {
-      best_cost = cost;
-      best = rows;
     }
   }
   return best;
@@ -403,12 +407,11 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   p.batch = batch, p.height = height, p.width = width, p.channels = channels;
   p.tiles_x = ceil_div(width, tile_cols);
   p.channel_tiles = ceil_div(channels, kChannels);
-  p.tile_rows = pick_tile_rows(height, static_cast<long long>(p.tiles_x) * p.channel_tiles * batch);
-  p.tiles_y = ceil_div(height, p.tile_rows);
+  p.strip_chunks = ceil_div(height, kChunkRows);
   p.act = act, p.swizzled = swizzled, p.status = status, p.debug = g_dw_debug;
-  const long long ctas = static_cast<long long>(p.tiles_x) * p.tiles_y * p.channel_tiles * batch;
-  if (ctas > 0x7fffffffLL) return kUnsupported;
-  p.total_tiles = static_cast<int>(ctas);
+  const long long units = static_cast<long long>(p.tiles_x) * p.channel_tiles * batch * p.strip_chunks;
+  if (units > 0x7fffffffLL) return kUnsupported;
+  p.total_units = static_cast<int>(units);
 
   CUtensorMap map;
   const uint64_t dims[4] = {static_cast<uint64_t>(channels), static_cast<uint64_t>(width), static_cast<uint64_t>(height),
@@ -419,7 +422,9 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != kOk) return rc;
 
-  const unsigned grid = static_cast<unsigned>(ctas < 148LL * 2 ? ctas : 148LL * 2);  // two persistent CTAs per SM
+  // two persistent CTAs per SM; a small problem gets fewer, each with at least four units so the halo chunk stays cheap
+  const long long want = (units + 3) / 4;
+  const unsigned grid = static_cast<unsigned>(want < 148LL * 2 ? want : 148LL * 2);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const cudaError_t e = warps == 4 ? launch_kernel<MODE, 4>(map, p, act, grid, s) : launch_kernel<MODE, 5>(map, p, act, grid, s);
   return static_cast<int>(e);
