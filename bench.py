@@ -121,12 +121,24 @@ def _rotation(bytes_per_buffer: int) -> int:
 
 
 def _time_launches(fn, count: int) -> float:
-    """Average device time of `fn`'s launches in ms, CUDA events on the launching (current) stream."""
+    """Average device time of one call of `fn` in ms: `count` calls are captured into a CUDA graph (so that the host's
+    launch cost, 40-60 us per op from Python, is not in the figure for kernels shorter than that) and the replay is
+    bracketed by CUDA events on the stream it runs on. `fn` should rotate over inputs larger than L2."""
+    count = max(count, 10)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(count):
+            fn()
+    graph.replay()  # warm
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     start.record()
-    for _ in range(count):
-        fn()
+    graph.replay()
     end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) / count
@@ -443,11 +455,13 @@ WORKLOADS = {"stack": StackWorkload, "conv": ConvWorkload, "int8": Int8Workload,
 DEFAULT_WORKLOAD = "stack"
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel, from the ncu
+# captures summarised under profiles/ (file named beside each figure); None where no capture exists.
+NCU_TRAFFIC: dict[str, float] = {}
+
+
 def _traffic(name: str):
-    path = ROOT / "profiles" / "dram_traffic.json"
-    if path.is_file():
-        return json.loads(path.read_text()).get(name)
-    return None
+    return NCU_TRAFFIC.get(name)
 
 
 def _cpu_loop(fn, units_per_call: float, budget_s: float, unit: str, sample: str) -> dict:
@@ -538,8 +552,12 @@ def main() -> None:
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--pairs", type=int, default=StackWorkload.PAIRS,
+                        help="image pairs of the stack workload (BASELINE config 5 has 64; smaller values are for ncu captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    StackWorkload.PAIRS = args.pairs
+    StackWorkload.name = f"refiner-stack-{args.pairs}-pairs"
 
     if args.impl == "reference":
         run_reference(args)

@@ -90,7 +90,7 @@ __device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_
 }
 
 // bf16x2 words r[16] -> E4M3 codes of value * 2**-e, four per output word
-__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[32]) {
+__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[16]) {
   const float inv = exp2_int(-e);
   const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
@@ -102,16 +102,10 @@ __device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, ui
   }
 }
 
+// fp32 value (+ INT8 dequantisation) + bias of one chunk, as 16 packed pairs
 template <bool INT8>
-__device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, size_t pixel,
-                                             int b, int y, int x, bool valid, float a_scale, uint32_t (&w)[32]) {
-  if (INT8 && p.out_mode == FIM_OUT_INT32) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = raw[i];
-    return;
-  }
-  // ---- fp32 value + bias, as packed pairs ----
-  uint64_t v2[16];
+__device__ __forceinline__ void biased_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
+                                             uint64_t (&v2)[16]) {
   if (INT8) {
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
@@ -134,24 +128,48 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
       v2[2 * i + 1] = add2(v2[2 * i + 1], b1);
     }
   }
-  if (!INT8 && p.out_mode == FIM_OUT_F32) {
+}
+
+// Four-byte outputs: the int32 accumulators as they are, or the biased fp32 values
+template <bool INT8>
+__device__ __forceinline__ void wide_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
+                                           uint32_t (&w)[32]) {
+  if (INT8 && p.out_mode == FIM_OUT_INT32) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float lo, hi;
-      unpack2(v2[i], lo, hi);
-      w[2 * i] = __float_as_uint(lo), w[2 * i + 1] = __float_as_uint(hi);
-    }
+    for (int i = 0; i < 32; ++i) w[i] = raw[i];
     return;
   }
-  // ---- one bf16 rounding; activation on the rounded value (ReLU waits for the residual when there is one) ----
-  const bool has_res = p.residual != nullptr;
-  uint32_t r[16];
+  uint64_t v2[16];
+  biased_chunk<INT8>(p, raw, n, bias_at, a_scale, v2);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float lo, hi;
+    unpack2(v2[i], lo, hi);
+    w[2 * i] = __float_as_uint(lo), w[2 * i + 1] = __float_as_uint(hi);
+  }
+}
+
+// First step of the other outputs: one bf16 rounding of the biased values, 16 bf16x2 words. This step is short, so the
+// accumulator can go back to the MMA warp before the long arithmetic starts.
+template <bool INT8>
+__device__ __forceinline__ void round_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
+                                            uint32_t (&r)[16]) {
+  uint64_t v2[16];
+  biased_chunk<INT8>(p, raw, n, bias_at, a_scale, v2);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     float lo, hi;
     unpack2(v2[i], lo, hi);
     r[i] = pack_bf16(lo, hi);
   }
+}
+
+// Second step, on the rounded values: activation (ReLU waits for the residual when there is one), residual, and the
+// output format.
+template <bool INT8>
+__device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[16], int n, size_t pixel, int b, int y, int x,
+                                             bool valid, uint32_t (&w)[16]) {
+  const bool has_res = p.residual != nullptr;
   if (p.act == kActGelu) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -233,13 +251,14 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, const uint32_t
 
 // Write this row's 32 * elem bytes of a panel into swizzled shared memory (the layout a TMA store with swizzle mode
 // 32 * elem bytes reads): 16-byte slot i of row r lands in slot i ^ ((r * pitch / 128) mod slots).
-__device__ __forceinline__ void stage_row(uint32_t panel, int row, int elem, const uint32_t (&w)[32]) {
+template <int WORDS>
+__device__ __forceinline__ void stage_row(uint32_t panel, int row, int elem, const uint32_t (&w)[WORDS]) {
   const uint32_t pitch = 32u * elem;           // 32, 64 or 128 bytes
   const uint32_t slots = pitch >> 4;           // 2, 4 or 8
   const uint32_t phase = ((static_cast<uint32_t>(row) * pitch) >> 7) & (slots - 1);
   const uint32_t base = panel + row * pitch;
 #pragma unroll
-  for (uint32_t i = 0; i < 8; ++i) {
+  for (uint32_t i = 0; i < WORDS / 4; ++i) {
     if (i < slots) {
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + ((i ^ phase) << 4)), "r"(w[4 * i]), "r"(w[4 * i + 1]),
                    "r"(w[4 * i + 2]), "r"(w[4 * i + 3])
@@ -489,44 +508,70 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
-      // Drain two 32-column chunks at a time into registers (ten warps share a register file quarter three deep, which
-      // caps a thread at 168 registers) and hand the accumulator back as soon as the last chunk is read, before its
-      // arithmetic.
-      constexpr int kGroup = 1;
+      // Drain: every chunk of this warp is read, biased and rounded to bf16x2 words first (16 registers per chunk), and
+      // the accumulator goes back to the MMA warp right after the last read; the long arithmetic follows. Four-byte
+      // outputs cannot be held that compactly: their chunks are finished one by one.
+      const bool wide = p.out_elem == 4;
+      auto take_panel = [&]() -> uint32_t {  // a free output panel of this group
+        const uint32_t panel = panels + (chunk_it & (p.panels_per_half - 1)) * panel_bytes;
+        ++chunk_it;
+        if (leader) {  // the store that last read this panel has finished with it
+          if (p.panels_per_half == 2) {
+            bulk_wait_read<1>();
+          } else {
+            bulk_wait_read<0>();
+          }
+        }
+        named_barrier(bar_id, 128);
+        return panel;
+      };
+      auto send_panel = [&](uint32_t panel, int n) {
+        fence_async_proxy();
+        named_barrier(bar_id, 128);
+        if (leader && store) {
+          tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
+          bulk_commit();
+        }
+      };
+      auto release_accumulator = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
+      };
+      if (wide) {
 #pragma unroll
-      for (int g = 0; g < kChunksPerWarp; g += kGroup) {
-        uint32_t raw[kGroup][32];
+        for (int g = 0; g < kChunksPerWarp; ++g) {
+          const int n = n0 + group * kGroupColumns + g * 32;
+          uint32_t raw[32], w[32];
+          tmem_load_32(lane_addr + g * 32, raw);
+          tmem_load_wait();
+          if (g + 1 == kChunksPerWarp) release_accumulator();
+          if (n >= p.cout) continue;  // uniform over the four warps of this group
+          wide_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, w);
+          const uint32_t panel = take_panel();
+          stage_row<32>(panel, row, p.out_elem, w);
+          send_panel(panel, n);
+        }
+      } else {
+        uint32_t q[kChunksPerWarp][16];
 #pragma unroll
-        for (int i = 0; i < kGroup; ++i) tmem_load_32(lane_addr + (g + i) * 32, raw[i]);
-        tmem_load_wait();
-        if (g + kGroup >= kChunksPerWarp) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
+        for (int g = 0; g < kChunksPerWarp; ++g) {
+          const int n = n0 + group * kGroupColumns + g * 32;
+          uint32_t raw[32];
+          tmem_load_32(lane_addr + g * 32, raw);
+          tmem_load_wait();
+          if (g + 1 == kChunksPerWarp) release_accumulator();
+          if (n < p.cout) round_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, q[g]);
         }
 #pragma unroll
-        for (int i = 0; i < kGroup; ++i) {
-          const int n = n0 + group * kGroupColumns + (g + i) * 32;
+        for (int g = 0; g < kChunksPerWarp; ++g) {
+          const int n = n0 + group * kGroupColumns + g * 32;
           if (n >= p.cout) continue;  // uniform over the four warps of this group
-          uint32_t w[32];
-          finish_chunk<INT8>(p, raw[i], n, smem_bias + static_cast<uint32_t>(n) * 4u, pixel, b, y, x, valid, a_scale, w);
-          const uint32_t panel = panels + (chunk_it & (p.panels_per_half - 1)) * panel_bytes;
-          ++chunk_it;
-          if (leader) {  // the store that last read this panel has finished with it
-            if (p.panels_per_half == 2) {
-              bulk_wait_read<1>();
-            } else {
-              bulk_wait_read<0>();
-            }
-          }
-          named_barrier(bar_id, 128);
-          stage_row(panel, row, p.out_elem, w);
-          fence_async_proxy();
-          named_barrier(bar_id, 128);
-          if (leader && store) {
-            tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
-            bulk_commit();
-          }
+          uint32_t w[16];
+          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, w);
+          const uint32_t panel = take_panel();
+          stage_row<16>(panel, row, p.out_elem, w);
+          send_panel(panel, n);
         }
       }
     }
