@@ -31,6 +31,7 @@ struct ConvParams {
   int cin, cout, out_h, out_w;
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
+  int full_tiles;  // tiles [0, full_tiles) are BN wide; the rest are the halves (BN / 2 columns) of the last few tiles
   int k_chunks, stages;
   int panels_per_half;  // output panels each column group of the epilogue rotates through (1 or 2)
   // scales (MXFP8)
@@ -267,6 +268,23 @@ __device__ __forceinline__ void stage_row(uint32_t panel, int row, int elem, con
   }
 }
 
+// Tile index -> row tile, first output channel and width. The tiles of the last, partial round of the persistent CTAs are
+// split into two half-width tiles each when that lets the round finish in half the time (the host decides: full_tiles).
+template <int BN>
+__device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& m_tile, int& n0, int& width) {
+  if (tile < p.full_tiles) {
+    m_tile = tile / p.tiles_n;
+    n0 = (tile - m_tile * p.tiles_n) * BN;
+    width = BN;
+  } else {
+    const int h = tile - p.full_tiles;
+    const int whole = p.full_tiles + (h >> 1);
+    m_tile = whole / p.tiles_n;
+    n0 = (whole - m_tile * p.tiles_n) * BN + (h & 1) * (BN / 2);
+    width = BN / 2;
+  }
+}
+
 template <bool INT8, int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
@@ -275,6 +293,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   constexpr int kScaleTilesB = scale_tiles_b(BN);
   constexpr int kKSteps = BK / 32;
   constexpr uint32_t kABytes = kTileM * BK, kBBytes = BN * BK;
+  constexpr int kWeightBoxRows = BN < 128 ? BN : 128;  // rows of one weight TMA box
   constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
   constexpr uint32_t kSfbColumn = kAccStages * BN;                        // one set of kSfbColumns per stage
   constexpr uint32_t kSfaColumn = kSfbColumn + kMaxStages * kSfbColumns;  // static scales: 4 columns per 128 input channels,
@@ -355,18 +374,21 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     if (lane == 0) {
       const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
       const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
-      const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? kBBytes : 0u) +
-                                (INT8 ? 0u : kScaleTilesB * 512u + (dynamic_a ? 512u : 0u));
       uint32_t s = 0, phase = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x) {
-        const int nt = tile % p.tiles_n;
-        const int m_tile = tile / p.tiles_n;
+        int m_tile, n0, width;
+        decode_tile<BN>(p, tile, m_tile, n0, width);
         int m = m_tile;
         const int tx = m % p.tiles_x; m /= p.tiles_x;
         const int ty = m % p.tiles_y;
         const int b = m / p.tiles_y;
-        const int x0 = tx * p.tile_w - p.pad_w, y0 = ty * p.tile_h - p.pad_h, n0 = nt * BN;
+        const int x0 = tx * p.tile_w - p.pad_w, y0 = ty * p.tile_h - p.pad_h;
+        // the weight tile arrives in boxes of kWeightBoxRows rows (a 256-wide tile is two boxes, its half one)
+        const int b_parts = width / kWeightBoxRows;
+        const int scale_tiles = BN <= 128 ? 1 : width / 128;
+        const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? static_cast<uint32_t>(width) * BK : 0u) +
+                                  (INT8 ? 0u : scale_tiles * 512u + (dynamic_a ? 512u : 0u));
         const uint8_t* sfb_src[kScaleTilesB];
 #pragma unroll
         for (int i = 0; i < kScaleTilesB; ++i) {
@@ -390,12 +412,21 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 mbar_arrive_addr(bar);
               }
               if (load_a) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
-              if (load_b) tma_load_2d_addr(smem_b + s * kBBytes, &weight_map, bar, k0, n0);
+              if (load_b) {
+#pragma unroll
+                for (int part = 0; part < BN / kWeightBoxRows; ++part) {
+                  if (part < b_parts) {
+                    tma_load_2d_addr(smem_b + s * kBBytes + part * kWeightBoxRows * BK, &weight_map, bar, k0, n0 + part * kWeightBoxRows);
+                  }
+                }
+              }
               if (!INT8) {
                 const int w_tile = k0 >> 7;
 #pragma unroll
                 for (int i = 0; i < kScaleTilesB; ++i) {
-                  bulk_load_addr(smem_sfb + (s * kScaleTilesB + i) * 512, sfb_src[i] + static_cast<size_t>(w_tile) * 512, 512, bar);
+                  if (i < scale_tiles) {
+                    bulk_load_addr(smem_sfb + (s * kScaleTilesB + i) * 512, sfb_src[i] + static_cast<size_t>(w_tile) * 512, 512, bar);
+                  }
                 }
                 if (dynamic_a) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
               }
@@ -410,7 +441,6 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     if (lane == 0) {
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
-      const uint32_t idesc = INT8 ? idesc_i8(BN) : idesc_mxf8(BN);
       const int k_iters = taps * p.k_chunks;
       const bool copy_scales = !INT8 && !(p.debug & 8);
       if (!INT8 && !dynamic_a) {
@@ -426,6 +456,10 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         if (!mbar_wait_addr(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
+        int m_tile, n0, width;
+        decode_tile<BN>(p, tile, m_tile, n0, width);
+        const uint32_t idesc = INT8 ? idesc_i8(width) : idesc_mxf8(width);
+        const int scale_tiles = BN <= 128 ? 1 : width / 128;
         int j = 0;            // channel chunk within the tap
         uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
         for (int ki = 0; ki < k_iters; ++ki) {
@@ -445,7 +479,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           if (copy_scales) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
-              tc_copy_scales(sfb_tmem + 4 * i, sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4));
+              if (i < scale_tiles) {
+                tc_copy_scales(sfb_tmem + 4 * i, sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4));
+              }
             }
             if (dynamic_a) tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
           }
@@ -485,12 +521,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_it) {
-      const int nt = tile % p.tiles_n;
-      int m = tile / p.tiles_n;
+      int m, n0, width;
+      decode_tile<BN>(p, tile, m, n0, width);
+      const int n_end = min(p.cout, n0 + width);  // columns of this tile that exist
       const int tx = m % p.tiles_x; m /= p.tiles_x;
       const int ty = m % p.tiles_y;
       const int b = m / p.tiles_y;
-      const int x0 = tx * p.tile_w, y0 = ty * p.tile_h, n0 = nt * BN;
+      const int x0 = tx * p.tile_w, y0 = ty * p.tile_h;
       const int x = x0 + rx, y = y0 + ry;
       const bool valid = row_in_tile && x < p.out_w && y < p.out_h;
       const size_t pixel = (static_cast<size_t>(b) * p.out_h + y) * p.out_w + x;
@@ -546,7 +583,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           tmem_load_32(lane_addr + g * 32, raw);
           tmem_load_wait();
           if (g + 1 == kChunksPerWarp) release_accumulator();
-          if (n >= p.cout) continue;  // uniform over the four warps of this group
+          if (n >= n_end) continue;  // uniform over the four warps of this group
           wide_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, w);
           const uint32_t panel = take_panel();
           stage_row<32>(panel, row, p.out_elem, w);
@@ -561,12 +598,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           tmem_load_32(lane_addr + g * 32, raw);
           tmem_load_wait();
           if (g + 1 == kChunksPerWarp) release_accumulator();
-          if (n < p.cout) round_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, q[g]);
+          if (n < n_end) round_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, q[g]);
         }
 #pragma unroll
         for (int g = 0; g < kChunksPerWarp; ++g) {
           const int n = n0 + group * kGroupColumns + g * 32;
-          if (n >= p.cout) continue;  // uniform over the four warps of this group
+          if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
           finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, w);
           const uint32_t panel = take_panel();
@@ -750,6 +787,16 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.kh = g->kh, p.kw = g->kw, p.pad_h = g->pad_h, p.pad_w = g->pad_w, p.dil_h = g->dil_h, p.dil_w = g->dil_w;
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
   p.total_tiles = pl.total_tiles;
+  p.full_tiles = pl.total_tiles;
+  if (pl.block_n == 256 && pl.total_tiles > pl.ctas) {
+    // the last round of the persistent CTAs: when at most half of them would have a tile, two half-width tiles each
+    // finish it in half the time
+    const int rest = pl.total_tiles % pl.ctas;
+    if (rest > 0 && 2 * rest <= pl.ctas && !(g_debug_flags & 16)) {
+      p.full_tiles = pl.total_tiles - rest;
+      p.total_tiles = p.full_tiles + 2 * rest;
+    }
+  }
   p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages, p.panels_per_half = pl.panels_per_half;
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
@@ -792,7 +839,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     const uint64_t k_total = static_cast<uint64_t>(g->kh) * g->kw * g->cin;
     const uint64_t dims[2] = {k_total, static_cast<uint64_t>(g->cout)};
     const uint64_t strides[1] = {k_total};
-    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n)};
+    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n < 128 ? pl.block_n : 128)};
     const int rcm = make_tensor_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, dims, strides, box, swizzle_for_bytes(pl.block_k));
     if (rcm != kOk) return rcm;
   }
