@@ -457,10 +457,22 @@ DEFAULT_WORKLOAD = "stack"
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel, from the ncu
 # captures summarised under profiles/ (file named beside each figure); None where no capture exists.
-NCU_TRAFFIC: dict[str, float] = {}
+NCU_TRAFFIC: dict[str, float] = {
+    # conv_kernel 1x1 128 -> 256 + GELU + requant on 8 x 400 x 400 (the launch the stack's roofline times), same shape for
+    # every --pairs >= 4: profiles/conv_mxfp8_1x1_up_refiner_level_400x400x128.md (169.05 MB read + 284.43 MB written)
+    "refiner-stack": 453.48e6,
+    # profiles/conv_mxfp8_3x3_100x100x512.md (22.99 MB read; the 20 MB output is still in L2 when the kernel ends)
+    "mxfp8-conv-100x100x512-k3": 23.01e6,
+    # profiles/conv_int8_3x3_100x100x256.md
+    "int8-conv-100x100x256-k3": 5.80e6,
+    # profiles/depthwise_gelu_bf16_4x200x200x256.md (103.24 MB read + 38.44 MB written; the rest of the output in L2)
+    "depthwise5x5-gelu-4x200x200x256": 141.68e6,
+}
 
 
 def _traffic(name: str):
+    if name.startswith("refiner-stack"):
+        return NCU_TRAFFIC["refiner-stack"]
     return NCU_TRAFFIC.get(name)
 
 

@@ -6,13 +6,14 @@
 // out-of-image part TMA fills with zeros: the conv padding, no im2col buffer) and the weight tile into a ring of
 // swizzled K-major stages, plus the 512-byte scale tiles. Warp 1 issues tcgen05.mma from one lane, accumulating in
 // tensor memory; scale tiles go shared memory -> tensor memory with tcgen05.cp in front of the MMAs that use them, into
-// two alternating column sets so a copy never waits for the MMAs of the stage before. Warps 2-9 are the epilogue: two
-// warps per 32-lane quarter of tensor memory, each owning half of the BN columns. They tcgen05.ld 32 columns at a
-// time, apply bias / bf16 rounding / activation / residual / requantisation in registers, write the 32-column panel of
-// the tile into swizzled shared memory and hand it to a TMA store, which clips the ragged image edge. Accumulators are
-// double-buffered in tensor memory when two of them fit, so the epilogue of tile i overlaps the main loop of tile i + 1.
-// The producer and MMA loops keep stage addresses, descriptors and phase bits in registers: a single lane issues them
-// and every instruction there is on the critical path of the tensor pipe.
+// the stage's own column set, so a copy never waits for the MMAs of another stage. Warps 2-17 are the epilogue: four
+// column groups of four warps, one per 32-lane quarter of tensor memory. They tcgen05.ld 32 columns at a time, add the
+// bias, round to bf16x2 words and hand the accumulator back at once; activation / residual / requantisation then run on
+// packed pairs in registers, the 32-column panel of the tile goes to swizzled shared memory and on to a TMA store,
+// which clips the ragged image edge. Accumulators are double-buffered in tensor memory when two of them fit, so the
+// epilogue of tile i overlaps the main loop of tile i + 1. The producer and MMA loops keep stage addresses, descriptors
+// and phase bits in registers: a single lane issues them and every instruction there is on the critical path of the
+// tensor pipe.
 //
 // Rounding points follow FlashIM's torch reference: flashim/ops/conv.py:174-206,309-342 and flashim/ops/gemm.py:58-98.
 #include "common.cuh"

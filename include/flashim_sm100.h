@@ -78,7 +78,7 @@ int fim_quantize_int8_static(const void* value, int dtype, const float* scale, v
 
 /* out[b,y,x,c] = act(sum_{ky,kx} value[b,y+ky-2,x+kx-2,c] * weight[ky*5+kx, c] + bias[c]) with fp32 accumulation
  * over bf16 inputs, written as bf16 NHWC. `value` bf16 NHWC, `weight` bf16 [25, C] (tap-major), `bias` fp32 [C].
- * C must be a multiple of 64. Extension of the reference's depthwise producers (which always end in a quantiser):
+ * C must be a multiple of 32. Extension of the reference's depthwise producers (which always end in a quantiser):
  * same operands and arithmetic as flashim/ops/conv.py:30-41. */
 int fim_dw5x5_bf16(const void* value, const void* weight, const float* bias, void* out, int batch, int height, int width,
                    int channels, int act, int* status, void* stream);
