@@ -48,6 +48,16 @@ def check_status(device: torch.device | str | None = None) -> None:
         raise RuntimeError(f"sm100 kernel gave up waiting: {_native.STATUS.get(code, hex(code))}; outputs are invalid")
 
 
+def _swizzled_scale_buffer(rows: int, groups: int, device) -> Tensor:
+    """Byte buffer of the swizzled E8M0 layout. Its padding (rows up to a multiple of 128, groups up to a multiple of 4) is
+    zero like the reference's ``swizzle_scales``; a kernel writes every other byte, so a buffer without padding needs no
+    fill."""
+    size = swizzled_scale_bytes(rows, groups)
+    if rows % 128 == 0 and groups % 4 == 0:
+        return torch.empty(size, device=device, dtype=torch.uint8)
+    return torch.zeros(size, device=device, dtype=torch.uint8)
+
+
 def _stream(t: Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -97,7 +107,7 @@ def dw5x5_mxfp8(pixels: Tensor, weight: Tensor, bias: Tensor, act: int, swizzled
     rows = b * h * w
     out = torch.empty((rows, c), device=pixels.device, dtype=E4M3)
     if swizzled:
-        scales = torch.zeros(swizzled_scale_bytes(rows, c // BLOCK), device=pixels.device, dtype=torch.uint8)
+        scales = _swizzled_scale_buffer(rows, c // BLOCK, pixels.device)
     else:
         scales = torch.empty((rows, c // BLOCK), device=pixels.device, dtype=torch.uint8)
     code = _native.library().fim_dw5x5_mxfp8(
@@ -157,7 +167,7 @@ def quantize_mxfp8_dynamic(value: Tensor, swizzled: bool) -> tuple[Tensor, Tenso
     rows = value.numel() // channels
     out = torch.empty(value.shape, device=value.device, dtype=E4M3)
     if swizzled:
-        scales = torch.zeros(swizzled_scale_bytes(rows, channels // BLOCK), device=value.device, dtype=torch.uint8)
+        scales = _swizzled_scale_buffer(rows, channels // BLOCK, value.device)
     else:
         scales = torch.empty((rows, channels // BLOCK), device=value.device, dtype=torch.uint8)
     code = _native.library().fim_quantize_mxfp8_dynamic(
@@ -231,7 +241,7 @@ def mxfp8_conv2d_launch(
     ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
     out = torch.empty((b, ho, wo, cout), device=x.device, dtype=_OUT_DTYPES[out_mode])
     if out_mode == _native.OUT_E4M3_DYNAMIC:
-        out_scales = torch.zeros(swizzled_scale_bytes(b * ho * wo, cout // BLOCK), device=x.device, dtype=torch.uint8)
+        out_scales = _swizzled_scale_buffer(b * ho * wo, cout // BLOCK, x.device)
     else:
         out_scales = torch.empty(0, device=x.device, dtype=torch.uint8)
     geometry = _geometry(x, cout, kh, kw, ph, pw, dh, dw)

@@ -332,6 +332,29 @@ __device__ __forceinline__ int int8_code(float value, float scale) {
   return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
 }
 
+// The same code for many values under one scale, arranged for issue slots. With inv = RN(1 / scale), the product
+// value * inv corrected once by its fma residual is within two ulp of the true quotient; the IEEE division is only needed
+// where that estimate lies within 1e-4 of a rounding boundary (k + 0.5), which is where two ulp at |q| <= 128 could
+// change the integer. Everything else (about 9998 values in 10000) takes three fp32 operations instead of a division.
+struct Int8Quantizer {
+  float scale, inv;
+  bool exact_only;
+};
+__device__ __forceinline__ Int8Quantizer make_int8_quantizer(float s) {
+  Int8Quantizer q;
+  q.scale = s;
+  q.inv = __frcp_rn(s);
+  q.exact_only = !(fabsf(s) >= 1e-30f && fabsf(s) <= 1e30f);  // reciprocal of a tiny, huge or non-finite scale: divide
+  return q;
+}
+__device__ __forceinline__ int int8_code(const Int8Quantizer& z, float value) {
+  float q = value * z.inv;
+  q = fmaf(fmaf(-q, z.scale, value), z.inv, q);
+  float n = rintf(q);
+  if (z.exact_only || fabsf(fabsf(q - n) - 0.5f) < 1e-4f || !(fabsf(q) < 1e6f)) n = rintf(__fdiv_rn(value, z.scale));
+  return static_cast<int>(fminf(fmaxf(n, -127.0f), 127.0f));
+}
+
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }

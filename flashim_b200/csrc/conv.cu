@@ -218,13 +218,13 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[
     return;
   }
   if (INT8) {  // FIM_OUT_INT8
-    const float scale = __ldg(p.out_scale);
+    const Int8Quantizer quantizer = make_int8_quantizer(__ldg(p.out_scale));
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t q0 = static_cast<uint32_t>(int8_code(bf16_lo(r[2 * i]), scale)) & 0xFFu;
-      const uint32_t q1 = static_cast<uint32_t>(int8_code(bf16_hi(r[2 * i]), scale)) & 0xFFu;
-      const uint32_t q2 = static_cast<uint32_t>(int8_code(bf16_lo(r[2 * i + 1]), scale)) & 0xFFu;
-      const uint32_t q3 = static_cast<uint32_t>(int8_code(bf16_hi(r[2 * i + 1]), scale)) & 0xFFu;
+      const uint32_t q0 = static_cast<uint32_t>(int8_code(quantizer, bf16_lo(r[2 * i]))) & 0xFFu;
+      const uint32_t q1 = static_cast<uint32_t>(int8_code(quantizer, bf16_hi(r[2 * i]))) & 0xFFu;
+      const uint32_t q2 = static_cast<uint32_t>(int8_code(quantizer, bf16_lo(r[2 * i + 1]))) & 0xFFu;
+      const uint32_t q3 = static_cast<uint32_t>(int8_code(quantizer, bf16_hi(r[2 * i + 1]))) & 0xFFu;
       w[i] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
     }
     return;

@@ -56,7 +56,7 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v) {
 // index in the batch; `cols_ok` has bit j set when column x0 + j exists (0 for a lane without channels).
 template <int MODE, int ACT>
 __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, void* out_row,
-                                         size_t pixel0, int c, uint32_t cols_ok, float int8_scale) {
+                                         size_t pixel0, int c, uint32_t cols_ok, const Int8Quantizer& int8) {
   const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
   uint64_t v[kCols];
 #pragma unroll
@@ -120,7 +120,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     for (int j = 0; j < kCols; ++j) {
       float lo, hi;
       unpack2(v[j], lo, hi);
-      const int qlo = int8_code(bf16_round(lo), int8_scale), qhi = int8_code(bf16_round(hi), int8_scale);
+      const int qlo = int8_code(int8, bf16_round(lo)), qhi = int8_code(int8, bf16_round(hi));
       if (cols_ok & (1u << j)) out[j * pair_stride] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
     }
   }
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
     }
   } else if (u_end > u_begin) {
     // ===== consumers =====
-    const float int8_scale = MODE == kOutInt8 ? __ldg(p.scale) : 1.0f;
+    const Int8Quantizer int8_scale = make_int8_quantizer(MODE == kOutInt8 ? __ldg(p.scale) : 1.0f);
     const uint32_t lane_smem = smem0 + (warp * kCols * (kChannels / 2) + lane) * 4;
     constexpr int kOutBytes = MODE == kOutBf16 ? 4 : 2;  // per channel pair
     const size_t pair_stride = static_cast<size_t>(p.channels >> 1);

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kThreads) quantize_mx_dynamic_kernel(const T* 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) quantize_int8_kernel(const T* __restrict__ in, const float* __restrict__ scale_ptr,
                                                                  int8_t* __restrict__ out, long long count) {
-  const float scale = __ldg(scale_ptr);
+  const Int8Quantizer quantizer = make_int8_quantizer(__ldg(scale_ptr));
   const long long chunks = count / 16;
   for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < chunks;
        i += static_cast<long long>(gridDim.x) * kThreads) {
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(kThreads) quantize_int8_kernel(const T* __rest
     for (int j = 0; j < 4; ++j) {
       uint32_t w = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) w |= (static_cast<uint32_t>(int8_code(v[4 * j + k], scale)) & 0xFFu) << (8 * k);
+      for (int k = 0; k < 4; ++k) w |= (static_cast<uint32_t>(int8_code(quantizer, v[4 * j + k])) & 0xFFu) << (8 * k);
       q[j] = w;
     }
     *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(q[0], q[1], q[2], q[3]);
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(kThreads) quantize_int8_kernel(const T* __rest
   // tail shorter than one chunk
   const long long done = chunks * 16;
   if (blockIdx.x == 0 && threadIdx.x < count - done) {
-    out[done + threadIdx.x] = static_cast<int8_t>(int8_code(static_cast<float>(in[done + threadIdx.x]), scale));
+    out[done + threadIdx.x] = static_cast<int8_t>(int8_code(quantizer, static_cast<float>(in[done + threadIdx.x])));
   }
 }
 
