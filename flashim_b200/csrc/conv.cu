@@ -25,7 +25,7 @@ namespace {
 constexpr int kThreads = 576;  // producer warp, MMA warp, 16 epilogue warps
 constexpr int kTileM = 128;
 constexpr uint32_t kTmemColumns = 512;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;  // a short K loop is bound by the latency of a stage's round trip: more stages in flight
 constexpr int kSmemLimit = 226 * 1024;
 
 struct ConvParams {
@@ -312,7 +312,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_a = base;
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + p.stages * kBBytes;
-  const uint32_t smem_sfb = smem_out + 4 * p.panels_per_half * panel_bytes;
+  const uint32_t smem_sfb = smem_out + kEpiGroups * p.panels_per_half * panel_bytes;
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
@@ -708,7 +708,8 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_tiles_b(bn) * 512 + 512;
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
-  const int fixed = 1024 + 4 * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes;
+  const int epilogue_groups = bn >= 128 ? 4 : 2;
+  const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;

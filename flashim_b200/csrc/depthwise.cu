@@ -120,7 +120,8 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     for (int j = 0; j < kCols; ++j) {
       float lo, hi;
       unpack2(v[j], lo, hi);
-      const int qlo = int8_code(int8, bf16_round(lo)), qhi = int8_code(int8, bf16_round(hi));
+      const uint32_t rounded = pack_bf16(lo, hi);  // one packed conversion instead of two scalar ones
+      const int qlo = int8_code(int8, bf16_lo(rounded)), qhi = int8_code(int8, bf16_hi(rounded));
       if (cols_ok & (1u << j)) out[j * pair_stride] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
     }
   }
