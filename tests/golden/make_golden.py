@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = os.environ.get("FLASHIM_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("FLASHIM_REFERENCE") or str(Path(__file__).resolve().parents[3] / "reference")  # a FlashIM checkout
 sys.path.insert(0, REFERENCE)
 
 from flashim import ops  # noqa: E402

@@ -7,7 +7,8 @@ import sys
 import pytest
 import torch
 
-reference = os.environ.get("FLASHIM_REFERENCE", "/root/reference")
+# a FlashIM checkout: $FLASHIM_REFERENCE, else a directory "reference" beside this repository
+reference = os.environ.get("FLASHIM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 if os.path.isdir(os.path.join(reference, "flashim")) and reference not in sys.path:
     sys.path.append(reference)  # behind this repository, whose `tests` package must keep winning
 flashim = pytest.importorskip("flashim")
