@@ -108,12 +108,15 @@ __device__ __forceinline__ bool mbar_try_addr(uint32_t bar, uint32_t parity) {
 }
 // `heed_abort` = false: only this wait's own time limit ends it. Warps that meet at a named barrier afterwards use it, so
 // that all of them take the same decision (either the phase completes for all or it times out for all).
+// `backoff_ns` > 0 sleeps that long between polls: a warp that expects to wait for microseconds (an epilogue warp during
+// the main loop of its tile) then leaves the issue slots and the power budget to the warps that are working.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
-                                            bool heed_abort) {
+                                            bool heed_abort, uint32_t backoff_ns) {
   const uint64_t start = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_addr(bar, parity)) return true;
+    if (backoff_ns != 0) __nanosleep(backoff_ns);
     if ((++spins & 31u) == 0u) {
       if (heed_abort && *abort_flag) return false;
       if (global_timer_ns() - start > kWaitLimitNs) {
@@ -125,10 +128,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
   }
 }
 __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
-                                               bool heed_abort = true) {
+                                               bool heed_abort = true, uint32_t backoff_ns = 0) {
   if (mbar_try_addr(bar, parity)) return true;
   if (mbar_try_addr(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, code, heed_abort);
+  return mbar_wait_slow(bar, parity, abort_flag, status, code, heed_abort, backoff_ns);
 }
 __device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -177,6 +180,37 @@ __device__ __forceinline__ void bulk_load_addr(uint32_t dst, const void* src, ui
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
       : "memory");
 }
+// ---- CTA pairs (a cluster of two CTAs driving one cta_group::2 tensor-core instruction stream) ------------------------
+// Shared-memory addresses of the odd CTA of a pair carry this bit in the cluster's shared address space; clearing it
+// names the same location in the even (leader) CTA, setting it the one in the odd CTA.
+constexpr uint32_t kPeerBit = 1u << 24;
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tiled loads of a CTA pair: the bytes land in this CTA's shared memory and are counted on the barrier `bar`, which may
+// live in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// One arrival on a barrier anywhere in the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // Tiled store shared -> global (clipped at the tensor bounds), tracked by the thread's bulk async-group.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -210,15 +244,53 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
 }
+// The same for a CTA pair: one warp (the same warp index) of each CTA of the pair executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot_in_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // All tcgen05 operations this thread issued so far arrive on `bar` when they complete.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Pair form, issued by the leader CTA: arrives on the barrier at cluster address `bar` (either CTA of the pair) when the
+// pair's tcgen05 operations issued so far complete.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 // 32 rows x 16 bytes of shared memory -> 4 tensor-memory columns, replicated into the four 32-lane quarters.
 __device__ __forceinline__ void tc_copy_scales(uint32_t tmem_addr, uint64_t smem_desc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
+}
+// Pair forms (issued by the leader): each CTA copies from its own shared memory into its own tensor memory; the MMA has
+// M = 256 (128 rows per CTA), reads A and its half of B from each CTA's shared memory at the same offsets.
+__device__ __forceinline__ void tc_copy_scales_pair(uint32_t tmem_addr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf8_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 __device__ __forceinline__ void tc_mma_mxf8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
   asm volatile(

@@ -32,6 +32,7 @@ struct ConvParams {
   int cin, cout, out_h, out_w;
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
+  int batch;       // images (rows of a flattened 1x1 conv count as one)
   int full_tiles;  // tiles [0, full_tiles) are BN wide; the rest are the halves (BN / 2 columns) of the last few tiles
   int k_chunks, stages;
   int panels_per_half;  // output panels each column group of the epilogue rotates through (1 or 2)
@@ -71,14 +72,15 @@ __host__ __device__ constexpr int acc_stages(int bn) {
 }
 __host__ __device__ constexpr int scale_tiles_b(int bn) { return bn <= 128 ? 1 : bn / 128; }
 
-__device__ __forceinline__ uint32_t idesc_mxf8(int block_n) {
-  // E4M3 x E4M3 (format 0), both K-major, UE8M0 scales, M = 128, N = block_n; scale ids are OR-ed in per MMA
-  return (static_cast<uint32_t>(block_n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+__device__ __forceinline__ uint32_t idesc_mxf8(int block_n, int block_m = kTileM) {
+  // E4M3 x E4M3 (format 0), both K-major, UE8M0 scales, M = block_m (256 for a CTA pair), N = block_n; scale ids are
+  // OR-ed in per MMA
+  return (static_cast<uint32_t>(block_n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(block_m >> 4) << 24);
 }
-__device__ __forceinline__ uint32_t idesc_i8(int block_n) {
-  // S32 accumulator (2), signed 8-bit A and B (1), both K-major, M = 128, N = block_n
+__device__ __forceinline__ uint32_t idesc_i8(int block_n, int block_m = kTileM) {
+  // S32 accumulator (2), signed 8-bit A and B (1), both K-major, M = block_m, N = block_n
   return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(block_n >> 3) << 17) |
-         (static_cast<uint32_t>(kTileM >> 4) << 24);
+         (static_cast<uint32_t>(block_m >> 4) << 24);
 }
 
 // ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
@@ -286,14 +288,22 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
   }
 }
 
-template <bool INT8, int BN, int BK>
+// PAIR: the kernel runs as clusters of two CTAs that share one tcgen05 instruction stream (cta_group::2): a pair owns
+// 256 pixels (128 per CTA) x BN channels, each CTA loads its own pixels and half of the weight rows, the even CTA (the
+// leader) issues M = 256 MMAs that read both halves, and each CTA drains its own 128 accumulator rows. A CTA then moves
+// 2/3 of the operand bytes per MMA through its shared memory, which is what bounds the single-CTA form. Barriers: the
+// stage's "full" barrier lives in the leader and counts both CTAs' bytes; "empty" and "accumulator full" exist in both
+// CTAs and the leader's commits arrive on both; "accumulator empty" lives in the leader and collects both epilogues.
+template <bool INT8, int BN, int BK, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
-            const __grid_constant__ CUtensorMap out_map, const ConvParams p) {
+            const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
+            const __grid_constant__ CUtensorMap sfa_map, const ConvParams p) {
+  static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
   constexpr int kAccStages = acc_stages(BN);
   constexpr int kScaleTilesB = scale_tiles_b(BN);
   constexpr int kKSteps = BK / 32;
-  constexpr uint32_t kABytes = kTileM * BK, kBBytes = BN * BK;
+  constexpr uint32_t kABytes = kTileM * BK, kBBytes = (PAIR ? BN / 2 : BN) * BK;  // per CTA
   constexpr int kWeightBoxRows = BN < 128 ? BN : 128;  // rows of one weight TMA box
   constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
   constexpr uint32_t kSfbColumn = kAccStages * BN;                        // one set of kSfbColumns per stage
@@ -320,6 +330,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dynamic_a = !INT8 && p.act_scales != nullptr;
   const int taps = p.kh * p.kw;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                   // 0: the CTA that issues the MMAs
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);  // tile walker index
+  const int workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -329,7 +342,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl.tmem_full[s], 1);
-      mbar_init(&ctl.tmem_empty[s], 4 * kEpiGroups);
+      mbar_init(&ctl.tmem_empty[s], (PAIR ? 2 : 1) * 4 * kEpiGroups);
     }
     mbar_fence_init();
     tma_prefetch_desc(&act_map);
@@ -337,8 +350,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     tma_prefetch_desc(&out_map);
   }
   if (warp == 1) {
-    tmem_alloc(&ctl.tmem_base, kTmemColumns);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(&ctl.tmem_base, kTmemColumns);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&ctl.tmem_base, kTmemColumns);
+      tmem_relinquish();
+    }
   }
   if (warp == 2 && !INT8 && !dynamic_a) {
     // static activation scales: one 512-byte tile per 128 input channels, the same 4 bytes in all 128 rows
@@ -364,6 +382,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();  // the other CTA's barriers and static scale tiles exist before anything refers to them
   tc_fence_after();
   const uint32_t tmem = ctl.tmem_base;
   const uint32_t full0 = smem_u32(&ctl.full[0]), empty0 = smem_u32(&ctl.empty[0]);
@@ -377,19 +396,22 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
       uint32_t s = 0, phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x) {
+      for (int tile = worker; tile < p.total_tiles && alive; tile += workers) {
         int m_tile, n0, width;
         decode_tile<BN>(p, tile, m_tile, n0, width);
+        if (PAIR) m_tile = 2 * m_tile + static_cast<int>(rank);  // a pair owns two consecutive row tiles
         int m = m_tile;
         const int tx = m % p.tiles_x; m /= p.tiles_x;
         const int ty = m % p.tiles_y;
         const int b = m / p.tiles_y;
         const int x0 = tx * p.tile_w - p.pad_w, y0 = ty * p.tile_h - p.pad_h;
         // the weight tile arrives in boxes of kWeightBoxRows rows (a 256-wide tile is two boxes, its half one)
-        const int b_parts = width / kWeightBoxRows;
+        const int b_parts = PAIR ? 1 : width / kWeightBoxRows;
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
-        const uint32_t tx_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? static_cast<uint32_t>(width) * BK : 0u) +
-                                  (INT8 ? 0u : scale_tiles * 512u + (dynamic_a ? 512u : 0u));
+        // a pair's barrier (in the leader) counts the bytes of both CTAs, which load the same amounts
+        const uint32_t tx_bytes = (PAIR ? 2u : 1u) * ((load_a ? a_box_bytes : 0u) +
+                                                      (load_b ? static_cast<uint32_t>(PAIR ? width / 2 : width) * BK : 0u) +
+                                                      (INT8 ? 0u : scale_tiles * 512u + (dynamic_a ? 512u : 0u)));
         const uint8_t* sfb_src[kScaleTilesB];
 #pragma unroll
         for (int i = 0; i < kScaleTilesB; ++i) {
@@ -406,11 +428,32 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 alive = false;
                 break;
               }
-              const uint32_t bar = full0 + 8 * s;
-              if (tx_bytes != 0) {
-                mbar_expect_tx_addr(bar, tx_bytes);
-              } else {
-                mbar_arrive_addr(bar);
+              const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
+              if (!PAIR || rank == 0) {
+                if (tx_bytes != 0) {
+                  mbar_expect_tx_addr(full0 + 8 * s, tx_bytes);
+                } else {
+                  mbar_arrive_addr(full0 + 8 * s);
+                }
+              }
+              if (PAIR) {
+                if (load_a) tma_load_4d_pair(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
+                if (load_b) tma_load_2d_pair(smem_b + s * kBBytes, &weight_map, bar, k0, n0 + static_cast<int>(rank) * (BN / 2));
+                if (!INT8) {
+                  // scale tiles through their tensor maps (128 words of 4 bytes per tile): only a tiled load can count
+                  // on a barrier in the other CTA
+                  const int w_tile = k0 >> 7;
+#pragma unroll
+                  for (int i = 0; i < kScaleTilesB; ++i) {
+                    const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
+                    tma_load_2d_pair(smem_sfb + (s * kScaleTilesB + i) * 512, &sfb_map, bar, 0, row_tile * p.weight_scale_tiles + w_tile);
+                  }
+                  if (dynamic_a) {
+                    tma_load_2d_pair(smem_sfa + s * 512, &sfa_map, bar, 0, m_tile * p.act_scale_tiles + ((j * BK) >> 7));
+                  }
+                }
+                if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
+                continue;
               }
               if (load_a) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
               if (load_b) {
@@ -438,8 +481,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    // ===== MMA issuer =====
-    if (lane == 0) {
+    // ===== MMA issuer (of a pair: the leader CTA's) =====
+    if (lane == 0 && rank == 0) {
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
       const int k_iters = taps * p.k_chunks;
@@ -447,11 +490,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       if (!INT8 && !dynamic_a) {
         // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
         const int tiles = (p.cin + 127) / 128;
-        for (int t = 0; t < tiles; ++t) tc_copy_scales(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+        for (int t = 0; t < tiles; ++t) {
+          if (PAIR) {
+            tc_copy_scales_pair(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+          } else {
+            tc_copy_scales(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+          }
+        }
       }
       uint32_t s = 0, phase = 0, tile_it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && alive; tile += gridDim.x, ++tile_it) {
+      for (int tile = worker; tile < p.total_tiles && alive; tile += workers, ++tile_it) {
         const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
         const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
         if (!mbar_wait_addr(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
@@ -459,7 +508,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const uint32_t d_tmem = tmem + acc * BN;
         int m_tile, n0, width;
         decode_tile<BN>(p, tile, m_tile, n0, width);
-        const uint32_t idesc = INT8 ? idesc_i8(width) : idesc_mxf8(width);
+        const uint32_t idesc = INT8 ? idesc_i8(width, PAIR ? 256 : kTileM) : idesc_mxf8(width, PAIR ? 256 : kTileM);
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         int j = 0;            // channel chunk within the tap
         uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
@@ -474,17 +523,29 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           if (BK != 128) a_id = kb_a & 3;
           // scale tiles of this stage: shared memory -> the stage's own tensor-memory columns, in front of its MMAs (the
           // tensor pipe runs both in issue order; a column set is rewritten only after the MMAs that read it, a whole
-          // ring of stages earlier)
+          // ring of stages earlier). Issuing a stage's copies one stage early was measured: no gain, the pipe serialises
+          // copies and MMAs either way.
           const uint32_t sfb_tmem = tmem + kSfbColumn + kSfbColumns * s;
           const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * (dynamic_a ? s : (kb_a >> 2));
           if (copy_scales) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
               if (i < scale_tiles) {
-                tc_copy_scales(sfb_tmem + 4 * i, sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4));
+                const uint64_t from = sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4);
+                if (PAIR) {
+                  tc_copy_scales_pair(sfb_tmem + 4 * i, from);
+                } else {
+                  tc_copy_scales(sfb_tmem + 4 * i, from);
+                }
               }
             }
-            if (dynamic_a) tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
+            if (dynamic_a) {
+              if (PAIR) {
+                tc_copy_scales_pair(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
+              } else {
+                tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
+              }
+            }
           }
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
@@ -492,18 +553,39 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           for (int k = 0; k < kKSteps; ++k) {
             const uint32_t accumulate = (ki > 0 || k > 0) ? 1u : 0u;
             if (INT8) {
-              tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+              if (PAIR) {
+                tc_mma_i8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+              } else {
+                tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+              }
             } else {
-              tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc | ((a_id + k) << 29) | ((b_id + k) << 4), sfa_tmem,
-                          sfb_tmem, accumulate);
+              const uint32_t scaled = idesc | ((a_id + k) << 29) | ((b_id + k) << 4);
+              if (PAIR) {
+                tc_mma_mxf8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
+              } else {
+                tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
+              }
             }
           }
-          tc_commit(&ctl.empty[s]);  // the stage is free once these MMAs have read it
+          // the stage is free once these MMAs have read it (of a pair: in both CTAs)
+          if (PAIR) {
+            tc_commit_pair(empty0 + 8 * s);
+            tc_commit_pair((empty0 + 8 * s) | kPeerBit);
+          } else {
+            tc_commit(&ctl.empty[s]);
+          }
           if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
           if (++j == p.k_chunks) j = 0;
           if (BK != 128) b_id = (b_id + kKSteps) & 3;
         }
-        if (alive) tc_commit(&ctl.tmem_full[acc]);
+        if (alive) {
+          if (PAIR) {
+            tc_commit_pair(tfull0 + 8 * acc);
+            tc_commit_pair((tfull0 + 8 * acc) | kPeerBit);
+          } else {
+            tc_commit(&ctl.tmem_full[acc]);
+          }
+        }
       }
     }
   } else {
@@ -521,16 +603,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     const bool store = !(p.debug & 4);
     constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++tile_it) {
+    for (int tile = worker; tile < p.total_tiles; tile += workers, ++tile_it) {
       int m, n0, width;
       decode_tile<BN>(p, tile, m, n0, width);
+      if (PAIR) m = 2 * m + static_cast<int>(rank);
       const int n_end = min(p.cout, n0 + width);  // columns of this tile that exist
       const int tx = m % p.tiles_x; m /= p.tiles_x;
       const int ty = m % p.tiles_y;
       const int b = m / p.tiles_y;
       const int x0 = tx * p.tile_w, y0 = ty * p.tile_h;
       const int x = x0 + rx, y = y0 + ry;
-      const bool valid = row_in_tile && x < p.out_w && y < p.out_h;
+      const bool valid = row_in_tile && x < p.out_w && y < p.out_h && b < p.batch;
       const size_t pixel = (static_cast<size_t>(b) * p.out_h + y) * p.out_w + x;
       const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
       const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
@@ -543,7 +626,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                                                           n_first));
         }
       }
-      if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false)) break;
+      if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.debug & 32 ? 0u : 200u)) break;
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
       // Drain: every chunk of this warp is read, biased and rounded to bf16x2 words first (16 registers per chunk), and
@@ -574,7 +657,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       auto release_accumulator = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
+        if (lane == 0) {
+          if (PAIR) {
+            mbar_arrive_cluster((tempty0 + 8 * acc) & ~kPeerBit);  // the barrier the leader's MMA thread waits on
+          } else {
+            mbar_arrive_addr(tempty0 + 8 * acc);
+          }
+        }
       };
       if (wide) {
 #pragma unroll
@@ -624,9 +713,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();  // neither CTA leaves while the other may still touch its barriers or tensor memory
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTmemColumns);
+    if (PAIR) {
+      tmem_dealloc_pair(tmem, kTmemColumns);
+    } else {
+      tmem_dealloc(tmem, kTmemColumns);
+    }
   }
 }
 
@@ -640,6 +734,7 @@ struct Plan {
   int tile_h, tile_w, block_n, block_k, stages, ctas, panels_per_half;
   int tiles_x, tiles_y, tiles_n, total_tiles;
   bool flat;
+  bool pair;  // clusters of two CTAs driving one cta_group::2 instruction stream
   int out_h, out_w;
   size_t smem;
 };
@@ -697,15 +792,20 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
     pl.tiles_x = ceil_div(out_w, pl.tile_w), pl.tiles_y = ceil_div(out_h, pl.tile_h);
   }
   pl.tiles_n = ceil_div(g.cout, bn);
-  const long long total = static_cast<long long>(pl.tiles_x) * pl.tiles_y * (pl.flat ? 1 : g.batch) * pl.tiles_n;
-  if (total > 0x7fffffffLL) return kUnsupported;
+  const long long row_tiles = static_cast<long long>(pl.tiles_x) * pl.tiles_y * (pl.flat ? 1 : g.batch);
+  // CTA pairs for the wide, compute-bound INT8 tiles: a pair owns two consecutive row tiles (the last one may not exist:
+  // its loads are zero-filled and its stores clipped). The block-scaled form is correct too but measured slower than
+  // single CTAs (its scale copies serialise the pair's tensor pipes): it only runs when asked for (tuning flag 128).
+  pl.pair = bn == 256 && row_tiles >= 2 && !(g_debug_flags & 64) && (int8 || (g_debug_flags & 128));
+  const long long total = (pl.pair ? (row_tiles + 1) / 2 : row_tiles) * pl.tiles_n;
+  if (total > 0x3fffffffLL) return kUnsupported;
   pl.total_tiles = static_cast<int>(total);
   // shared memory: alignment slack + output panels + static activation-scale tiles + the stage ring. A layer with few
   // K iterations per tile is bound by its stores: it gets more panels in flight; a long main loop gets the stages.
   const int k_iters = g.kh * g.kw * (g.cin / pl.block_k);
   pl.panels_per_half = out_elem == 4 ? 1 : 2;  // 16 KB panels of a 4-byte output: one per column group
   (void)k_iters;
-  const int stage_bytes = kTileM * pl.block_k + bn * pl.block_k + scale_tiles_b(bn) * 512 + 512;
+  const int stage_bytes = kTileM * pl.block_k + (pl.pair ? bn / 2 : bn) * pl.block_k + scale_tiles_b(bn) * 512 + 512;
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
   const int epilogue_groups = bn >= 128 ? 4 : 2;
@@ -716,29 +816,54 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   pl.smem = static_cast<size_t>(fixed) + static_cast<size_t>(pl.stages) * stage_bytes;
   const int sms = g_max_ctas > 0 && g_max_ctas < 148 ? g_max_ctas : 148;
   pl.ctas = pl.total_tiles < sms ? pl.total_tiles : sms;
+  if (pl.pair) pl.ctas = 2 * (pl.total_tiles < sms / 2 ? pl.total_tiles : sms / 2);
   *plan = pl;
   return kOk;
 }
 
-template <bool INT8, int BN, int BK>
-int launch_conv(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& out_map, const ConvParams& p,
-                const Plan& pl, cudaStream_t stream) {
+struct ConvMaps {
+  CUtensorMap act, weight, out, sfb, sfa;
+};
+
+template <bool INT8, int BN, int BK, bool PAIR>
+int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(conv_kernel<INT8, BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    const cudaError_t e =
+        cudaFuncSetAttribute(conv_kernel<INT8, BN, BK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  conv_kernel<INT8, BN, BK><<<pl.ctas, kThreads, pl.smem, stream>>>(act_map, weight_map, out_map, p);
+  if (PAIR) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(pl.ctas), 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = pl.smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<INT8, BN, BK, PAIR>, maps.act, maps.weight, maps.out, maps.sfb,
+                                               maps.sfa, p));
+  }
+  conv_kernel<INT8, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, p);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <bool INT8, int BN>
-int launch_conv_k(const CUtensorMap& a, const CUtensorMap& w, const CUtensorMap& o, const ConvParams& p, const Plan& pl,
-                  cudaStream_t stream) {
-  if (pl.block_k == 128) return launch_conv<INT8, BN, 128>(a, w, o, p, pl, stream);
-  if (pl.block_k == 64) return launch_conv<INT8, BN, 64>(a, w, o, p, pl, stream);
-  return launch_conv<INT8, BN, 32>(a, w, o, p, pl, stream);
+int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
+  if constexpr (BN == 256) {
+    if (pl.pair) {
+      if (pl.block_k == 128) return launch_conv<INT8, BN, 128, true>(maps, p, pl, stream);
+      if (pl.block_k == 64) return launch_conv<INT8, BN, 64, true>(maps, p, pl, stream);
+      return launch_conv<INT8, BN, 32, true>(maps, p, pl, stream);
+    }
+  }
+  if (pl.block_k == 128) return launch_conv<INT8, BN, 128, false>(maps, p, pl, stream);
+  if (pl.block_k == 64) return launch_conv<INT8, BN, 64, false>(maps, p, pl, stream);
+  return launch_conv<INT8, BN, 32, false>(maps, p, pl, stream);
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
@@ -790,7 +915,8 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
   p.total_tiles = pl.total_tiles;
   p.full_tiles = pl.total_tiles;
-  if (pl.block_n == 256 && pl.total_tiles > pl.ctas) {
+  p.batch = pl.flat ? 1 : g->batch;
+  if (pl.block_n == 256 && !pl.pair && pl.total_tiles > pl.ctas) {
     // the last round of the persistent CTAs: when at most half of them would have a tile, two half-width tiles each
     // finish it in half the time
     const int rest = pl.total_tiles % pl.ctas;
@@ -827,7 +953,10 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     p.out_h = 1, p.out_w = static_cast<int>(o_w);
     if (p.residual != nullptr) p.res_stride[0] = 0, p.res_stride[1] = 0;  // dense: the flat column index addresses it
   }
-  CUtensorMap act_map, weight_map, out_map;
+  ConvMaps maps;
+  CUtensorMap& act_map = maps.act;
+  CUtensorMap& weight_map = maps.weight;
+  CUtensorMap& out_map = maps.out;
   {
     const uint64_t dims[4] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w), static_cast<uint64_t>(in_h),
                               static_cast<uint64_t>(in_b)};
@@ -841,7 +970,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     const uint64_t k_total = static_cast<uint64_t>(g->kh) * g->kw * g->cin;
     const uint64_t dims[2] = {k_total, static_cast<uint64_t>(g->cout)};
     const uint64_t strides[1] = {k_total};
-    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n < 128 ? pl.block_n : 128)};
+    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n < 128 ? pl.block_n : 128)};  // a pair's CTA loads 128 rows too
     const int rcm = make_tensor_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, dims, strides, box, swizzle_for_bytes(pl.block_k));
     if (rcm != kOk) return rcm;
   }
@@ -854,15 +983,31 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     if (rcm != kOk) return rcm;
   }
 
+  // scale tiles as tensors of 128 four-byte words per 512-byte tile: the loads of a CTA pair go through these
+  maps.sfb = act_map, maps.sfa = act_map;
+  if (pl.pair && !int8) {
+    const uint64_t dims[2] = {128, static_cast<uint64_t>(p.weight_row_tiles) * p.weight_scale_tiles};
+    const uint64_t strides[1] = {512};
+    const uint32_t box[2] = {128, 1};
+    const int rcm = make_tensor_map(&maps.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, weight_scales, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rcm != kOk) return rcm;
+    if (act_scales != nullptr) {
+      const long long pixel_rows = static_cast<long long>(g->batch) * g->height * g->width;
+      const uint64_t adims[2] = {128, static_cast<uint64_t>((pixel_rows + 127) / 128) * p.act_scale_tiles};
+      const int rca = make_tensor_map(&maps.sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, act_scales, adims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rca != kOk) return rca;
+    }
+  }
+
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int8) {
-    if (pl.block_n == 64) return launch_conv_k<true, 64>(act_map, weight_map, out_map, p, pl, s);
-    if (pl.block_n == 128) return launch_conv_k<true, 128>(act_map, weight_map, out_map, p, pl, s);
-    return launch_conv_k<true, 256>(act_map, weight_map, out_map, p, pl, s);
+    if (pl.block_n == 64) return launch_conv_k<true, 64>(maps, p, pl, s);
+    if (pl.block_n == 128) return launch_conv_k<true, 128>(maps, p, pl, s);
+    return launch_conv_k<true, 256>(maps, p, pl, s);
   }
-  if (pl.block_n == 64) return launch_conv_k<false, 64>(act_map, weight_map, out_map, p, pl, s);
-  if (pl.block_n == 128) return launch_conv_k<false, 128>(act_map, weight_map, out_map, p, pl, s);
-  return launch_conv_k<false, 256>(act_map, weight_map, out_map, p, pl, s);
+  if (pl.block_n == 64) return launch_conv_k<false, 64>(maps, p, pl, s);
+  if (pl.block_n == 128) return launch_conv_k<false, 128>(maps, p, pl, s);
+  return launch_conv_k<false, 256>(maps, p, pl, s);
 }
 
 }  // namespace

@@ -141,7 +141,10 @@ int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scale
 
 /* Tuning and measurement hooks for the following conv launches of this process (all 0 = automatic / off):
  * `block_n` forces the output-channel tile (64 / 128 / 256); `max_ctas` caps the persistent grid; `debug_flags` is for
- * timing experiments only and makes results invalid (1: skip activation loads, 2: skip weight loads, 4: skip stores, 8: skip scale copies). */
+ * timing experiments: bits 1, 2, 4, 8 make results invalid (skip activation loads / weight loads / stores / scale copies);
+ * 16 keeps the last partial round of tiles at full width, 32 makes the epilogue warps poll without back-off, 64 disables
+ * CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; default for INT8 with 256-wide tiles), 128
+ * enables them for MXFP8 too. Results stay valid under 16-128. */
 void fim_conv_tune(int block_n, int max_ctas, int debug_flags);
 
 #ifdef __cplusplus
