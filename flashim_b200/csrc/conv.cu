@@ -32,9 +32,12 @@ struct ConvParams {
   int cin, cout, out_h, out_w;
   int kh, kw, pad_h, pad_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
+  int row_tiles;   // row tiles (of a CTA pair: pairs of them) per output-channel tile
+  int n_major;     // tile order: 1 = all row tiles of an output-channel tile before the next (keeps weight scales resident)
   int batch;       // images (rows of a flattened 1x1 conv count as one)
   int full_tiles;  // tiles [0, full_tiles) are BN wide; the rest are the halves (BN / 2 columns) of the last few tiles
   int k_chunks, stages;
+  int resident_k;  // weight-scale tiles of the first resident_k K iterations stay in tensor memory from tile to tile
   int panels_per_half;  // output panels each column group of the epilogue rotates through (1 or 2)
   // scales (MXFP8)
   const int8_t* act_exponent;     // static: [cin / 32]
@@ -275,17 +278,23 @@ __device__ __forceinline__ void stage_row(uint32_t panel, int row, int elem, con
 // split into two half-width tiles each when that lets the round finish in half the time (the host decides: full_tiles).
 template <int BN>
 __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& m_tile, int& n0, int& width) {
-  if (tile < p.full_tiles) {
-    m_tile = tile / p.tiles_n;
-    n0 = (tile - m_tile * p.tiles_n) * BN;
-    width = BN;
-  } else {
+  int whole = tile, half = 0;
+  width = BN;
+  if (tile >= p.full_tiles) {
     const int h = tile - p.full_tiles;
-    const int whole = p.full_tiles + (h >> 1);
-    m_tile = whole / p.tiles_n;
-    n0 = (whole - m_tile * p.tiles_n) * BN + (h & 1) * (BN / 2);
+    whole = p.full_tiles + (h >> 1);
+    half = h & 1;
     width = BN / 2;
   }
+  int nt;
+  if (p.n_major) {
+    nt = whole / p.row_tiles;
+    m_tile = whole - nt * p.row_tiles;
+  } else {
+    m_tile = whole / p.tiles_n;
+    nt = whole - m_tile * p.tiles_n;
+  }
+  n0 = nt * BN + half * (BN / 2);
 }
 
 // PAIR: the kernel runs as clusters of two CTAs that share one tcgen05 instruction stream (cta_group::2): a pair owns
@@ -307,8 +316,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   constexpr int kWeightBoxRows = BN < 128 ? BN : 128;  // rows of one weight TMA box
   constexpr uint32_t kSfbColumns = BN < 128 ? 4 : BN / 32;
   constexpr uint32_t kSfbColumn = kAccStages * BN;                        // one set of kSfbColumns per stage
-  constexpr uint32_t kSfaColumn = kSfbColumn + kMaxStages * kSfbColumns;  // static scales: 4 columns per 128 input channels,
-                                                                          // copied once; per-pixel scales: 4 columns per stage
+  // then the activation scales (static: 4 columns per 128 input channels, copied once; per-pixel: 4 columns per stage),
+  // then the resident weight scales (kSfbColumns per K iteration, kept while consecutive tiles share their channels)
+  const uint32_t sfa_column = kSfbColumn + static_cast<uint32_t>(p.stages) * kSfbColumns;
+  const uint32_t resident_column =
+      sfa_column + 4u * static_cast<uint32_t>(!INT8 && p.act_scales != nullptr ? p.stages : (p.cin + 127) / 128);
   constexpr int kEpiGroups = BN >= 128 ? 4 : 2;          // column groups of the epilogue, four warps (one per lane quarter) each
   constexpr int kChunksPerWarp = BN / (32 * kEpiGroups); // 32-column chunks each epilogue warp owns
 
@@ -396,6 +408,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
       uint32_t s = 0, phase = 0;
       bool alive = true;
+      int last_n0 = -1;
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers) {
         int m_tile, n0, width;
         decode_tile<BN>(p, tile, m_tile, n0, width);
@@ -409,9 +422,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int b_parts = PAIR ? 1 : width / kWeightBoxRows;
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         // a pair's barrier (in the leader) counts the bytes of both CTAs, which load the same amounts
-        const uint32_t tx_bytes = (PAIR ? 2u : 1u) * ((load_a ? a_box_bytes : 0u) +
-                                                      (load_b ? static_cast<uint32_t>(PAIR ? width / 2 : width) * BK : 0u) +
-                                                      (INT8 ? 0u : scale_tiles * 512u + (dynamic_a ? 512u : 0u)));
+        const uint32_t operand_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? static_cast<uint32_t>(PAIR ? width / 2 : width) * BK : 0u) +
+                                       (dynamic_a ? 512u : 0u);
+        const uint32_t sfb_bytes = INT8 ? 0u : scale_tiles * 512u;
+        // weight scales of the first resident_k iterations are already in tensor memory when the tile before this one
+        // had the same output channels
+        const bool fresh = n0 != last_n0;
+        last_n0 = n0;
         const uint8_t* sfb_src[kScaleTilesB];
 #pragma unroll
         for (int i = 0; i < kScaleTilesB; ++i) {
@@ -429,6 +446,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 break;
               }
               const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
+              const bool load_sfb = !INT8 && (fresh || k0 >= p.resident_k * BK);
+              const uint32_t tx_bytes = (PAIR ? 2u : 1u) * (operand_bytes + (load_sfb ? sfb_bytes : 0u));
               if (!PAIR || rank == 0) {
                 if (tx_bytes != 0) {
                   mbar_expect_tx_addr(full0 + 8 * s, tx_bytes);
@@ -443,10 +462,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                   // scale tiles through their tensor maps (128 words of 4 bytes per tile): only a tiled load can count
                   // on a barrier in the other CTA
                   const int w_tile = k0 >> 7;
+                  if (load_sfb) {
 #pragma unroll
-                  for (int i = 0; i < kScaleTilesB; ++i) {
-                    const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
-                    tma_load_2d_pair(smem_sfb + (s * kScaleTilesB + i) * 512, &sfb_map, bar, 0, row_tile * p.weight_scale_tiles + w_tile);
+                    for (int i = 0; i < kScaleTilesB; ++i) {
+                      const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
+                      tma_load_2d_pair(smem_sfb + (s * kScaleTilesB + i) * 512, &sfb_map, bar, 0, row_tile * p.weight_scale_tiles + w_tile);
+                    }
                   }
                   if (dynamic_a) {
                     tma_load_2d_pair(smem_sfa + s * 512, &sfa_map, bar, 0, m_tile * p.act_scale_tiles + ((j * BK) >> 7));
@@ -468,7 +489,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 const int w_tile = k0 >> 7;
 #pragma unroll
                 for (int i = 0; i < kScaleTilesB; ++i) {
-                  if (i < scale_tiles) {
+                  if (i < scale_tiles && load_sfb) {
                     bulk_load_addr(smem_sfb + (s * kScaleTilesB + i) * 512, sfb_src[i] + static_cast<size_t>(w_tile) * 512, 512, bar);
                   }
                 }
@@ -492,14 +513,15 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int tiles = (p.cin + 127) / 128;
         for (int t = 0; t < tiles; ++t) {
           if (PAIR) {
-            tc_copy_scales_pair(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+            tc_copy_scales_pair(tmem + sfa_column + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
           } else {
-            tc_copy_scales(tmem + kSfaColumn + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
+            tc_copy_scales(tmem + sfa_column + 4 * t, sfa_desc0 + static_cast<uint64_t>((t * 512) >> 4));
           }
         }
       }
       uint32_t s = 0, phase = 0, tile_it = 0;
       bool alive = true;
+      int last_n0 = -1;
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers, ++tile_it) {
         const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
         const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
@@ -510,6 +532,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         decode_tile<BN>(p, tile, m_tile, n0, width);
         const uint32_t idesc = INT8 ? idesc_i8(width, PAIR ? 256 : kTileM) : idesc_mxf8(width, PAIR ? 256 : kTileM);
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
+        const bool fresh = n0 != last_n0;  // the resident weight scales belong to other output channels
+        last_n0 = n0;
         int j = 0;            // channel chunk within the tap
         uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
         for (int ki = 0; ki < k_iters; ++ki) {
@@ -525,12 +549,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           // tensor pipe runs both in issue order; a column set is rewritten only after the MMAs that read it, a whole
           // ring of stages earlier). Issuing a stage's copies one stage early was measured: no gain, the pipe serialises
           // copies and MMAs either way.
-          const uint32_t sfb_tmem = tmem + kSfbColumn + kSfbColumns * s;
-          const uint32_t sfa_tmem = tmem + kSfaColumn + 4 * (dynamic_a ? s : (kb_a >> 2));
+          // the first resident_k iterations keep their weight scales in columns of their own from tile to tile
+          const bool resident = ki < p.resident_k;
+          const uint32_t sfb_tmem = tmem + (resident ? resident_column + kSfbColumns * ki : kSfbColumn + kSfbColumns * s);
+          const uint32_t sfa_tmem = tmem + sfa_column + 4 * (dynamic_a ? s : (kb_a >> 2));
           if (copy_scales) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
-              if (i < scale_tiles) {
+              if (i < scale_tiles && (fresh || !resident)) {
                 const uint64_t from = sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4);
                 if (PAIR) {
                   tc_copy_scales_pair(sfb_tmem + 4 * i, from);
@@ -926,6 +952,24 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
     }
   }
   p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages, p.panels_per_half = pl.panels_per_half;
+  p.row_tiles = pl.total_tiles / pl.tiles_n;
+  p.resident_k = 0, p.n_major = 0;
+  if (!int8 && pl.block_k == 128 && !(g_debug_flags & 256)) {
+    // Tensor-memory columns left after the accumulators, the per-stage scale sets and the activation scales hold the
+    // weight scales of the first K iterations for as long as consecutive tiles of a CTA share their output channels.
+    // That needs the row tiles of one channel tile to follow each other, which re-reads the activations once per channel
+    // tile: fine when they stay in L2 or the layer is compute-bound, not for a wide memory-bound layer.
+    const int sfb_columns = pl.block_n < 128 ? 4 : pl.block_n / 32;
+    const int sfa_columns = 4 * (act_scales != nullptr ? pl.stages : (g->cin + 127) / 128);
+    const int room = 512 - acc_stages(pl.block_n) * pl.block_n - pl.stages * sfb_columns - sfa_columns;
+    const int k_iters = g->kh * g->kw * (g->cin / pl.block_k);
+    const long long activation_bytes = static_cast<long long>(g->batch) * g->height * g->width * g->cin;
+    const bool cheap_reread = pl.tiles_n == 1 || k_iters >= 8 || activation_bytes <= (48LL << 20);
+    if (room >= sfb_columns && cheap_reread) {
+      p.resident_k = room / sfb_columns < k_iters ? room / sfb_columns : k_iters;
+      p.n_major = 1;
+    }
+  }
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;

@@ -254,3 +254,43 @@ def test_repeated_launches_are_identical(ops):
     first = ops.mxfp8_conv2d.get("sm100")(*xd, 3, 3, 1, 1, 1, 1, 1, 1)
     for _ in range(10):
         assert same_bytes(ops.mxfp8_conv2d.get("sm100")(*xd, 3, 3, 1, 1, 1, 1, 1, 1), first)
+
+
+# -- CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream) -----------------------------------------
+
+
+@pytest.mark.parametrize("shape", [(3, 8, 16), (1, 40, 33), (5, 17, 19)])
+def test_int8_cta_pairs_cover_odd_row_tiles(ops, shape):
+    """256-wide INT8 tiles run as CTA pairs that own two row tiles each; an odd number of row tiles leaves the last
+    pair with a tile that does not exist (zero-filled loads, clipped stores). Sums stay exact."""
+    b, h, w = shape
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(-127, 128, (b, h, w, 128), dtype=torch.int8, generator=g)
+    weight = torch.randint(-127, 128, (256, 9 * 128), dtype=torch.int8, generator=g)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    acc = ops.int8_conv2d_accumulators.get("sm100")(*to_dev(x, weight), *geometry)
+    assert torch.equal(acc.cpu(), oracle.int8_conv2d_accumulators_ext(x, weight, *geometry))
+    a_scale, w_scale = torch.tensor(0.02), torch.rand(256, generator=g) * 0.01 + 0.001
+    bias = torch.randn(256, generator=g).to(BF16)
+    got = ops.int8_conv2d.get("sm100")(*to_dev(x, weight, a_scale, w_scale, bias), *geometry, relu=True)
+    assert same_bytes(got.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry, relu=True))
+
+
+@pytest.mark.parametrize("flags", [128, 64, 256, 16])
+def test_mxfp8_conv2d_scheduling_variants_agree(ops, flags):
+    """The tuning switches that keep results valid — CTA pairs for MXFP8 (128), no pairs (64), no resident weight scales
+    (256), no half-width tail tiles (16) — must give the bits of the default schedule (same MMAs, same epilogue)."""
+    from flashim_b200 import _native
+
+    x, ce, wq, we, bias = _mx_operands(3, 24, 40, 256, 512, 3, 3, seed=4)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    fast = ops.mxfp8_conv2d.get("sm100")
+    want = fast(*to_dev(x, ce, wq, we, bias), *geometry)
+    assert rel_l2(want, oracle.mxfp8_conv2d(x, ce, wq, we, bias, *geometry)) < 1e-3
+    lib = _native.library()
+    try:
+        lib.fim_conv_tune(0, 0, flags)
+        got = fast(*to_dev(x, ce, wq, we, bias), *geometry)
+    finally:
+        lib.fim_conv_tune(0, 0, 0)
+    assert same_bytes(got, want)
