@@ -565,7 +565,8 @@ inline CUtensorMapSwizzle swizzle_for_bytes(int inner_bytes) {
 
 // Tiled tensor map over `rank` dimensions (innermost first). `strides_bytes` has rank-1 entries (dimension 0 is dense).
 inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const uint64_t* dims,
-                           const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+                           const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
+                           CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return kNoDriver;
   cuuint64_t d[5], s[4];
@@ -577,7 +578,7 @@ inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank,
     if (i + 1 < rank) s[i] = strides_bytes[i];
   }
   const CUresult r = fn(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        swizzle, promotion, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kOk : kNoDriver;
 }
 

@@ -420,7 +420,10 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   const uint64_t strides[3] = {static_cast<uint64_t>(channels) * 2, static_cast<uint64_t>(width) * channels * 2,
                                static_cast<uint64_t>(height) * width * channels * 2};
   const uint32_t box[4] = {kChannels, static_cast<uint32_t>(tile_cols + 4), kChunkRows, 1};
-  const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+  // a CTA reads 128 bytes (64 channels) of every pixel: with more channels than that, fetching 256-byte granules into L2
+  // would drag in the neighbouring channel tile, which another CTA reads much later
+  const int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 channels > kChannels ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rc != kOk) return rc;
 
   // two persistent CTAs per SM; a small problem gets fewer, each with at least four units so the halo chunk stays cheap
