@@ -56,7 +56,7 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v) {
 // index in the batch; `cols_ok` has bit j set when column x0 + j exists (0 for a lane without channels).
 template <int MODE, int ACT>
 __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[kCols], uint64_t bias2, void* out_row,
-                                         size_t pixel0, int c, uint32_t cols_ok, const Int8Quantizer& int8) {
+                                         size_t pixel0, int c, uint32_t cols_ok, const Int8Quantizer& int8, int lane) {
   const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
   uint64_t v[kCols];
 #pragma unroll
@@ -80,7 +80,6 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
       unpack2(v[j], lo, hi);
       m[j] = fmaxf(fabsf(lo), fabsf(hi));
     }
-    const int lane = threadIdx.x & 31;
     {
       const bool odd = lane & 1;  // even lanes keep pixels 0, 1 and odd lanes pixels 2, 3
       const float s0 = __shfl_xor_sync(0xffffffffu, odd ? m[0] : m[2], 1);
@@ -98,12 +97,17 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     const int e = e8m0_exponent_bits(__float_as_uint(m[0]));
     const float inv_mine = exp2_int(-e);
     const int mine = ((lane & 1) << 1) | ((lane >> 1) & 1);  // the pixel this lane holds
-    if ((lane & 12) == 0 && ((cols_ok >> mine) & 1u)) {
+    {
+      // the owner lanes (0-3 of each half-warp) store their pixel's scale byte; the address is computed by all lanes and
+      // only the store is predicated, which keeps the warp converged
       const size_t pixel = pixel0 + mine;
       const int groups = p.channels >> 5;
       const int g = c >> 5;
       const size_t at = p.swizzled ? swizzled_scale_offset(pixel, g, (groups + 3) >> 2) : pixel * groups + g;
-      p.scales[at] = static_cast<uint8_t>(e + 127);
+      const uint32_t owner = ((lane & 12) == 0 && ((cols_ok >> mine) & 1u)) ? 1u : 0u;
+      asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q st.global.u8 [%0], %1;\n\t}" ::"l"(p.scales + at),
+                   "r"(static_cast<uint32_t>(e + 127)), "r"(owner)
+                   : "memory");
     }
     const int half = lane & 16;
     uint16_t* out = static_cast<uint16_t*>(out_row);
@@ -287,7 +291,7 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
             for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + s_next * kChunkBytes + j * (kChannels * 2));
           }
         }
-        if (!(PROBE && (p.debug & 2))) emit_row<MODE, ACT>(p, fin, bias2, fin_out, fin_pixel, c, fin_mask, int8_scale);
+        if (!(PROBE && (p.debug & 2))) emit_row<MODE, ACT>(p, fin, bias2, fin_out, fin_pixel, c, fin_mask, int8_scale, lane);
         if (!(PROBE && (p.debug & 1))) {
           // 100 packed FMAs: input row r = 5 g + ph feeds tap row ky of the output row in slot (ph - ky) mod 5. Tap column
           // outermost, so neighbouring instructions belong to 20 different accumulators and nothing waits on the FMA
