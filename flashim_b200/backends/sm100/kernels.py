@@ -435,6 +435,49 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         def int8_conv2d_accumulators(x, weight, kh, kw, sh, sw, ph, pw, dh, dw):
             return int8_conv2d_launch(x, weight, None, None, None, None, None, kh, kw, ph, pw, dh, dw, 0, _native.OUT_INT32)
 
+    # -- GEMMs: a 1x1 conv over a one-row image of M pixels -------------------------------------------------------------
+    if hasattr(ops, "mxfp8_scaled_mm"):
+        def scaled_mm_when(a, b_t, a_scale, b_scale, bias=None):
+            return (
+                have() and _cuda(a, b_t, a_scale, b_scale, bias) and a.dim() == 2 and b_t.dim() == 2
+                and a.dtype == E4M3 and b_t.dtype == E4M3 and a.is_contiguous() and b_t.t().is_contiguous()
+                and a.shape[1] == b_t.shape[0] and a.shape[1] % 32 == 0 and b_t.shape[1] % 32 == 0 and a.shape[0] > 0
+                and a_scale.element_size() == 1 and b_scale.element_size() == 1
+                and a_scale.numel() == swizzled_scale_bytes(a.shape[0], a.shape[1] // BLOCK)
+                and b_scale.numel() == swizzled_scale_bytes(b_t.shape[1], a.shape[1] // BLOCK)
+                and (bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == b_t.shape[1]))
+            )
+
+        @ops.mxfp8_scaled_mm.register("sm100", device=spec, requires=requires, priority=3, when=scaled_mm_when)
+        def mxfp8_scaled_mm(a, b_t, a_scale, b_scale, bias=None):
+            m, k = a.shape
+            out, _ = mxfp8_conv2d_launch(
+                a.view(1, 1, m, k), None, a_scale.view(torch.uint8).reshape(-1), b_t.t(), b_scale.view(torch.uint8).reshape(-1),
+                None if bias is None else bias.contiguous(), None, None, 1, 1, 0, 0, 1, 1, act_code["none"], _native.OUT_BF16)
+            return out.view(m, -1)
+
+    if hasattr(ops, "int8_linear"):
+        def int8_linear_when(a, weight, a_scale, w_scale, bias, *, relu=False, gelu=False, residual=None):
+            return (
+                have() and _cuda(a, weight, a_scale, w_scale, bias, residual) and a.dim() == 2 and weight.dim() == 2
+                and a.dtype == torch.int8 and weight.dtype == torch.int8 and a.is_contiguous() and weight.is_contiguous()
+                and a.shape[1] == weight.shape[1] and a.shape[1] % 32 == 0 and weight.shape[0] % 32 == 0 and a.shape[0] > 0
+                and a_scale.numel() == 1 and w_scale.numel() == weight.shape[0] and not gelu
+                and (bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == weight.shape[0]))
+                # the conv epilogue applies ReLU after the residual, the linear before it: both at once are not covered
+                and (residual is None or (not relu and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+                                          and tuple(residual.shape) == (a.shape[0], weight.shape[0])))
+            )
+
+        @ops.int8_linear.register("sm100", device=spec, requires=requires, priority=3, when=int8_linear_when)
+        def int8_linear(a, weight, a_scale, w_scale, bias, *, relu=False, gelu=False, residual=None):
+            m, k = a.shape
+            out = int8_conv2d_launch(
+                a.view(1, 1, m, k), weight, a_scale.float().reshape(1), w_scale.float().contiguous(),
+                None if bias is None else bias.contiguous(), None if residual is None else residual.view(1, 1, m, -1), None,
+                1, 1, 0, 0, 1, 1, act_code["relu" if relu else "none"], _native.OUT_BF16)
+            return out.view(m, -1)
+
     # -- depthwise ---------------------------------------------------------------------------------------------------
     dw_requires = [feature.TMA] + ([feature.SM100A_KERNELS] if hasattr(feature, "SM100A_KERNELS") else [])
 

@@ -2,7 +2,7 @@
 
 ``register_into_flashim()`` registers the ``"sm100"`` implementations into FlashIM's own op registry
 (``flashim.ops.mxfp8_conv2d``, ``int8_conv2d``, ``depthwise5x5_relu_mxfp8``, ``depthwise5x5_relu_int8``,
-``quantize_mxfp8``, ``quantize_int8``) with FlashIM's ``DeviceSpec`` / ``Feature`` types, so ``flashim.load(name,
+``quantize_mxfp8``, ``quantize_int8``, ``mxfp8_scaled_mm``, ``int8_linear``) with FlashIM's ``DeviceSpec`` / ``Feature`` types, so ``flashim.load(name,
 preset)`` dispatches to them on a compute-capability-10.0 device. It is what an entry point of group
 ``flashim.backends`` (flashim/backends/_loader.py:63-70) or a ``Backend("sm100", ...)`` row of ``BACKENDS`` would call.
 
@@ -25,7 +25,7 @@ def register_into_flashim() -> list[str]:
     from flashim_b200.backends.sm100 import kernels
 
     names = ["mxfp8_conv2d", "int8_conv2d", "depthwise5x5_relu_mxfp8", "depthwise5x5_relu_int8", "quantize_mxfp8",
-             "quantize_int8"]
+             "quantize_int8", "mxfp8_scaled_mm", "int8_linear"]
     if not _DONE:
         kernels.register(their_ops, DeviceSpec, Feature)
         _DONE = True

@@ -25,6 +25,12 @@ mxfp8_conv2d = Op("mxfp8_conv2d", doc="(x E4M3 NHWC, channel_exponent, weight E4
 int8_conv2d = Op("int8_conv2d", doc="(x int8 NHWC, weight int8 [Cout, K], a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, "
                  "dh, dw, *, relu, residual, out_scale) -> bf16 / int8 NHWC (flashim/ops/conv.py:174-206)")
 
+mxfp8_scaled_mm = Op("mxfp8_scaled_mm", doc="(a E4M3 [M, K], b_t E4M3 [K, N] (the transpose of a row-major [N, K]), a_scale, "
+                     "b_scale swizzled E8M0, bias=None) -> bf16 [M, N]: the block-scaled GEMM the pointwise composites end "
+                     "in (flashim/ops/gemm.py:40-52)")
+int8_linear = Op("int8_linear", doc="(a int8 [M, K], weight int8 [N, K], a_scale, w_scale, bias, *, relu, gelu, residual) -> "
+                 "bf16 [M, N] (flashim/ops/gemm.py:82-98)")
+
 # -- extensions --------------------------------------------------------------------------------------------------------
 quantize_mxfp8_dynamic = Op("quantize_mxfp8_dynamic", doc="(value [..., C]) -> (E4M3 [..., C], swizzled E8M0 bytes): "
                             "per-(row, 32) dynamic MXFP8, the quantiser of flashim/quant/formats/mx.py:50-60 as an op")

@@ -34,7 +34,7 @@ __all__ = [
     "pack_int8_conv_weight", "gather_taps", "conv_out_size", "mx_matmul_fp32", "int8_matmul_int32",
     "mxfp8_conv2d", "int8_conv2d", "add_residual", "depthwise5x5_fp32", "depthwise5x5_relu_mxfp8",
     "depthwise5x5_relu_int8", "depthwise5x5_act_ext", "depthwise5x5_act_mxfp8_ext", "mxfp8_conv2d_ext",
-    "int8_conv2d_accumulators_ext", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
+    "int8_conv2d_accumulators_ext", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
     "dequantize_mx",
 ]
 
@@ -272,6 +272,36 @@ def int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, d
     if residual is not None:
         out = add_residual(out, residual, relu)
     return out if out_scale is None else quantize_int8(out, out_scale.float().reshape(()))
+
+
+def mxfp8_scaled_mm(a: Tensor, b_t: Tensor, a_scale: Tensor, b_scale: Tensor, bias: Tensor | None = None) -> Tensor:
+    """Block-scaled MXFP8 GEMM ``a [M, K] x b_t [K, N]`` with swizzled E8M0 scales of both operands (rows of ``a``, rows
+    of ``b_t.t()``), fp32 product, ``+ bias`` in fp32, one bf16 rounding (flashim/ops/gemm.py:21-52)."""
+    def dense(values: Tensor, swizzled: Tensor) -> Tensor:
+        rows, k = values.shape
+        exponent = unswizzle_32_4_4(swizzled.view(torch.uint8), rows, k // MX_BLOCK).float()
+        return (values.float().reshape(rows, k // MX_BLOCK, MX_BLOCK) * torch.exp2(exponent)[..., None]).reshape(rows, k)
+
+    out = dense(a, a_scale) @ dense(b_t.t(), b_scale).t()
+    if bias is not None:
+        out = out + bias.float()
+    return out.to(torch.bfloat16)
+
+
+def int8_linear(a, weight, a_scale, w_scale, bias, *, relu=False, gelu=False, residual=None) -> Tensor:
+    """``[M, K] int8 x [N, K] int8^T`` in int32, ``float(acc) * (a_scale * w_scale) + bias``, ReLU, one bf16 rounding,
+    GELU of the bf16 value (rounded to bf16), residual added in bf16 (flashim/ops/gemm.py:82-98)."""
+    out = int8_matmul_int32(a, weight).float() * (a_scale.float() * w_scale.float())
+    if bias is not None:
+        out = out + bias.float()
+    if relu:
+        out = out.relu()
+    out = out.to(torch.bfloat16)
+    if gelu:
+        out = F.gelu(out)
+    if residual is not None:
+        out = residual + out
+    return out
 
 
 def int8_conv2d_accumulators_ext(x, weight, kh, kw, sh, sw, ph, pw, dh, dw) -> Tensor:

@@ -182,9 +182,38 @@ def modules() -> None:
     )
 
 
+def gemms() -> None:
+    """Block-scaled MXFP8 GEMM and INT8 linear of the reference on small operands (rows and groups with padding)."""
+    g = torch.Generator().manual_seed(17)
+    arrays = {}
+    for i, (m, k, n) in enumerate([(37, 64, 32), (130, 128, 96), (256, 256, 64)]):
+        a = (torch.randn(m, k, generator=g) * 2).to(torch.float8_e4m3fn)
+        w = (torch.randn(n, k, generator=g) * 2).to(torch.float8_e4m3fn)
+        ae = torch.randint(-5, 4, (m, k // 32), dtype=torch.int8, generator=g)
+        we = torch.randint(-8, -2, (n, k // 32), dtype=torch.int8, generator=g)
+        bias = torch.randn(n, generator=g).to(torch.bfloat16) if i else None
+        sa, sw = ref_mx.swizzle_scales(ae), ref_mx.swizzle_scales(we)
+        out = ops.mxfp8_scaled_mm.get("reference")(a, w.t(), sa, sw, bias)
+        arrays.update({f"mm{i}_a": raw(a), f"mm{i}_w": raw(w), f"mm{i}_ae": raw(ae), f"mm{i}_we": raw(we),
+                       f"mm{i}_sa": raw(sa.view(torch.uint8)), f"mm{i}_sw": raw(sw.view(torch.uint8)), f"mm{i}_out": raw(out)})
+        if bias is not None:
+            arrays[f"mm{i}_bias"] = raw(bias)
+        a8 = torch.randint(-127, 128, (m, k), dtype=torch.int8, generator=g)
+        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=g)
+        ws = torch.rand(n, generator=g) * 0.01 + 0.001
+        res = torch.randn(m, n, generator=g).to(torch.bfloat16)
+        b8 = torch.randn(n, generator=g).to(torch.bfloat16)
+        plain = ops.int8_linear.get("reference")(a8, w8, torch.tensor(0.02), ws, b8, relu=bool(i & 1))
+        with_res = ops.int8_linear.get("reference")(a8, w8, torch.tensor(0.02), ws, b8, residual=res)
+        arrays.update({f"li{i}_a": raw(a8), f"li{i}_w": raw(w8), f"li{i}_ws": raw(ws), f"li{i}_b": raw(b8), f"li{i}_res": raw(res),
+                       f"li{i}_out": raw(plain), f"li{i}_out_res": raw(with_res)})
+    save("gemms", **arrays)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     formats()
     convs()
     depthwise()
     modules()
+    gemms()

@@ -294,3 +294,23 @@ def test_mxfp8_conv2d_scheduling_variants_agree(ops, flags):
     finally:
         lib.fim_conv_tune(0, 0, 0)
     assert same_bytes(got, want)
+
+
+# -- GEMMs (a 1x1 conv over M pixels): flashim/ops/gemm.py:40-98 -------------------------------------------------------
+
+
+def test_mxfp8_scaled_mm_and_int8_linear_golden(ops, golden):
+    g = golden("gemms")
+    for i in range(3):
+        a, w = g(f"mm{i}_a", E4M3), g(f"mm{i}_w", E4M3)
+        got = ops.mxfp8_scaled_mm.get("sm100")(to_dev(a), to_dev(w).t(), to_dev(g(f"mm{i}_sa")), to_dev(g(f"mm{i}_sw")),
+                                               to_dev(g.get(f"mm{i}_bias", BF16)))
+        assert rel_l2(got, g(f"mm{i}_out", BF16)) < 1e-3, f"scaled_mm case {i}"
+        assert float((bf16_ulp_distance(got.cpu(), g(f"mm{i}_out", BF16)) > 1).float().mean()) < 1e-2
+        args = to_dev(g(f"li{i}_a"), g(f"li{i}_w"), torch.tensor(0.02), g(f"li{i}_ws"), g(f"li{i}_b", BF16))
+        fast = ops.int8_linear.get("sm100")
+        assert same_bytes(fast(*args, relu=bool(i & 1)).cpu(), g(f"li{i}_out", BF16)), f"int8_linear case {i}"
+        assert same_bytes(fast(*args, residual=to_dev(g(f"li{i}_res", BF16))).cpu(), g(f"li{i}_out_res", BF16))
+    # what the kernel does not cover is declined, not approximated
+    a8, w8, s, ws, b = to_dev(g("li0_a"), g("li0_w"), torch.tensor(0.02), g("li0_ws"), g("li0_b", BF16))
+    assert ops.int8_linear.explain(a8, w8, s, ws, b, gelu=True)["sm100"] != "selected"

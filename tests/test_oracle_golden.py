@@ -232,3 +232,16 @@ def test_refiner_level_runs_and_is_deterministic():
     a, b = oracle.refiner_level_ext(x, level), oracle.refiner_level_ext(x, level)
     assert a.shape == (1, 10, 12, 32) and a.dtype == BF16 and same_bytes(a, b)
     assert torch.isfinite(a.float()).all()
+
+
+def test_gemm_ops_match_reference_outputs(golden):
+    """mxfp8_scaled_mm and int8_linear of the reference (flashim/ops/gemm.py:40-98) on operands with row / group padding."""
+    g = golden("gemms")
+    for i in range(3):
+        a, w = g(f"mm{i}_a", E4M3), g(f"mm{i}_w", E4M3)
+        assert same_bytes(oracle.swizzle_32_4_4(g(f"mm{i}_ae")), g(f"mm{i}_sa"))
+        out = oracle.mxfp8_scaled_mm(a, w.t(), g(f"mm{i}_sa"), g(f"mm{i}_sw"), g.get(f"mm{i}_bias", BF16))
+        assert same_bytes(out, g(f"mm{i}_out", BF16)), f"scaled_mm case {i}"
+        args = (g(f"li{i}_a"), g(f"li{i}_w"), torch.tensor(0.02), g(f"li{i}_ws"), g(f"li{i}_b", BF16))
+        assert same_bytes(oracle.int8_linear(*args, relu=bool(i & 1)), g(f"li{i}_out", BF16)), f"int8_linear case {i}"
+        assert same_bytes(oracle.int8_linear(*args, residual=g(f"li{i}_res", BF16)), g(f"li{i}_out_res", BF16))
