@@ -1,10 +1,14 @@
-"""Model builder with FlashIM's public surface (flashim/build.py:50-148,212-232,344-430): ``ModelSpec`` +
-``RunConfig`` -> a ready-to-run module; ``register_spec`` / ``get_spec``; ``resolve`` (preset + config + overrides ->
-validated ``RunConfig``, FP8 replaced by the nearest preset on a GPU without FP8); ``build_config`` (stages: load ->
-pre-quant passes -> post-quant passes -> engine); ``load(name, preset, *, device, engine, strict, config, overrides)``.
+"""From a model name and a preset to a module that runs: the ``load(name, preset)`` surface of this backend.
 
-The models this package registers are synthetic stacks built from the conv-path ops (see ``flashim_b200.refiner``); the
-stages that need checkpoints or calibration tables in FlashIM have no counterpart here.
+The public names and their meaning follow FlashIM's builder (flashim/build.py:50-148,212-232,344-430) so that code
+written against ``flashim.load`` ports by changing the import: a model is described by a ``ModelSpec`` (how to
+construct it, its precision presets, its optional graph passes and its engines); ``resolve`` turns *preset + user
+config + overrides* into a validated ``RunConfig`` (substituting the nearest available precision when the asked one is
+missing, or FP8 is asked on a GPU without it); ``build_config`` constructs the module, applies the requested passes in
+two stages and installs the engine; ``load`` is the one-call form.
+
+The models registered here are synthetic stacks assembled from the conv-path ops (``flashim_b200.refiner``): there are
+no checkpoints or calibration tables, so the stages FlashIM has for those do not exist in this builder.
 """
 
 from __future__ import annotations
@@ -19,17 +23,26 @@ from typing import Any, Literal
 import torch
 from torch import nn
 
-from flashim_b200.config import RunConfig, load_file, merge, parse_overrides, resolve_preset
+from flashim_b200 import config as cfg
+from flashim_b200.config import RunConfig
 from flashim_b200.platforms import Feature, Platform, default_device, platform_for
 
-logger = logging.getLogger("flashim_b200.build")
+log = logging.getLogger("flashim_b200.build")
 
 PRECISIONS = ("fp32", "bf16", "int8", "fp8")
-NEAREST = {"fp8": ("int8", "bf16", "fp32"), "int8": ("bf16", "fp32"), "bf16": ("fp32",), "fp32": ("bf16",)}
+# which presets stand in for a missing one, best first
+_SUBSTITUTES = {"fp8": ("int8", "bf16", "fp32"), "int8": ("bf16", "fp32"), "bf16": ("fp32",), "fp32": ("bf16",)}
+_STAGES = ("pre_quant", "post_quant")
+
+
+# ---- what a model declares -------------------------------------------------------------------------------------------
 
 
 @dataclass(frozen=True)
 class Pass:
+    """A named, optional transformation of the built module. ``apply(model, ctx)`` may return a summary that lands in the
+    build report; ``requires(platform)`` gates it; ``exact`` says whether outputs stay bit-identical."""
+
     apply: Callable[[nn.Module, "BuildContext"], Any]
     stage: Literal["pre_quant", "post_quant"] = "post_quant"
     requires: Callable[[Platform], bool] | None = None
@@ -39,7 +52,7 @@ class Pass:
 
 @dataclass(frozen=True)
 class EngineSpec:
-    """``setup(model, ctx)`` prepares the engine (for ``cuda-graph``: wraps the forward in a graph runner)."""
+    """An execution engine: ``setup(model, ctx)`` installs it on the built module (``None``: plain eager calls)."""
 
     regions: Sequence[str] = ()
     setup: Callable[[nn.Module, "BuildContext"], None] | None = None
@@ -61,23 +74,34 @@ class ModelSpec:
     validate: Callable[[RunConfig], None] | None = None
 
     def __post_init__(self) -> None:
-        unknown = sorted(set(self.presets) - set(PRECISIONS))
-        if unknown or self.default_preset not in self.presets:
-            raise ValueError(f"{self.name}: presets must be among {PRECISIONS} and include the default, got "
-                             f"{sorted(self.presets)} (default {self.default_preset!r})")
+        foreign = [p for p in self.presets if p not in PRECISIONS]
+        if foreign:
+            raise ValueError(f"{self.name}: preset names are precisions ({', '.join(PRECISIONS)}); got {foreign}")
+        if self.default_preset not in self.presets:
+            raise ValueError(f"{self.name}: the default preset {self.default_preset!r} is not among its presets")
 
     def check(self, config: RunConfig) -> None:
-        unknown = [p for p in config.optimize.passes if p not in self.passes]
-        if unknown:
-            raise ValueError(f"{self.name}: unknown pass(es) {unknown}; available: {sorted(self.passes)}")
+        """Raise if ``config`` names a pass or an engine this model does not have, then run the model's own validation."""
+        for name in config.optimize.passes:
+            if name not in self.passes:
+                raise ValueError(f"{self.name}: unknown pass {name!r} (it has: {', '.join(sorted(self.passes)) or 'none'})")
         if config.engine.kind not in self.engines:
-            raise ValueError(f"{self.name}: unknown engine {config.engine.kind!r}; choose from {sorted(self.engines)}")
+            raise ValueError(f"{self.name}: unknown engine {config.engine.kind!r} (it has: {', '.join(sorted(self.engines))})")
         if self.validate is not None:
             self.validate(config)
+
+    def closest_preset(self, wanted: str, *, excluding: str | None = None) -> str:
+        for candidate in (wanted, *_SUBSTITUTES[wanted]):
+            if candidate in self.presets and candidate != excluding:
+                return candidate
+        raise ValueError(f"{self.name}: nothing can stand in for preset {wanted!r}")
 
 
 @dataclass
 class BuildReport:
+    """What happened while building: which passes ran (and what they returned), which were skipped and why, which
+    precision substitutions were made."""
+
     config_digest: str
     platform: str
     passes: dict[str, Any] = field(default_factory=dict)
@@ -97,90 +121,117 @@ class BuildContext:
         return self.config.optimize.options.get(name, default)
 
 
-_SPEC_PATHS: dict[str, str] = {"refiner-stack": "flashim_b200.refiner:SPEC"}
-_SPECS: dict[str, ModelSpec] = {}
+# ---- the model table -------------------------------------------------------------------------------------------------
+
+
+class _SpecTable:
+    """Specs by name; an entry may be a ``"module:attribute"`` path that is imported on first use."""
+
+    def __init__(self) -> None:
+        self._entries: dict[str, str | ModelSpec] = {"refiner-stack": "flashim_b200.refiner:SPEC"}
+
+    def add(self, name: str, target: str | ModelSpec) -> None:
+        self._entries[name] = target
+
+    def names(self) -> list[str]:
+        return sorted(self._entries)
+
+    def get(self, name: str) -> ModelSpec:
+        try:
+            entry = self._entries[name]
+        except KeyError:
+            raise ValueError(f"no model named {name!r}; registered: {', '.join(self.names())}") from None
+        if isinstance(entry, str):
+            module, _, attribute = entry.partition(":")
+            entry = self._entries[name] = getattr(importlib.import_module(module), attribute)
+        return entry
+
+
+_TABLE = _SpecTable()
 
 
 def register_spec(name: str, target: str | ModelSpec) -> None:
-    if isinstance(target, ModelSpec):
-        _SPECS[name] = target
-    else:
-        _SPEC_PATHS[name] = target
+    _TABLE.add(name, target)
 
 
 def get_spec(name: str) -> ModelSpec:
-    spec = _SPECS.get(name)
-    if spec is None:
-        if name not in _SPEC_PATHS:
-            raise ValueError(f"Unknown model {name!r}; available: {sorted({*_SPECS, *_SPEC_PATHS})}")
-        module, attr = _SPEC_PATHS[name].split(":")
-        spec = _SPECS[name] = getattr(importlib.import_module(module), attr)
-    return spec
+    return _TABLE.get(name)
 
 
 def spec_names() -> list[str]:
-    return sorted({*_SPECS, *_SPEC_PATHS})
+    return _TABLE.names()
 
 
-def _nearest(spec: ModelSpec, preset: str, skip: str | None = None) -> str:
-    return next(p for p in (preset, *NEAREST[preset]) if p in spec.presets and p != skip)
+# ---- resolve ---------------------------------------------------------------------------------------------------------
 
 
-def _user_overlay(config) -> dict[str, Any]:
+def _as_table(config) -> dict[str, Any]:
+    """The user's layer as a plain table, from a RunConfig, a path, a mapping or nothing."""
+    if config is None:
+        return {}
     if isinstance(config, RunConfig):
         return config.to_dict()
     if isinstance(config, (str, Path)):
-        return load_file(config)
-    return dict(config) if config is not None else {}
+        return cfg.load_file(config)
+    return dict(config)
 
 
 def resolve(name: str, preset: str | None = None, config=None, overrides: Iterable[str] | Mapping[str, Any] = (), *,
             platform: Platform | None = None, fallbacks: dict[str, str] | None = None) -> RunConfig:
+    """Preset + user config + overrides -> a validated ``RunConfig``. A preset the model lacks, or FP8 on a GPU without
+    FP8, is replaced by the closest one the model has (recorded in ``fallbacks``; an error under ``optimize.strict``)."""
     spec = get_spec(name)
-    user = merge(_user_overlay(config), parse_overrides(overrides))
+    user = cfg.merge(_as_table(config), cfg.parse_overrides(overrides))
     user.pop("model", None)
-    preset = preset or user.pop("preset", None) or spec.default_preset
-    user.pop("preset", None)
-    if preset not in PRECISIONS:
-        raise ValueError(f"{spec.name}: unknown preset {preset!r}; choose from {PRECISIONS}")
-    strict = bool((user.get("optimize") or {}).get("strict", False))
-    built, reason = _nearest(spec, preset), None
-    if built != preset:
+    from_user = user.pop("preset", None)
+    wanted = preset or from_user or spec.default_preset
+    if wanted not in PRECISIONS:
+        raise ValueError(f"{spec.name}: {wanted!r} is not a preset; presets are {', '.join(PRECISIONS)}")
+    strict = bool((user.get("optimize") or {}).get("strict"))
+
+    chosen, why = spec.closest_preset(wanted), None
+    if chosen != wanted:
         if strict:
-            raise ValueError(f"{spec.name}: no {preset!r} preset (optimize.strict); available: {sorted(spec.presets)}")
-        reason = f"{spec.name} has no {preset}"
-    if built == "fp8" and platform is not None and platform.device_type != "cpu" and not platform.supports(Feature.FP8_E4M3):
+            raise ValueError(f"{spec.name} has no {wanted!r} preset and optimize.strict forbids a substitute "
+                             f"(it has: {', '.join(sorted(spec.presets))})")
+        why = f"{spec.name} has no {wanted} preset"
+    on_gpu_without_fp8 = (platform is not None and platform.device_type != "cpu" and not platform.supports(Feature.FP8_E4M3))
+    if chosen == "fp8" and on_gpu_without_fp8:
         if strict:
-            logger.warning("%s: no FP8 on %s, preset 'fp8' kept (optimize.strict)", spec.name, platform.describe())
+            log.warning("%s: %s has no FP8; keeping preset 'fp8' because optimize.strict is set", spec.name, platform.describe())
         else:
-            built, reason = _nearest(spec, "fp8", skip="fp8"), f"no FP8 on {platform.describe()}"
-    if reason is not None:
-        logger.warning("%s: preset %r replaced by %r (%s)", spec.name, preset, built, reason)
+            chosen, why = spec.closest_preset("fp8", excluding="fp8"), f"{platform.describe()} has no FP8"
+    if why is not None:
+        log.warning("%s: building preset %r instead of %r: %s", spec.name, chosen, wanted, why)
         if fallbacks is not None:
-            fallbacks[spec.name] = f"{preset} -> {built} ({reason})"
-    data = merge(resolve_preset(spec.presets, built), user)
-    data.update(model=spec.name, preset=built)
-    resolved = RunConfig.from_dict(data)
+            fallbacks[spec.name] = f"{wanted} -> {chosen} ({why})"
+
+    table = cfg.merge(cfg.resolve_preset(spec.presets, chosen), user)
+    table["model"], table["preset"] = spec.name, chosen
+    resolved = RunConfig.from_dict(table)
     spec.check(resolved)
     return resolved
 
 
-def _run_passes(model: nn.Module, ctx: BuildContext, stage: str) -> None:
-    for name in ctx.config.optimize.passes:
-        p = ctx.spec.passes[name]
-        if p.stage != stage:
-            continue
-        if p.requires is not None and not p.requires(ctx.platform):
-            reason = f"not supported on {ctx.platform.describe()}"
+# ---- build -----------------------------------------------------------------------------------------------------------
+
+
+def _apply_stage(model: nn.Module, ctx: BuildContext, stage: str) -> None:
+    wanted = [(name, ctx.spec.passes[name]) for name in ctx.config.optimize.passes if ctx.spec.passes[name].stage == stage]
+    for name, step in wanted:
+        if step.requires is not None and not step.requires(ctx.platform):
+            reason = f"needs a capability {ctx.platform.describe()} lacks"
             if ctx.config.optimize.strict:
-                raise RuntimeError(f"{ctx.spec.name}: pass {name!r} {reason}")
-            logger.warning("%s: skipping pass %r (%s)", ctx.spec.name, name, reason)
+                raise RuntimeError(f"{ctx.spec.name}: pass {name!r} {reason} (optimize.strict)")
+            log.warning("%s: pass %r left out: %s", ctx.spec.name, name, reason)
             ctx.report.skipped[name] = reason
-            continue
-        ctx.report.passes[name] = p.apply(model, ctx)
+        else:
+            ctx.report.passes[name] = step.apply(model, ctx)
 
 
 def build_config(config: RunConfig) -> nn.Module:
+    """Construct the model of a resolved configuration: load, passes (pre-quant, then post-quant), engine. The module
+    gets ``run_config``, ``build_report``, ``preset`` and ``engine`` attributes."""
     spec = get_spec(config.model)
     spec.check(config)
     if config.optimize.ops:
@@ -188,34 +239,33 @@ def build_config(config: RunConfig) -> nn.Module:
 
         ops.configure(config.optimize.ops)
     model = spec.load(config)
-    device = next((b.device for b in model.buffers()), torch.device(config.device or "cpu"))
-    platform = platform_for(device)
-    report = BuildReport(config.digest(), platform.describe(), engine=config.engine.kind)
-    ctx = BuildContext(config, spec, platform, report)
-    _run_passes(model, ctx, "pre_quant")
-    _run_passes(model, ctx, "post_quant")
-    engine = spec.engines[config.engine.kind]
-    if engine.setup is not None:
-        engine.setup(model, ctx)
-    model.run_config, model.build_report = config, report
+    where = next((buffer.device for buffer in model.buffers()), None) or torch.device(config.device or "cpu")
+    platform = platform_for(where)
+    ctx = BuildContext(config, spec, platform, BuildReport(config.digest(), platform.describe(), engine=config.engine.kind))
+    for stage in _STAGES:
+        _apply_stage(model, ctx, stage)
+    setup = spec.engines[config.engine.kind].setup
+    if setup is not None:
+        setup(model, ctx)
+    model.run_config, model.build_report = config, ctx.report
     model.preset, model.engine = config.preset, config.engine.kind
     return model
 
 
 def load(name: str, preset: str | None = None, *, device: torch.device | str | None = None, engine: str | None = None,
          strict: bool | None = None, config=None, overrides: Iterable[str] | Mapping[str, Any] = ()) -> nn.Module:
-    """Load a registered model: ``preset`` + ``config`` (RunConfig / dict / file) + dotted ``overrides`` + the keyword
-    arguments (later layers win), resolved for the target device's platform and built."""
-    overlay: dict[str, Any] = {}
+    """``load("refiner-stack", "fp8", device="cuda", engine="cuda-graph")``: resolve for the platform of the target
+    device and build. Layers, weakest first: preset, ``config`` (RunConfig / table / file), ``overrides``, keywords."""
+    keywords: dict[str, Any] = {}
     if device is not None:
-        overlay["device"] = str(device)
+        keywords["device"] = str(device)
     if engine is not None:
-        overlay["engine"] = {"kind": engine}
+        keywords["engine"] = {"kind": engine}
     if strict is not None:
-        overlay["optimize"] = {"strict": strict}
-    user = merge(merge(_user_overlay(config), parse_overrides(overrides)), overlay)
-    fallbacks: dict[str, str] = {}
+        keywords["optimize"] = {"strict": strict}
+    user = cfg.merge(cfg.merge(_as_table(config), cfg.parse_overrides(overrides)), keywords)
+    substitutions: dict[str, str] = {}
     platform = platform_for(user.get("device") or default_device())
-    model = build_config(resolve(name, preset, user, platform=platform, fallbacks=fallbacks))
-    model.build_report.fallbacks = fallbacks
+    model = build_config(resolve(name, preset, user, platform=platform, fallbacks=substitutions))
+    model.build_report.fallbacks = substitutions
     return model

@@ -1,54 +1,70 @@
-"""Op declaration and dispatch with the semantics of FlashIM's registry (flashim/ops/_registry.py:44-428): an op is
-declared once, implementations register for a device spec + required features + priority + a per-call ``when``
-predicate; selection is highest priority, then narrowest capability range, then registration order; ``get(name)`` pins
-an implementation, ``explain`` reports why each one was (not) chosen, ``configure`` applies ``FLASHIM_OPS`` overrides
-and strict mode forbids falling back.
+"""Ops and their implementations: declaration, registration and per-call dispatch.
 
-One deliberate difference: FlashIM's fallback is a torch reference implementation. This package ships none. An op
+The vocabulary and the selection rule are those of FlashIM's op registry (flashim/ops/_registry.py:44-428), so that an
+implementation module written for one registers unchanged into the other: an ``Op`` is declared once by name;
+implementations attach with ``op.register(name, device=DeviceSpec(...), requires=[features], priority=n, when=predicate)``;
+a call goes to the applicable implementation with the highest priority, ties broken by the narrower compute-capability
+range and then by registration order; a negative priority means "only when asked for by name". ``op.get(name)`` pins an
+implementation, ``op.explain(*args)`` says per implementation why it was or was not taken, ``configure("-op,op:impl")``
+disables or forces by name, and strict mode turns a fall-back on a GPU into an error.
+
+One deliberate difference: FlashIM's last resort is a torch reference implementation; this package ships none. An op
 declared without a reference raises :class:`NoImplementation` where FlashIM would have fallen back, so a call can never
 silently leave the CUDA path.
 """
 
 from __future__ import annotations
 
+import dataclasses
 import os
 from collections import Counter
 from collections.abc import Callable, Iterable
-from dataclasses import dataclass, fields, is_dataclass
+from dataclasses import dataclass
 
 import torch
 
 from flashim_b200.platforms import Feature, Platform, platform_for
 
 REFERENCE = "reference"
+OPS: dict[str, "Op"] = {}
 
 
 class NoImplementation(RuntimeError):
     """No registered implementation applies to the call and the op has no reference to fall back to."""
 
 
+# ---- where an implementation runs ------------------------------------------------------------------------------------
+
+
 @dataclass(frozen=True)
 class DeviceSpec:
+    """A device type (``"cuda"``, ``"cpu"`` or ``"*"``) and, optionally, an inclusive compute-capability range."""
+
     type: str
     min_capability: tuple[int, int] | None = None
     max_capability: tuple[int, int] | None = None
 
     def matches(self, platform: Platform) -> bool:
-        if self.type not in ("*", platform.device_type):
+        if self.type != "*" and self.type != platform.device_type:
             return False
-        if self.min_capability is None and self.max_capability is None:
+        bounded = self.min_capability is not None or self.max_capability is not None
+        if not bounded:
             return True
-        cap = platform.capability
-        if cap is None or (self.min_capability is not None and cap < self.min_capability):
+        have = platform.capability
+        if have is None:
             return False
-        return self.max_capability is None or cap <= self.max_capability
+        above = self.min_capability is None or have >= self.min_capability
+        below = self.max_capability is None or have <= self.max_capability
+        return above and below
 
     @property
     def span(self) -> float:
+        """Width of the capability range in (major * 100 + minor) units; a wildcard device is infinitely wide."""
         if self.type == "*":
             return float("inf")
-        lo, hi = self.min_capability or (0, 0), self.max_capability or (99, 99)
-        return (hi[0] * 100 + hi[1]) - (lo[0] * 100 + lo[1])
+        low = self.min_capability if self.min_capability is not None else (0, 0)
+        high = self.max_capability if self.max_capability is not None else (99, 99)
+        return (100 * high[0] + high[1]) - (100 * low[0] + low[1])
 
 
 @dataclass
@@ -65,120 +81,150 @@ class Impl:
     def opt_in(self) -> bool:
         return self.priority < 0
 
+    @property
+    def rank(self) -> tuple:
+        """Sort key: better implementations first."""
+        return (-self.priority, self.device.span, self.order)
+
     def available(self, platform: Platform) -> bool:
         return self.device.matches(platform) and platform.supports(*self.requires)
 
+    def accepts(self, args: tuple, kwargs: dict) -> bool:
+        return self.when is None or bool(self.when(*args, **kwargs))
+
     def rejection(self, platform: Platform, args: tuple, kwargs: dict) -> str | None:
+        """Why this implementation does not serve the call; ``None`` when it would."""
         if not self.device.matches(platform):
-            return f"device {self.device} does not match {platform.device_type} {platform.arch}".rstrip()
-        missing = sorted(f.value for f in self.requires if not platform.supports(f))
-        if missing:
-            return "missing features " + ",".join(missing)
-        if self.when is not None and not self.when(*args, **kwargs):
-            return "when() rejected the arguments"
+            return f"registered for {self.device}, the call is on {platform.device_type} {platform.arch}".rstrip()
+        lacking = sorted(feature.value for feature in self.requires if not platform.supports(feature))
+        if lacking:
+            return "missing features " + ",".join(lacking)
+        if not self.accepts(args, kwargs):
+            return "its when() predicate declined these arguments"
         return None
 
 
-class _Config:
+# ---- overrides by name -----------------------------------------------------------------------------------------------
+
+
+class _Overrides:
+    """Process-wide switches: ops whose implementations are all off, ops forced to one implementation, strict mode."""
+
     def __init__(self) -> None:
-        self.disabled: set[str] = set()
+        self.off: set[str] = set()
         self.forced: dict[str, str] = {}
         self.strict = False
 
+    def parse(self, text: str | None) -> None:
+        off, forced = set(), {}
+        for item in (text or "").split(","):
+            item = item.strip()
+            if item == "" or item[0] == "+":  # "+op" = leave enabled (the default): accepted for symmetry
+                continue
+            if item[0] == "-":
+                off.add(item[1:])
+                continue
+            op_name, colon, impl_name = item.partition(":")
+            if not colon:
+                raise ValueError(f"cannot read op override {item!r}: write -op to disable or op:impl to force")
+            forced[op_name] = impl_name
+        self.off, self.forced = off, forced
 
-_CONFIG = _Config()
-OPS: dict[str, "Op"] = {}
+
+_OVERRIDES = _Overrides()
 
 
 def configure(spec: str | None) -> None:
-    """Apply a ``FLASHIM_OPS``-style string: ``-op`` disables an op's implementations, ``op:impl`` forces one."""
-    _CONFIG.disabled.clear()
-    _CONFIG.forced.clear()
-    for token in (spec or "").split(","):
-        token = token.strip()
-        if not token or token.startswith("+"):
-            continue
-        if token.startswith("-"):
-            _CONFIG.disabled.add(token[1:])
-        elif ":" in token:
-            op, impl = token.split(":", 1)
-            _CONFIG.forced[op] = impl
-        else:
-            raise ValueError(f"Invalid FLASHIM_OPS token {token!r}")
+    """Replace the name overrides: ``"-op"`` turns an op's implementations off, ``"op:impl"`` forces one (``op:reference``
+    forces the fall-back), comma-separated. ``None`` or ``""`` clears them."""
+    _OVERRIDES.parse(spec)
 
 
 def set_strict(strict: bool) -> None:
-    _CONFIG.strict = strict
+    _OVERRIDES.strict = bool(strict)
 
 
 configure(os.environ.get("FLASHIM_OPS"))
-set_strict(os.environ.get("FLASHIM_STRICT_OPS", "0") == "1")
+set_strict(os.environ.get("FLASHIM_STRICT_OPS") == "1")
 
 
-def _first_device(values: Iterable) -> torch.device | None:
+def _device_of(values: Iterable) -> torch.device | None:
+    """The device of the first tensor found in the arguments, looking into sequences and dataclass containers."""
     for value in values:
         if isinstance(value, torch.Tensor):
             return value.device
-        if is_dataclass(value) and not isinstance(value, type):
-            value = [getattr(value, f.name) for f in fields(value)]
+        if dataclasses.is_dataclass(value) and not isinstance(value, type):
+            value = [getattr(value, f.name) for f in dataclasses.fields(value)]
         if isinstance(value, (list, tuple)):
-            found = _first_device(value)
-            if found is not None:
-                return found
+            inner = _device_of(value)
+            if inner is not None:
+                return inner
     return None
+
+
+# ---- the op ----------------------------------------------------------------------------------------------------------
 
 
 class Op:
     def __init__(self, name: str, reference: Callable | None = None, *, doc: str = "") -> None:
         if name in OPS:
-            raise ValueError(f"Duplicate op {name!r}")
+            raise ValueError(f"an op named {name!r} is already declared")
         self.name = name
         self.reference = reference
         self.impls: list[Impl] = []
         self.calls: Counter = Counter()
-        self.__doc__ = doc or (reference.__doc__ if reference is not None else None)
+        self.__doc__ = doc or getattr(reference, "__doc__", None)
         OPS[name] = self
 
+    def __repr__(self) -> str:
+        return f"Op({self.name}: {', '.join(i.name for i in self.impls) or 'no impls'})"
+
+    # -- registration ------------------------------------------------------------------------------------------------
     def register(self, name: str, *, device: DeviceSpec, requires: Iterable[Feature] = (), priority: int = 0,
                  when: Callable[..., bool] | None = None) -> Callable[[Callable], Callable]:
-        if name == REFERENCE or any(i.name == name for i in self.impls):
-            raise ValueError(f"Duplicate impl {name!r} for op {self.name!r}")
+        if name == REFERENCE or name in {impl.name for impl in self.impls}:
+            raise ValueError(f"op {self.name!r} already has an implementation named {name!r}")
 
-        def decorator(fn: Callable) -> Callable:
-            self.impls.append(Impl(name, fn, device, frozenset(requires), priority, when, len(self.impls)))
+        def attach(fn: Callable) -> Callable:
+            self.impls.append(Impl(name, fn, device, frozenset(requires), priority, when, order=len(self.impls)))
             return fn
 
-        return decorator
+        return attach
 
-    def candidates(self, platform: Platform) -> list[Impl]:
-        usable = [i for i in self.impls if i.available(platform)]
-        return sorted(usable, key=lambda i: (-i.priority, i.device.span, i.order))
-
-    def _platform(self, args: tuple, kwargs: dict) -> Platform:
-        return platform_for(_first_device(args) or _first_device(kwargs.values()) or torch.device("cpu"))
-
-    def _find(self, name: str) -> Impl:
+    def _named(self, name: str) -> Impl:
         for impl in self.impls:
             if impl.name == name:
                 return impl
-        raise ValueError(f"Op {self.name!r} has no impl {name!r} (registered: {[i.name for i in self.impls]})")
+        raise ValueError(f"op {self.name!r} has no implementation {name!r}; registered: {[i.name for i in self.impls]}")
+
+    # -- selection ---------------------------------------------------------------------------------------------------
+    def candidates(self, platform: Platform) -> list[Impl]:
+        """Implementations usable on ``platform``, best first (the per-call ``when`` predicates are not consulted)."""
+        return sorted((impl for impl in self.impls if impl.available(platform)), key=lambda impl: impl.rank)
+
+    def _platform(self, args: tuple, kwargs: dict) -> Platform:
+        device = _device_of(args) or _device_of(kwargs.values()) or torch.device("cpu")
+        return platform_for(device)
 
     def _choose(self, args: tuple, kwargs: dict, pin: str | None = None, strict: bool = True) -> Impl | None:
-        forced = _CONFIG.forced.get(self.name)
-        if forced == REFERENCE or self.name in _CONFIG.disabled:
+        """The implementation that serves the call, or ``None`` for the fall-back. Precedence: the name overrides, then a
+        pin (``get(name)``), then the ranking."""
+        forced = _OVERRIDES.forced.get(self.name)
+        if self.name in _OVERRIDES.off or forced == REFERENCE:
             return None
         if forced is not None:
-            return self._find(forced)
+            return self._named(forced)
         if pin == REFERENCE:
             return None
         platform = self._platform(args, kwargs)
-        for impl in [self._find(pin)] if pin is not None else self.candidates(platform):
-            if not impl.available(platform) or (pin is None and impl.opt_in):
-                continue
-            if impl.when is None or impl.when(*args, **kwargs):
+        if pin is not None:
+            impl = self._named(pin)
+            return impl if impl.available(platform) and impl.accepts(args, kwargs) else None
+        for impl in self.candidates(platform):
+            if not impl.opt_in and impl.accepts(args, kwargs):
                 return impl
-        if pin is None and strict and _CONFIG.strict and platform.device_type != "cpu":
-            raise RuntimeError(f"Op {self.name!r} fell back to the reference on {platform.describe()}")
+        if strict and _OVERRIDES.strict and platform.device_type != "cpu":
+            raise RuntimeError(f"op {self.name!r}: strict mode, and nothing but the fall-back applies on {platform.describe()}")
         return None
 
     def supports(self, *args, **kwargs) -> bool:
@@ -186,56 +232,62 @@ class Op:
 
     def select(self, *args, **kwargs) -> tuple[str, Callable | None]:
         impl = self._choose(args, kwargs)
-        return (REFERENCE, self.reference) if impl is None else (impl.name, impl.fn)
+        if impl is None:
+            return REFERENCE, self.reference
+        return impl.name, impl.fn
 
     def explain(self, *args, **kwargs) -> dict[str, str]:
+        """Per implementation (best first, unavailable ones last): ``"selected"``, the reason it was passed over, or
+        ``"outranked"``; plus a ``"reference"`` entry for the fall-back."""
         platform = self._platform(args, kwargs)
-        chosen = self._choose(args, kwargs, strict=False)
-        ranked = self.candidates(platform)
-        ranked += [i for i in self.impls if i not in ranked]
-        report = {}
-        for impl in ranked:
-            if chosen is not None and impl.name == chosen.name:
+        winner = self._choose(args, kwargs, strict=False)
+        usable = self.candidates(platform)
+        listing = usable + [impl for impl in self.impls if impl not in usable]
+        report: dict[str, str] = {}
+        for impl in listing:
+            if winner is not None and impl.name == winner.name:
                 report[impl.name] = "selected"
-            else:
-                fallback = "opt-in (negative priority): pin it" if impl.opt_in else "lower priority"
-                report[impl.name] = impl.rejection(platform, args, kwargs) or fallback
-        report[REFERENCE] = ("selected" if self.reference is not None else "none shipped: the call raises") \
-            if chosen is None else "fallback"
+                continue
+            reason = impl.rejection(platform, args, kwargs)
+            if reason is None:
+                reason = "opt-in (negative priority): ask for it by name" if impl.opt_in else "outranked"
+            report[impl.name] = reason
+        if winner is not None:
+            report[REFERENCE] = "fallback"
+        else:
+            report[REFERENCE] = "selected" if self.reference is not None else "none shipped: the call raises"
         return report
 
+    # -- calling -----------------------------------------------------------------------------------------------------
     def _run(self, impl: Impl | None, args: tuple, kwargs: dict):
-        if impl is None:
-            if self.reference is None:
-                platform = self._platform(args, kwargs)
-                reasons = "; ".join(f"{i.name}: {i.rejection(platform, args, kwargs) or 'forced off'}" for i in self.impls)
-                raise NoImplementation(
-                    f"op {self.name!r}: no implementation applies on {platform.describe()} ({reasons or 'none registered'}) "
-                    "and flashim_b200 ships no fallback"
-                )
-            name, fn = REFERENCE, self.reference
+        if impl is not None:
+            label, fn = impl.name, impl.fn
+        elif self.reference is not None:
+            label, fn = REFERENCE, self.reference
         else:
-            name, fn = impl.name, impl.fn
+            platform = self._platform(args, kwargs)
+            why = "; ".join(f"{i.name}: {i.rejection(platform, args, kwargs) or 'forced off'}" for i in self.impls)
+            raise NoImplementation(f"op {self.name!r}: no implementation applies on {platform.describe()} "
+                                   f"({why or 'none registered'}) and flashim_b200 ships no fallback")
         if not torch.compiler.is_compiling():
-            self.calls[name] += 1
+            self.calls[label] += 1
         return fn(*args, **kwargs)
 
     def __call__(self, *args, **kwargs):
         return self._run(self._choose(args, kwargs), args, kwargs)
 
     def get(self, name: str | None) -> Callable:
+        """The op pinned to one implementation (``None``: the dispatching op itself). A pinned implementation whose
+        device or predicate does not fit the call hands over to the fall-back, as in FlashIM."""
         if name is None:
             return self
         if name != REFERENCE:
-            self._find(name)
+            self._named(name)  # raise now for a name that does not exist
 
         def pinned(*args, **kwargs):
             return self._run(self._choose(args, kwargs, pin=name), args, kwargs)
 
         return pinned
-
-    def __repr__(self) -> str:
-        return f"Op({self.name}: {', '.join(i.name for i in self.impls) or 'no impls'})"
 
 
 def reset_call_counts() -> None:
@@ -244,4 +296,6 @@ def reset_call_counts() -> None:
 
 
 def call_counts() -> dict[str, dict[str, int]]:
-    return {name: dict(op.calls) for name, op in OPS.items() if op.calls}
+    """``{op: {implementation: calls}}`` for the ops called since the last reset (calls traced by torch.compile are not
+    counted)."""
+    return {op.name: dict(op.calls) for op in OPS.values() if sum(op.calls.values())}

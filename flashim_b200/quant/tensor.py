@@ -1,9 +1,11 @@
-"""Quantized tensor containers and the load-time weight packing of the conv path.
+"""Containers for quantised operands and the load-time packing of conv weights.
 
-Same containers and field names as FlashIM (flashim/quant/tensor.py:16-145) so modules written against them work
-unchanged: ``QuantizedTensor`` (E4M3 activations + one static exponent per 32 channels), ``QuantizedWeight`` (E4M3
-``[N, K]`` + one exponent per (row, 32 inputs)), ``Int8Tensor``. Weight packing runs once when a model is built, in
-torch on the weights' own device; activations are only ever quantized by the CUDA kernels.
+The three containers carry the field names FlashIM's carry (flashim/quant/tensor.py:16-145: ``values`` /
+``scale_exponent`` / ``logical_shape``, ``values`` / ``scale``) so a module written against those reads these the same
+way: ``QuantizedTensor`` is an E4M3 activation whose 32-channel blocks share one static power-of-two scale across all
+rows, ``QuantizedWeight`` an E4M3 ``[N, K]`` matrix with a scale per (row, 32 inputs), ``Int8Tensor`` int8 values under
+one fp32 scale. Packing a weight happens once, when a model is built, in torch on the weight's own device; activations
+are only ever quantised by the CUDA kernels.
 """
 
 from __future__ import annotations
@@ -12,62 +14,90 @@ import math
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 from torch import Tensor
 
-BLOCK = 32
-FP8_MAX = 448.0
+BLOCK = 32          # elements that share one E8M0 scale
+FP8_MAX = 448.0     # largest finite E4M3 magnitude
 INT8_MAX = 127.0
+_SCALE_TILE_ROWS, _SCALE_TILE_GROUPS = 128, 4  # one 512-byte tile of the swizzled scale layout
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return (value + multiple - 1) // multiple * multiple
 
 
 def padded_channels(channels: int) -> int:
-    return -(-channels // BLOCK) * BLOCK
+    """Channels as stored: the next multiple of the 32-element block."""
+    return _round_up(channels, BLOCK)
+
+
+# ---- E8M0 scales -----------------------------------------------------------------------------------------------------
 
 
 def scale_exponent_from_amax(amax: Tensor) -> Tensor:
-    """int8 exponent ``clamp(ceil(log2(amax / 448)))``, ``-127`` for zero (flashim/quant/formats/mx.py:22-26)."""
-    e = torch.ceil(torch.log2(amax / FP8_MAX))
-    e = torch.where(amax == 0, torch.full_like(e, -127.0), e)
-    return e.clamp(-127, 127).to(torch.int8)
+    """The int8 exponent ``e`` with ``amax / 2**e <= 448``, i.e. ``ceil(log2(amax / 448))`` in fp32, limited to
+    [-127, 127]; an all-zero block gets -127 (the rule of flashim/quant/formats/mx.py:22-26)."""
+    exponent = torch.log2(amax.float() / FP8_MAX).ceil()
+    exponent = exponent.masked_fill(amax == 0, -127.0)
+    return exponent.clamp_(-127.0, 127.0).to(torch.int8)
 
 
 def exponent_to_e8m0(exponent: Tensor) -> Tensor:
-    """Biased E8M0 bytes (uint8) of int8 exponents."""
+    """int8 exponents -> the biased bytes E8M0 stores (uint8, bias 127)."""
     return (exponent.to(torch.int16) + 127).to(torch.uint8)
 
 
-def swizzle_scales(exponent: Tensor) -> Tensor:
-    """``[rows, groups]`` int8 exponents -> flat uint8 E8M0 bytes in 512-byte tiles of 128 rows x 4 groups (32 rows of 16
-    bytes: row ``r % 32``, then ``(r % 128) // 32``, then group), zero padded: the layout tcgen05.cp moves to tensor
-    memory unchanged and cuBLAS calls SWIZZLE_32_4_4 (flashim/quant/formats/mx.py:67-86)."""
-    raw = exponent_to_e8m0(exponent)
-    rows, groups = raw.shape
-    pr, pg = -(-rows // 128) * 128, -(-groups // 4) * 4
-    padded = torch.zeros((pr, pg), dtype=torch.uint8, device=raw.device)
-    padded[:rows, :groups] = raw
-    return padded.view(pr // 128, 4, 32, pg // 4, 4).permute(0, 3, 2, 1, 4).reshape(-1).contiguous()
-
-
 def swizzled_scale_bytes(rows: int, groups: int) -> int:
-    return (-(-rows // 128)) * (-(-groups // 4)) * 512
+    """Size of the swizzled layout of a ``[rows, groups]`` scale matrix: whole 128 x 4 tiles of 512 bytes."""
+    return (_round_up(rows, _SCALE_TILE_ROWS) // _SCALE_TILE_ROWS) * (_round_up(groups, _SCALE_TILE_GROUPS) // _SCALE_TILE_GROUPS) * 512
+
+
+def swizzle_scales(exponent: Tensor) -> Tensor:
+    """``[rows, groups]`` int8 exponents -> flat E8M0 bytes in the tiled order the tensor cores read.
+
+    The matrix is cut into tiles of 128 rows x 4 groups (zero-padded at the edges); a tile is stored as 32 lines of 16
+    bytes, line ``r % 32`` holding, for the four 32-row quarters ``q = (r % 128) // 32`` in turn, the 4 group bytes of row
+    ``32 q + r % 32``. Tiles follow each other group-tile fastest. ``tcgen05.cp.32x128b.warpx4`` moves such a tile into
+    4 tensor-memory columns unchanged; cuBLAS names the order SWIZZLE_32_4_4 and FlashIM's ``swizzle_scales`` produces
+    it (flashim/quant/formats/mx.py:67-86)."""
+    rows, groups = exponent.shape
+    tall, wide = _round_up(rows, _SCALE_TILE_ROWS), _round_up(groups, _SCALE_TILE_GROUPS)
+    plane = exponent.new_zeros((tall, wide), dtype=torch.uint8)
+    plane[:rows, :groups] = exponent_to_e8m0(exponent)
+    # axes: row tile, quarter, line, group tile, group  ->  row tile, group tile, line, quarter, group
+    tiles = plane.reshape(tall // _SCALE_TILE_ROWS, 4, 32, wide // _SCALE_TILE_GROUPS, _SCALE_TILE_GROUPS)
+    return tiles.permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
+
+
+def _apply_block_scales(values: Tensor, exponent: Tensor) -> Tensor:
+    """``values [R, K]`` (E4M3) times ``2**exponent`` per 32-element block; ``exponent`` is ``[K/32]`` or ``[R, K/32]``."""
+    rows, width = values.shape
+    scale = torch.exp2(exponent.float()).unsqueeze(-1)
+    return (values.float().reshape(rows, width // BLOCK, BLOCK) * scale).reshape(rows, width)
+
+
+# ---- containers ------------------------------------------------------------------------------------------------------
 
 
 @dataclass(frozen=True)
 class QuantizedTensor:
+    """E4M3 ``[*leading, Cp]`` with ``Cp`` the padded channel count, one int8 exponent per 32 channels shared by every
+    row, and the unpadded shape the values stand for."""
+
     values: Tensor
     scale_exponent: Tensor
     logical_shape: tuple[int, ...]
 
     def __post_init__(self) -> None:
         if self.values.dtype != torch.float8_e4m3fn:
-            raise ValueError(f"Expected float8_e4m3fn values, got {self.values.dtype}")
+            raise ValueError(f"QuantizedTensor.values must be float8_e4m3fn, not {self.values.dtype}")
         if self.scale_exponent.dtype != torch.int8:
-            raise ValueError("scale_exponent must be int8 unbiased exponents")
-        channels = self.values.shape[-1]
-        if channels % BLOCK or channels < self.logical_shape[-1]:
-            raise ValueError(f"Bad physical channels {channels} for {self.logical_shape}")
-        if tuple(self.scale_exponent.shape) != (channels // BLOCK,):
-            raise ValueError(f"Expected scale shape {(channels // BLOCK,)}")
+            raise ValueError(f"QuantizedTensor.scale_exponent holds int8 exponents, not {self.scale_exponent.dtype}")
+        stored = self.values.shape[-1]
+        if stored % BLOCK != 0 or stored < self.logical_shape[-1]:
+            raise ValueError(f"{stored} stored channels cannot hold logical shape {self.logical_shape} in blocks of {BLOCK}")
+        if self.scale_exponent.shape != (stored // BLOCK,):
+            raise ValueError(f"{stored} channels need {stored // BLOCK} exponents, got shape {tuple(self.scale_exponent.shape)}")
 
     @property
     def device(self) -> torch.device:
@@ -82,16 +112,18 @@ class QuantizedTensor:
         return math.prod(self.values.shape[:-1])
 
     def matrix(self) -> Tensor:
-        return self.values.reshape(-1, self.channels)
+        """The values as ``[rows, Cp]``."""
+        return self.values.reshape(self.rows, self.channels)
 
     def dequantize(self, dtype: torch.dtype = torch.float32) -> Tensor:
-        blocks = self.values.reshape(self.rows, self.channels // BLOCK, BLOCK).float()
-        dense = (blocks * torch.exp2(self.scale_exponent.float())[..., None]).reshape(self.rows, -1)
+        dense = _apply_block_scales(self.matrix(), self.scale_exponent)
         return dense[:, : self.logical_shape[-1]].reshape(self.logical_shape).to(dtype)
 
 
 @dataclass(frozen=True)
 class QuantizedWeight:
+    """E4M3 ``[Np, Kp]`` (both padded to 32) with int8 exponents ``[Np, Kp / 32]``."""
+
     values: Tensor
     scale_exponent: Tensor
     logical_shape: tuple[int, int]
@@ -106,45 +138,50 @@ class QuantizedWeight:
 
     @classmethod
     def from_float(cls, weight: Tensor) -> "QuantizedWeight":
-        """Pad both dimensions to 32, one exponent per (row, 32 inputs), ``w / 2**e`` saturated, E4M3
-        (flashim/quant/tensor.py:76-87)."""
-        if weight.ndim != 2:
-            raise ValueError(f"Unsupported weight shape: {tuple(weight.shape)}")
-        if not torch.isfinite(weight).all():
-            raise ValueError("Cannot quantize non-finite weights")
-        n, k = padded_channels(weight.shape[0]), padded_channels(weight.shape[1])
-        blocks = F.pad(weight.float(), (0, k - weight.shape[1], 0, n - weight.shape[0])).reshape(n, k // BLOCK, BLOCK)
-        exponent = scale_exponent_from_amax(blocks.abs().amax(dim=-1))
-        q = (blocks / torch.exp2(exponent.float())[..., None]).clamp(-FP8_MAX, FP8_MAX)
-        return cls(q.reshape(n, k).to(torch.float8_e4m3fn), exponent, tuple(weight.shape))
+        """Quantise a dense ``[N, K]`` matrix: zero-pad to multiples of 32, take each (row, 32 inputs) block's exponent
+        from its largest magnitude, divide, saturate at +-448 and round to E4M3 (as flashim/quant/tensor.py:76-87)."""
+        if weight.dim() != 2:
+            raise ValueError(f"a weight matrix has two dimensions; got shape {tuple(weight.shape)}")
+        if not bool(torch.isfinite(weight).all()):
+            raise ValueError("the weight contains inf or nan and cannot be quantised")
+        n, k = weight.shape
+        stored = weight.new_zeros((padded_channels(n), padded_channels(k)), dtype=torch.float32)
+        stored[:n, :k] = weight
+        blocks = stored.unflatten(1, (-1, BLOCK))
+        exponent = scale_exponent_from_amax(blocks.abs().amax(dim=2))
+        scaled = (blocks / torch.exp2(exponent.float()).unsqueeze(-1)).clamp_(-FP8_MAX, FP8_MAX)
+        return cls(scaled.flatten(1).to(torch.float8_e4m3fn), exponent, (n, k))
 
     @classmethod
     def from_conv(cls, weight: Tensor) -> "QuantizedWeight":
-        """``[Cout, Cin, kh, kw]`` -> K order ``(ky, kx, c)`` with ``Cin`` padded to 32 per tap
+        """A conv weight ``[Cout, Cin, kh, kw]`` as the GEMM operand of the implicit-GEMM conv: taps outermost, channels
+        innermost along K — ``(ky, kx, c)`` — with ``Cin`` zero-padded to 32 inside every tap
         (flashim/quant/methods/conv2d.py:193-205)."""
-        cout, cin = weight.shape[:2]
-        w = F.pad(weight.detach().permute(0, 2, 3, 1), (0, padded_channels(cin) - cin))
-        return cls.from_float(w.reshape(cout, -1))
+        cout, cin, kh, kw = weight.shape
+        taps_last = weight.detach().new_zeros((cout, kh, kw, padded_channels(cin)))
+        taps_last[..., :cin] = weight.detach().movedim(1, -1)
+        return cls.from_float(taps_last.flatten(1))
 
     def swizzled_scales(self) -> Tensor:
         return swizzle_scales(self.scale_exponent)
 
     def dequantize(self, dtype: torch.dtype = torch.float32) -> Tensor:
-        blocks = self.values.reshape(self.out_features, self.in_features // BLOCK, BLOCK).float()
-        dense = (blocks * torch.exp2(self.scale_exponent.float())[..., None]).reshape(self.out_features, self.in_features)
+        dense = _apply_block_scales(self.values, self.scale_exponent)
         return dense[: self.logical_shape[0], : self.logical_shape[1]].to(dtype)
 
 
 @dataclass(frozen=True)
 class Int8Tensor:
+    """int8 values under one fp32 scale (``value = code * scale``)."""
+
     values: Tensor
     scale: Tensor
 
     def __post_init__(self) -> None:
         if self.values.dtype != torch.int8:
-            raise ValueError(f"Expected int8 values, got {self.values.dtype}")
+            raise ValueError(f"Int8Tensor.values must be int8, not {self.values.dtype}")
         if self.scale.dtype != torch.float32 or self.scale.numel() != 1:
-            raise ValueError("scale must be a single FP32 value")
+            raise ValueError("Int8Tensor.scale is one float32 number")
 
     @property
     def logical_shape(self) -> tuple[int, ...]:
@@ -157,18 +194,22 @@ class Int8Tensor:
         return (self.values.float() * self.scale).to(dtype)
 
 
-_EPS = torch.finfo(torch.float32).eps
+# ---- INT8 conv weights -----------------------------------------------------------------------------------------------
 
 
 def safe_scale(scale: Tensor) -> Tensor:
+    """Scales that are zero, negative, tiny or non-finite become fp32 epsilon, so a division by them stays finite."""
     scale = scale.float()
-    return torch.where(torch.isfinite(scale) & (scale > _EPS), scale, torch.full_like(scale, _EPS))
+    floor = torch.finfo(torch.float32).eps
+    usable = torch.isfinite(scale) & (scale > floor)
+    return torch.where(usable, scale, scale.new_full((), floor))
 
 
 def int8_weight_from_conv(weight: Tensor) -> tuple[Tensor, Tensor]:
-    """``[Cout, Cin, kh, kw]`` -> int8 ``[Cout, kh*kw*Cin]`` (ky, kx, c) and fp32 per-row scales ``amax / 127``
-    (flashim/quant/methods/conv2d.py:91-100, flashim/quant/formats/int8.py:19-26)."""
-    w = weight.detach().permute(0, 2, 3, 1).reshape(weight.shape[0], -1)
-    scale = safe_scale(w.float().abs().amax(dim=1) / INT8_MAX)
-    q = (w.float() / scale[:, None]).round().clamp(-INT8_MAX, INT8_MAX).to(torch.int8)
-    return q.contiguous(), scale
+    """A conv weight ``[Cout, Cin, kh, kw]`` -> int8 ``[Cout, kh * kw * Cin]`` in ``(ky, kx, c)`` order and one fp32
+    scale per output channel, ``max|w| / 127`` (flashim/quant/methods/conv2d.py:91-100,
+    flashim/quant/formats/int8.py:19-26)."""
+    rows = weight.detach().movedim(1, -1).flatten(1).float()
+    scale = safe_scale(rows.abs().amax(dim=1) / INT8_MAX)
+    codes = torch.round(rows / scale.unsqueeze(1)).clamp_(-INT8_MAX, INT8_MAX)
+    return codes.to(torch.int8).contiguous(), scale
