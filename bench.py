@@ -415,22 +415,19 @@ class StackWorkload(Workload):
         return sum(x.numel() * 2 for x in self.staging), sum(x.numel() * 2 for x in self.result_host)
 
     def roofline(self, steps):
-        # dominant kernel of the stack by time: the 1x1 MXFP8 conv C->2C of the 400x400x128 level (HBM-bound)
+        # dominant kernel of the stack by device time (38 % in the ncu launch list): the depthwise 5x5 + GELU -> MXFP8
+        # producer, timed on its largest level (400 x 400 x 128, one chunk of images)
         from flashim_b200 import ops
 
-        level = self.model.levels[-1]
-        block = level.blocks[0]
+        block = self.model.levels[-1].blocks[0]
         size, c = self.levels[-1]
         n = min(self.model.chunk, self.inputs[-1].shape[0])
-        x = self.inputs[-1][:n]
-        q, s = ops.depthwise5x5_act_mxfp8(x.permute(0, 3, 1, 2), block.dw_weight, block.dw_bias, "gelu")
-        q = q.view(n, size, size, c)
-        ms = _time_launches(lambda: block.up(q, s, act="gelu", dynamic_out=True), max(steps, 10))
-        pixels = n * size * size
-        algorithmic = pixels * (c + c / 32 + 2 * c + 2 * c / 32) + 2 * c * c  # E4M3 in + scales, E4M3 out + scales, weights
+        x = self.inputs[-1][:n].permute(0, 3, 1, 2)
+        ms = _time_launches(lambda: ops.depthwise5x5_act_mxfp8(x, block.dw_weight, block.dw_bias, "gelu"), max(steps, 10))
+        algorithmic = n * size * size * c * (2 + 1 + 1 / 32)  # bf16 in, E4M3 + E8M0 out
         peak, source = peaks()
         achieved = algorithmic / 1e9 / (ms * 1e-3)
-        return {"bound": "hbm", "kernel": "conv_kernel<mxfp8> 1x1 128->256 +gelu+requant", "achieved": achieved,
+        return {"bound": "hbm", "kernel": "dw5x5_kernel<mxfp8, gelu> 400x400x128", "achieved": achieved,
                 "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": achieved / peak["hbm_gbs"], "traffic": _traffic(self.name),
                 "launch_ms": ms, "peak_source": f"hbm_gbs of {source}"}
 
@@ -458,9 +455,9 @@ DEFAULT_WORKLOAD = "stack"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel, from the ncu
 # captures summarised under profiles/ (file named beside each figure); None where no capture exists.
 NCU_TRAFFIC: dict[str, float] = {
-    # conv_kernel 1x1 128 -> 256 + GELU + requant on 8 x 400 x 400 (the launch the stack's roofline times), same shape for
-    # every --pairs >= 4: profiles/conv_mxfp8_1x1_up_refiner_level_400x400x128.md (169.05 MB read + 284.43 MB written)
-    "refiner-stack": 453.48e6,
+    # dw5x5_kernel depthwise + GELU -> MXFP8 on 8 x 400 x 400 x 128 (the launch the stack's roofline times), same shape for
+    # every --pairs >= 4: profiles/depthwise_mxfp8_refiner_level_400x400x128.md (418.54 MB read + 153.63 MB written)
+    "refiner-stack": 572.17e6,
     # profiles/conv_mxfp8_3x3_100x100x512.md (22.99 MB read; the 20 MB output is still in L2 when the kernel ends)
     "mxfp8-conv-100x100x512-k3": 23.01e6,
     # profiles/conv_int8_3x3_100x100x256.md
