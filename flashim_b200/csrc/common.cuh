@@ -495,8 +495,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-// On a packed pair, arranged for issue slots: 0.5 x + 0.5 |x| (1 - c) with c = erfc(|x| / sqrt 2) avoids the
-// sign select, and the two MUFU operations per lane take their operands straight from the halves of the pair.
+// On a packed pair, arranged for issue slots (11 packed operations, 2 MUFU per element): with q = 1/2 - c/2 and
+// c = erfc(|x| / sqrt 2) the value is x/2 + |x| q, which needs no sign select; the polynomial carries the factor -1/2, so
+// q is one fma on the exponential, and the MUFU operations take their operands straight from the halves of the pair.
 __device__ __forceinline__ uint64_t gelu_fast2(uint64_t x2) {
   float x0, x1;
   unpack2(x2, x0, x1);
@@ -504,16 +505,14 @@ __device__ __forceinline__ uint64_t gelu_fast2(uint64_t x2) {
   float d0, d1;
   unpack2(fma2(pack2(0.23164190f, 0.23164190f), ax, pack2(1.0f, 1.0f)), d0, d1);  // 1 + 0.3275911 |x| / sqrt 2
   const uint64_t t = pack2(rcp_approx(d0), rcp_approx(d1));
-  uint64_t poly = fma2(pack2(1.061405429f, 1.061405429f), t, pack2(-1.453152027f, -1.453152027f));
-  poly = fma2(poly, t, pack2(1.421413741f, 1.421413741f));
-  poly = fma2(poly, t, pack2(-0.284496736f, -0.284496736f));
-  poly = fma2(poly, t, pack2(0.254829592f, 0.254829592f));
+  uint64_t poly = fma2(pack2(-0.5307027145f, -0.5307027145f), t, pack2(0.7265760135f, 0.7265760135f));  // -1/2 of A&S
+  poly = fma2(poly, t, pack2(-0.7107068705f, -0.7107068705f));
+  poly = fma2(poly, t, pack2(0.142248368f, 0.142248368f));
+  poly = fma2(poly, t, pack2(-0.127414796f, -0.127414796f));
   float a0, a1;
   unpack2(mul2(mul2(x2, x2), pack2(-0.72134752044448170f, -0.72134752044448170f)), a0, a1);  // -x^2 / 2 * log2(e)
-  const uint64_t c = mul2(mul2(poly, t), pack2(ex2_approx(a0), ex2_approx(a1)));
-  const uint64_t one_minus_c = fma2(c, pack2(-1.0f, -1.0f), pack2(1.0f, 1.0f));
-  const uint64_t half = pack2(0.5f, 0.5f);
-  return fma2(mul2(ax, half), one_minus_c, mul2(x2, half));
+  const uint64_t q = fma2(mul2(poly, t), pack2(ex2_approx(a0), ex2_approx(a1)), pack2(0.5f, 0.5f));
+  return fma2(ax, q, mul2(x2, pack2(0.5f, 0.5f)));
 }
 
 __device__ __forceinline__ float gelu_fast(float x) {

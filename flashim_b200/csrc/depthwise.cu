@@ -18,6 +18,14 @@
 namespace fim {
 namespace {
 
+// store only where `on` is non-zero, as a predicated instruction (no branch, the warp stays converged)
+__device__ __forceinline__ void store_if(uint32_t* at, uint32_t v, uint32_t on) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q st.global.b32 [%0], %1;\n\t}" ::"l"(at), "r"(v), "r"(on) : "memory");
+}
+__device__ __forceinline__ void store_if(uint16_t* at, uint16_t v, uint32_t on) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q st.global.b16 [%0], %1;\n\t}" ::"l"(at), "h"(v), "r"(on) : "memory");
+}
+
 constexpr int kChannels = 64;    // per CTA: one 128-byte line per pixel
 constexpr int kCols = 4;         // output columns per lane
 constexpr int kChunkRows = 5;    // input rows per ring chunk = accumulator slots
@@ -67,7 +75,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
     for (int j = 0; j < kCols; ++j) {
       float lo, hi;
       unpack2(v[j], lo, hi);
-      if (cols_ok & (1u << j)) out[j * pair_stride] = pack_bf16(lo, hi);
+      store_if(out + j * pair_stride, pack_bf16(lo, hi), cols_ok & (1u << j));
     }
   } else if (MODE == kOutMx) {
     // amax of each pixel over the 16 lanes of its 32-channel block by a transposing butterfly: after the exchanges lane
@@ -116,7 +124,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
       const float inv = __shfl_sync(0xffffffffu, inv_mine, half | ((j >> 1) & 1) | ((j & 1) << 1));
       float lo, hi;
       unpack2(mul2(v[j], pack2(inv, inv)), lo, hi);
-      if (cols_ok & (1u << j)) out[j * pair_stride] = e4m3x2(lo, hi);
+      store_if(out + j * pair_stride, e4m3x2(lo, hi), cols_ok & (1u << j));
     }
   } else {
     uint16_t* out = static_cast<uint16_t*>(out_row);
@@ -126,7 +134,8 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
       unpack2(v[j], lo, hi);
       const uint32_t rounded = pack_bf16(lo, hi);  // one packed conversion instead of two scalar ones
       const int qlo = int8_code(int8, bf16_lo(rounded)), qhi = int8_code(int8, bf16_hi(rounded));
-      if (cols_ok & (1u << j)) out[j * pair_stride] = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
+      const uint16_t codes = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
+      store_if(out + j * pair_stride, codes, cols_ok & (1u << j));
     }
   }
 }
@@ -222,12 +231,6 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[s][j] = 0ull;  // a slot is read for real only after its first multiply
 
-    uint64_t fin[kCols];  // the output row completed by the previous input row, with where it goes (mask 0: nowhere)
-    uint32_t fin_mask = 0;
-    uint8_t* fin_out = nullptr;
-    size_t fin_pixel = 0;
-#pragma unroll
-    for (int j = 0; j < kCols; ++j) fin[j] = 0ull;
     uint32_t s = 0, phase = 0;
     uint32_t raw[kCols + 4];  // bf16x2 words of the input row about to be used
     bool ok = !loads || mbar_wait_addr(full0, 0, &abort_flag, p.status, kStatusWaitRows);
@@ -291,7 +294,6 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
             for (int j = 0; j < kCols + 4; ++j) raw[j] = lds32(lane_smem + s_next * kChunkBytes + j * (kChannels * 2));
           }
         }
-        if (!(PROBE && (p.debug & 2))) emit_row<MODE, ACT>(p, fin, bias2, fin_out, fin_pixel, c, fin_mask, int8_scale, lane);
         if (!(PROBE && (p.debug & 1))) {
           // 100 packed FMAs: input row r = 5 g + ph feeds tap row ky of the output row in slot (ph - ky) mod 5. Tap column
           // outermost, so neighbouring instructions belong to 20 different accumulators and nothing waits on the FMA
@@ -311,16 +313,14 @@ __global__ void __launch_bounds__(32 * (WARPS + 1), 2) dw5x5_kernel(const __grid
 #pragma unroll
           for (int j = 0; j < kCols; ++j) acc[(ph + 1) % 5][j] = in[j] ^ in[j + 4];  // keep the loads alive
         }
-        // The output row in slot (ph + 1) mod 5 has now received all five input rows. It is finished (bias, activation,
-        // stores) beside the FMAs of the next input row: no branch separates the two, so they interleave, and a row that
-        // lies outside the span simply has an empty store mask.
+        // The output row in slot (ph + 1) mod 5 has now received all five input rows: finish it (bias, activation, stores)
+        // straight from its accumulators. Nothing branches here: a row outside the span has an empty store mask, so the
+        // compiler is free to overlap this epilogue with the FMAs of the next input row.
         {
           const bool valid = y_out >= y_base && y_out < y_end;
-#pragma unroll
-          for (int j = 0; j < kCols; ++j) fin[j] = acc[(ph + 1) % 5][j];
-          fin_mask = valid ? cols_ok : 0u;
-          fin_out = out_row;
-          fin_pixel = pixel0;
+          if (!(PROBE && (p.debug & 2))) {
+            emit_row<MODE, ACT>(p, acc[(ph + 1) % 5], bias2, out_row, pixel0, c, valid ? cols_ok : 0u, int8_scale, lane);
+          }
           pixel0 += valid ? static_cast<size_t>(p.width) : 0;
           out_row += valid ? row_pairs * kOutBytes : 0;
         }
