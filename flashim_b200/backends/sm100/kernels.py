@@ -200,6 +200,62 @@ def _(value, scale):
     return value.new_empty(value.shape, dtype=torch.int8)
 
 
+@torch.library.custom_op("flashim_b200::quantize_mxfp8_static_nchw", mutates_args=())
+def quantize_mxfp8_static_nchw(source: Tensor, exponent: Tensor) -> Tensor:
+    """``source`` NCHW-contiguous ``[B, C, H, W]`` -> E4M3 NHWC ``[B, H, W, Cp]`` (the quantiser does the layout change)."""
+    b, c, h, w = source.shape
+    out = torch.empty((b, h, w, padded_channels(c)), device=source.device, dtype=E4M3)
+    code = _native.library().fim_quantize_mxfp8_static_nchw(
+        source.data_ptr(), _IN_DTYPES[source.dtype], exponent.data_ptr(), out.data_ptr(), b, c, h * w, _stream(source))
+    _finish(code, f"quantize_mxfp8_static_nchw {tuple(source.shape)}", source.device)
+    return out
+
+
+@quantize_mxfp8_static_nchw.register_fake
+def _(source, exponent):
+    b, c, h, w = source.shape
+    return source.new_empty((b, h, w, padded_channels(c)), dtype=E4M3)
+
+
+@torch.library.custom_op("flashim_b200::quantize_int8_static_nchw", mutates_args=())
+def quantize_int8_static_nchw(source: Tensor, scale: Tensor) -> Tensor:
+    b, c, h, w = source.shape
+    out = torch.empty((b, h, w, c), device=source.device, dtype=torch.int8)
+    code = _native.library().fim_quantize_int8_static_nchw(
+        source.data_ptr(), _IN_DTYPES[source.dtype], scale.data_ptr(), out.data_ptr(), b, c, h * w, _stream(source))
+    _finish(code, f"quantize_int8_static_nchw {tuple(source.shape)}", source.device)
+    return out
+
+
+@quantize_int8_static_nchw.register_fake
+def _(source, scale):
+    b, c, h, w = source.shape
+    return source.new_empty((b, h, w, c), dtype=torch.int8)
+
+
+@torch.library.custom_op("flashim_b200::maxpool2_quantize_int8", mutates_args=())
+def maxpool2_quantize_int8(value: Tensor, scale: Tensor) -> Tensor:
+    """bf16 NHWC ``[B, H, W, C]`` -> int8 ``[B, H // 2, W // 2, C]``: MaxPool2d(2) and the static INT8 quantiser."""
+    b, h, w, c = value.shape
+    out = torch.empty((b, h // 2, w // 2, c), device=value.device, dtype=torch.int8)
+    code = _native.library().fim_maxpool2_quantize_int8(
+        value.data_ptr(), scale.data_ptr(), out.data_ptr(), b, h, w, c, _stream(value))
+    _finish(code, f"maxpool2_quantize_int8 {tuple(value.shape)}", value.device)
+    return out
+
+
+@maxpool2_quantize_int8.register_fake
+def _(value, scale):
+    b, h, w, c = value.shape
+    return value.new_empty((b, h // 2, w // 2, c), dtype=torch.int8)
+
+
+def _channels_first_view(value: Tensor) -> bool:
+    """``value`` is ``x.permute(0, 2, 3, 1)`` of an NCHW-contiguous ``x`` and not itself row-major — the case FlashIM's
+    quantisers read in place (flashim/backends/triton/quantize.py:237-239)."""
+    return value.ndim == 4 and not value.is_contiguous() and value.permute(0, 3, 1, 2).is_contiguous()
+
+
 # ---- custom ops: tcgen05 convs -----------------------------------------------------------------------------------------
 
 _OUT_DTYPES = {
@@ -425,6 +481,19 @@ def register(ops=None, device_spec=None, feature=None) -> None:
             residual, scale, kh, kw, ph, pw, dh, dw, act_code["relu" if relu else "none"],
             _native.OUT_BF16 if out_scale is None else _native.OUT_INT8)
 
+    if hasattr(ops, "int8_conv2d_maxpool"):
+        def pool_when(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, out_scale):
+            return (int8_when(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
+                    and _cuda(out_scale) and out_scale.numel() == 1 and weight.shape[0] % 8 == 0)
+
+        @ops.int8_conv2d_maxpool.register("sm100", device=spec, requires=requires, priority=3, when=pool_when)
+        def int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, out_scale):
+            # two launches: the conv writes its bf16 output (which the caller keeps), the pool reads it back (from L2 while
+            # it fits) and writes a quarter as many int8 codes
+            out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
+            scale = out_scale.to(device=x.device, dtype=torch.float32).reshape(1)
+            return out, maxpool2_quantize_int8(out, scale)
+
     if hasattr(ops, "int8_conv2d_accumulators"):
         def acc_when(x, weight, kh, kw, sh, sw, ph, pw, dh, dw):
             return (have() and _cuda(x, weight) and x.dtype == torch.int8 and weight.dtype == torch.int8
@@ -512,14 +581,16 @@ def register(ops=None, device_spec=None, feature=None) -> None:
     def quantize_when(value, scale_exponent):
         return (
             have() and _cuda(value, scale_exponent) and value.ndim >= 2 and value.dtype in _IN_DTYPES
-            and value.is_contiguous() and value.data_ptr() % 16 == 0
+            and ((value.is_contiguous() and value.data_ptr() % 16 == 0) or (_channels_first_view(value) and value.numel() > 0))
             and tuple(scale_exponent.shape) == (padded_channels(value.shape[-1]) // 32,)
         )
 
     @ops.quantize_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=quantize_when)
     def quantize_mxfp8(value, scale_exponent):
-        exponent = scale_exponent if scale_exponent.dtype == torch.int8 else scale_exponent.to(torch.int8)
-        return _make_quantized(quantize_mxfp8_static(value, exponent.contiguous()), scale_exponent, value)
+        exponent = (scale_exponent if scale_exponent.dtype == torch.int8 else scale_exponent.to(torch.int8)).contiguous()
+        if _channels_first_view(value):
+            return _make_quantized(quantize_mxfp8_static_nchw(value.permute(0, 3, 1, 2), exponent), scale_exponent, value)
+        return _make_quantized(quantize_mxfp8_static(value, exponent), scale_exponent, value)
 
     def _make_quantized(values, scale_exponent, value):
         qt = getattr(ops, "QuantizedTensor", None) or _quantized_tensor_type(ops)
@@ -527,12 +598,16 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         return qt(values, exponent, tuple(value.shape))
 
     def quantize_int8_when(value, scale, *, channel_scale=None):
+        row_major = value.is_contiguous() and value.data_ptr() % 16 == 0
+        channels_first = _channels_first_view(value) and value.numel() > 0 and value.shape[-1] % 16 == 0
         return (have() and channel_scale is None and _cuda(value, scale) and value.dtype in _IN_DTYPES
-                and value.is_contiguous() and value.data_ptr() % 16 == 0 and scale.numel() == 1)
+                and (row_major or channels_first) and scale.numel() == 1)
 
     @ops.quantize_int8.register("sm100", device=spec, requires=dw_requires, priority=3, when=quantize_int8_when)
     def quantize_int8(value, scale, *, channel_scale=None):
         scale32 = scale.to(device=value.device, dtype=torch.float32).reshape(())
+        if _channels_first_view(value):
+            return _int8_tensor_type(ops)(quantize_int8_static_nchw(value.permute(0, 3, 1, 2), scale32.reshape(1)), scale32)
         return _int8_tensor_type(ops)(quantize_int8_static(value, scale32.reshape(1)), scale32)
 
     if hasattr(ops, "quantize_mxfp8_dynamic"):

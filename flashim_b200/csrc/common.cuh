@@ -404,10 +404,15 @@ __device__ __forceinline__ int int8_code(float value, float scale) {
   return static_cast<int>(fminf(fmaxf(q, -127.0f), 127.0f));
 }
 
-// The same code for many values under one scale, arranged for issue slots. With inv = RN(1 / scale), the product
-// value * inv corrected once by its fma residual is within two ulp of the true quotient; the IEEE division is only needed
-// where that estimate lies within 1e-4 of a rounding boundary (k + 0.5), which is where two ulp at |q| <= 128 could
-// change the integer. Everything else (about 9998 values in 10000) takes three fp32 operations instead of a division.
+// The same code for many values under one scale, without a division instruction. With inv = RN(1 / scale), the product
+// q0 = value * inv is within two ulp of the quotient, and each step q <- RN(q + (value - q * scale) * inv), whose residual
+// the fma forms exactly, sharpens it: after the first step q is faithful (within one ulp), and a faithful q refined once
+// more with a correctly rounded reciprocal IS the correctly rounded quotient (Markstein's division theorem; its one
+// exception, a divisor whose significand is all ones, takes the IEEE division, as do scales whose reciprocal leaves the
+// normal range). Values whose quotient is huge, infinite or NaN keep q0, which saturates the same way.
+// Rounding to the nearest-even integer is then the fp32 addition of 1.5 * 2**23 (the sum has an ulp of one) after a clamp
+// to +-127.25 (anything beyond rounds or saturates to +-127; NaN becomes -127 like the saturating division path): the low
+// mantissa byte of the sum is the code in two's complement, so no round or convert instruction is needed either.
 struct Int8Quantizer {
   float scale, inv;
   bool exact_only;
@@ -416,15 +421,36 @@ __device__ __forceinline__ Int8Quantizer make_int8_quantizer(float s) {
   Int8Quantizer q;
   q.scale = s;
   q.inv = __frcp_rn(s);
-  q.exact_only = !(fabsf(s) >= 1e-30f && fabsf(s) <= 1e30f);  // reciprocal of a tiny, huge or non-finite scale: divide
+  q.exact_only = !(fabsf(s) >= 1e-25f && fabsf(s) <= 1e30f) || (__float_as_uint(s) & 0x7FFFFFu) == 0x7FFFFFu;
   return q;
 }
-__device__ __forceinline__ int int8_code(const Int8Quantizer& z, float value) {
-  float q = value * z.inv;
+__device__ __forceinline__ int int8_exact(float scale, float value) {
+  return static_cast<int>(fminf(fmaxf(rintf(__fdiv_rn(value, scale)), -127.0f), 127.0f));
+}
+// bits whose low byte is the code
+__device__ __forceinline__ uint32_t int8_bits(const Int8Quantizer& z, float value) {
+  constexpr float kMagic = 12582912.0f;  // 0x4B400000
+  const float q0 = value * z.inv;
+  float q = fmaf(fmaf(-q0, z.scale, value), z.inv, q0);
   q = fmaf(fmaf(-q, z.scale, value), z.inv, q);
-  float n = rintf(q);
-  if (z.exact_only || fabsf(fabsf(q - n) - 0.5f) < 1e-4f || !(fabsf(q) < 1e6f)) n = rintf(__fdiv_rn(value, z.scale));
-  return static_cast<int>(fminf(fmaxf(n, -127.0f), 127.0f));
+  q = fabsf(q0) < 1e6f ? q : q0;
+  return __float_as_uint(fminf(fmaxf(q, -127.25f), 127.25f) + kMagic);
+}
+__device__ __forceinline__ int int8_code(const Int8Quantizer& z, float value) {
+  if (z.exact_only) return int8_exact(z.scale, value);
+  return static_cast<int>(static_cast<int8_t>(int8_bits(z, value) & 0xFFu));
+}
+// Two / four codes in the low bytes of a word (value 0 first).
+__device__ __forceinline__ uint32_t int8_pack2(const Int8Quantizer& z, float v0, float v1) {
+  if (z.exact_only) return (static_cast<uint32_t>(int8_exact(z.scale, v0)) & 0xFFu) | ((static_cast<uint32_t>(int8_exact(z.scale, v1)) & 0xFFu) << 8);
+  return __byte_perm(int8_bits(z, v0), int8_bits(z, v1), 0x4440) & 0xFFFFu;
+}
+__device__ __forceinline__ uint32_t int8_pack4(const Int8Quantizer& z, float v0, float v1, float v2, float v3) {
+  if (z.exact_only) {
+    return (static_cast<uint32_t>(int8_exact(z.scale, v0)) & 0xFFu) | ((static_cast<uint32_t>(int8_exact(z.scale, v1)) & 0xFFu) << 8) |
+           ((static_cast<uint32_t>(int8_exact(z.scale, v2)) & 0xFFu) << 16) | ((static_cast<uint32_t>(int8_exact(z.scale, v3)) & 0xFFu) << 24);
+  }
+  return __byte_perm(__byte_perm(int8_bits(z, v0), int8_bits(z, v1), 0x4440), __byte_perm(int8_bits(z, v2), int8_bits(z, v3), 0x4440), 0x5410);
 }
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }

@@ -226,11 +226,7 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[
     const Int8Quantizer quantizer = make_int8_quantizer(__ldg(p.out_scale));
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t q0 = static_cast<uint32_t>(int8_code(quantizer, bf16_lo(r[2 * i]))) & 0xFFu;
-      const uint32_t q1 = static_cast<uint32_t>(int8_code(quantizer, bf16_hi(r[2 * i]))) & 0xFFu;
-      const uint32_t q2 = static_cast<uint32_t>(int8_code(quantizer, bf16_lo(r[2 * i + 1]))) & 0xFFu;
-      const uint32_t q3 = static_cast<uint32_t>(int8_code(quantizer, bf16_hi(r[2 * i + 1]))) & 0xFFu;
-      w[i] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+      w[i] = int8_pack4(quantizer, bf16_lo(r[2 * i]), bf16_hi(r[2 * i]), bf16_lo(r[2 * i + 1]), bf16_hi(r[2 * i + 1]));
     }
     return;
   }

@@ -133,8 +133,7 @@ __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc
       float lo, hi;
       unpack2(v[j], lo, hi);
       const uint32_t rounded = pack_bf16(lo, hi);  // one packed conversion instead of two scalar ones
-      const int qlo = int8_code(int8, bf16_lo(rounded)), qhi = int8_code(int8, bf16_hi(rounded));
-      const uint16_t codes = static_cast<uint16_t>((qlo & 0xFF) | ((qhi & 0xFF) << 8));
+      const uint16_t codes = static_cast<uint16_t>(int8_pack2(int8, bf16_lo(rounded), bf16_hi(rounded)));
       store_if(out + j * pair_stride, codes, cols_ok & (1u << j));
     }
   }

@@ -1,5 +1,7 @@
 // Standalone activation quantisers (memory-bound, one pass): static and dynamic block-32 MXFP8, static INT8.
 // Byte-exact with the FlashIM torch reference (flashim/quant/tensor.py:97-121,148-151; flashim/quant/formats/mx.py:50-60).
+#include <type_traits>
+
 #include "common.cuh"
 #include "flashim_sm100.h"
 
@@ -119,10 +121,7 @@ __global__ void __launch_bounds__(kThreads) quantize_int8_kernel(const T* __rest
     uint32_t q[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      uint32_t w = 0;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) w |= (static_cast<uint32_t>(int8_code(quantizer, v[4 * j + k])) & 0xFFu) << (8 * k);
-      q[j] = w;
+      q[j] = int8_pack4(quantizer, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
     *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(q[0], q[1], q[2], q[3]);
   }
@@ -140,6 +139,165 @@ int grid_for(long long work_items, int multiple) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Static quantisers that read the channels-last *view* of an NCHW-contiguous tensor ([B, C, P] in memory, P = H * W) and
+// write packed NHWC codes ([B, P, Cp]): the layout change rides on the quantiser instead of costing a copy pass
+// (flashim/backends/triton/quantize.py:217-234 does the same with a two-dimensional tile). A block owns 128 pixels x 64
+// channels: warps read along pixels (contiguous in the source), the code bytes cross through shared memory, and the tile
+// leaves as 16-byte pieces along channels (contiguous in the output). Per-element arithmetic is that of the row-major
+// kernels above, so the bytes are identical.
+constexpr int kTilePixels = 128, kTileChannels = 64, kTilePitch = kTileChannels + 4;
+
+// four consecutive pixels of one channel row (`valid` of them exist); VEC: one aligned 8- or 16-byte load
+template <typename T, bool VEC>
+__device__ __forceinline__ void load_pixels4(const T* p, int valid, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load_pixels4<__nv_bfloat16, true>(const __nv_bfloat16* p, int valid, float (&v)[4]) {
+  const uint2 w = valid > 0 ? __ldg(reinterpret_cast<const uint2*>(p)) : make_uint2(0u, 0u);
+  v[0] = bf16_lo(w.x), v[1] = bf16_hi(w.x), v[2] = bf16_lo(w.y), v[3] = bf16_hi(w.y);
+}
+template <>
+__device__ __forceinline__ void load_pixels4<float, true>(const float* p, int valid, float (&v)[4]) {
+  const float4 w = valid > 0 ? __ldg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  v[0] = w.x, v[1] = w.y, v[2] = w.z, v[3] = w.w;
+}
+template <>
+__device__ __forceinline__ void load_pixels4<__nv_bfloat16, false>(const __nv_bfloat16* p, int valid, float (&v)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = j < valid ? __bfloat162float(p[j]) : 0.0f;
+}
+template <>
+__device__ __forceinline__ void load_pixels4<float, false>(const float* p, int valid, float (&v)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = j < valid ? p[j] : 0.0f;
+}
+
+// A thread quantises 4 channels x 4 pixels per step (lane = pixel quad, so a warp reads 128 consecutive pixels of a
+// channel row), turns the four code words (one per channel, a byte per pixel) into four words of 4 channels per pixel
+// with byte permutes, and stores those to the shared tile.
+template <typename T, bool INT8, bool VEC>
+__global__ void __launch_bounds__(kThreads) quantize_nchw_kernel(const T* __restrict__ in, const int8_t* __restrict__ exps,
+                                                                 const float* __restrict__ scale_ptr, uint8_t* __restrict__ out,
+                                                                 int channels, int padded, long long pixels, int pixel_tiles,
+                                                                 int channel_tiles) {
+  __shared__ __align__(16) uint8_t tile[kTilePixels * kTilePitch];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long t = blockIdx.x;
+  const int ct = static_cast<int>(t % channel_tiles);
+  t /= channel_tiles;
+  const long long pt = t % pixel_tiles;
+  const long long b = t / pixel_tiles;
+  const int c0 = ct * kTileChannels;
+  const long long p0 = pt * kTilePixels + 4 * lane;
+  const int valid = static_cast<int>(pixels - p0 < 4 ? (pixels - p0 < 0 ? 0 : pixels - p0) : 4);
+  const Int8Quantizer quantizer = make_int8_quantizer(INT8 ? __ldg(scale_ptr) : 1.0f);
+
+  float v[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + 4 * (warp + 8 * i) + k;
+      load_pixels4<T, VEC>(in + (b * channels + (c < channels ? c : 0)) * pixels + p0, c < channels ? valid : 0, v[i][k]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int cq = warp + 8 * i;
+    if (c0 + 4 * cq >= padded) break;  // warp-uniform; channels in [channels, padded) were loaded as zeros
+    uint32_t r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (INT8) {
+        r[k] = int8_pack4(quantizer, v[i][k][0], v[i][k][1], v[i][k][2], v[i][k][3]);
+      } else {
+        const int c = min(c0 + 4 * cq + k, padded - 1);
+        const float inv = exp2_int(-static_cast<int>(exps[c >> 5]));
+        r[k] = e4m3x4(v[i][k][0] * inv, v[i][k][1] * inv, v[i][k][2] * inv, v[i][k][3] * inv);
+      }
+    }
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
+    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(tile + (4 * lane) * kTilePitch + 4 * cq);
+    dst[0] = __byte_perm(t0, t1, 0x5410);
+    dst[kTilePitch / 4] = __byte_perm(t0, t1, 0x7632);
+    dst[2 * (kTilePitch / 4)] = __byte_perm(t2, t3, 0x5410);
+    dst[3 * (kTilePitch / 4)] = __byte_perm(t2, t3, 0x7632);
+  }
+  __syncthreads();
+  const int part = threadIdx.x & 3;  // 16 channels
+  if (c0 + part * 16 >= padded) return;
+  const long long tile_p0 = pt * kTilePixels;
+#pragma unroll
+  for (int j = 0; j < kTilePixels / (kThreads / 4); ++j) {
+    const int p = (threadIdx.x >> 2) + j * (kThreads / 4);
+    if (tile_p0 + p >= pixels) break;
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(tile + p * kTilePitch + part * 16);
+    *reinterpret_cast<uint4*>(out + (b * pixels + tile_p0 + p) * padded + c0 + part * 16) = make_uint4(row[0], row[1], row[2], row[3]);
+  }
+}
+
+// 2x2 / stride-2 max pool of a bf16 NHWC tensor followed by the static INT8 quantiser: the second output of
+// int8_conv2d_maxpool (flashim/ops/conv.py:209-222). A thread owns eight channels of one pooled pixel: four 16-byte loads,
+// three packed bf16 maxima per word, eight codes, one 8-byte store. A trailing odd row or column is dropped, as
+// F.max_pool2d does.
+__global__ void __launch_bounds__(kThreads) maxpool2_int8_kernel(const uint4* __restrict__ in, const float* __restrict__ scale_ptr,
+                                                                 uint2* __restrict__ out, int batch, int height, int width,
+                                                                 int channels) {
+  const Int8Quantizer quantizer = make_int8_quantizer(__ldg(scale_ptr));
+  const int ho = height / 2, wo = width / 2, groups = channels / 8;
+  const long long total = static_cast<long long>(batch) * ho * wo * groups;
+  const long long row = static_cast<long long>(width) * groups;  // in 16-byte units
+  for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * kThreads) {
+    long long t = i;
+    const int g = static_cast<int>(t % groups); t /= groups;
+    const int x = static_cast<int>(t % wo); t /= wo;
+    const int y = static_cast<int>(t % ho);
+    const long long b = t / ho;
+    const uint4* src = in + ((b * height + 2 * y) * width + 2 * x) * groups + g;
+    const uint4 a = __ldg(src), c = __ldg(src + groups), d = __ldg(src + row), e = __ldg(src + row + groups);
+    const uint32_t m[4] = {bf16x2_max(bf16x2_max(a.x, c.x), bf16x2_max(d.x, e.x)), bf16x2_max(bf16x2_max(a.y, c.y), bf16x2_max(d.y, e.y)),
+                           bf16x2_max(bf16x2_max(a.z, c.z), bf16x2_max(d.z, e.z)), bf16x2_max(bf16x2_max(a.w, c.w), bf16x2_max(d.w, e.w))};
+    const uint32_t q[2] = {int8_pack4(quantizer, bf16_lo(m[0]), bf16_hi(m[0]), bf16_lo(m[1]), bf16_hi(m[1])),
+                           int8_pack4(quantizer, bf16_lo(m[2]), bf16_hi(m[2]), bf16_lo(m[3]), bf16_hi(m[3]))};
+    out[i] = make_uint2(q[0], q[1]);
+  }
+}
+
+template <bool INT8>
+int launch_nchw(const void* value, int dtype, const int8_t* exponent, const float* scale, void* out, int batch, int channels,
+                long long pixels, int padded, void* stream) {
+  if (batch < 0 || channels <= 0 || pixels < 0) return kBadArgument;
+  if (batch == 0 || pixels == 0) return kOk;
+  if (value == nullptr || out == nullptr || (INT8 ? scale == nullptr : exponent == nullptr)) return kBadArgument;
+  if (!aligned16(out) || padded % 16) return kBadLayout;
+  const long long pixel_tiles = (pixels + kTilePixels - 1) / kTilePixels;
+  const int channel_tiles = (padded + kTileChannels - 1) / kTileChannels;
+  const long long blocks = pixel_tiles * channel_tiles * batch;
+  if (blocks > 0x7fffffffLL) return kUnsupported;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(blocks);
+  auto launch = [&](auto zero, auto vec) {
+    using T = decltype(zero);
+    // one aligned load per four pixels needs every channel row to start on such a boundary
+    quantize_nchw_kernel<T, INT8, decltype(vec)::value><<<grid, kThreads, 0, s>>>(
+        static_cast<const T*>(value), exponent, scale, static_cast<uint8_t*>(out), channels, padded, pixels,
+        static_cast<int>(pixel_tiles), channel_tiles);
+  };
+  const size_t elem = dtype == FIM_DTYPE_BF16 ? 2 : 4;
+  const bool vec = pixels % 4 == 0 && (reinterpret_cast<uintptr_t>(value) % (4 * elem)) == 0;
+  if (dtype == FIM_DTYPE_BF16) {
+    if (vec) launch(__nv_bfloat16{}, std::true_type{});
+    else launch(__nv_bfloat16{}, std::false_type{});
+  } else if (dtype == FIM_DTYPE_F32) {
+    if (vec) launch(0.0f, std::true_type{});
+    else launch(0.0f, std::false_type{});
+  } else {
+    return kBadArgument;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
 
 }  // namespace
 }  // namespace fim
@@ -205,5 +363,29 @@ extern "C" int fim_quantize_int8_static(const void* value, int dtype, const floa
   } else {
     return kBadArgument;
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fim_quantize_mxfp8_static_nchw(const void* value, int dtype, const int8_t* exponent, void* out, int batch,
+                                              int channels, long long pixels, void* stream) {
+  return launch_nchw<false>(value, dtype, exponent, nullptr, out, batch, channels, pixels, (channels + 31) / 32 * 32, stream);
+}
+
+extern "C" int fim_quantize_int8_static_nchw(const void* value, int dtype, const float* scale, void* out, int batch, int channels,
+                                             long long pixels, void* stream) {
+  if (channels % 16) return kBadLayout;  // INT8 activations are not padded: the packed rows must stay 16-byte pieces
+  return launch_nchw<true>(value, dtype, nullptr, scale, out, batch, channels, pixels, channels, stream);
+}
+
+extern "C" int fim_maxpool2_quantize_int8(const void* value, const float* scale, void* out, int batch, int height, int width,
+                                          int channels, void* stream) {
+  if (batch < 0 || height < 0 || width < 0 || channels <= 0) return kBadArgument;
+  if (channels % 8) return kBadLayout;
+  if (batch == 0 || height < 2 || width < 2) return kOk;
+  if (value == nullptr || scale == nullptr || out == nullptr) return kBadArgument;
+  if (!aligned16(value) || (reinterpret_cast<uintptr_t>(out) & 7u)) return kBadLayout;
+  const long long work = static_cast<long long>(batch) * (height / 2) * (width / 2) * (channels / 8);
+  maxpool2_int8_kernel<<<grid_for(work, 16), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(value), scale, static_cast<uint2*>(out), batch, height, width, channels);
   return static_cast<int>(cudaGetLastError());
 }

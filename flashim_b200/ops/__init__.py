@@ -25,6 +25,10 @@ mxfp8_conv2d = Op("mxfp8_conv2d", doc="(x E4M3 NHWC, channel_exponent, weight E4
 int8_conv2d = Op("int8_conv2d", doc="(x int8 NHWC, weight int8 [Cout, K], a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, "
                  "dh, dw, *, relu, residual, out_scale) -> bf16 / int8 NHWC (flashim/ops/conv.py:174-206)")
 
+int8_conv2d_maxpool = Op("int8_conv2d_maxpool", doc="(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu, "
+                         "out_scale) -> (bf16 [B, Ho, Wo, Cout], int8 [B, Ho/2, Wo/2, Cout]): int8_conv2d and its 2x2 max "
+                         "pool quantised with out_scale (flashim/ops/conv.py:209-222)")
+
 mxfp8_scaled_mm = Op("mxfp8_scaled_mm", doc="(a E4M3 [M, K], b_t E4M3 [K, N] (the transpose of a row-major [N, K]), a_scale, "
                      "b_scale swizzled E8M0, bias=None) -> bf16 [M, N]: the block-scaled GEMM the pointwise composites end "
                      "in (flashim/ops/gemm.py:40-52)")

@@ -1,4 +1,4 @@
-"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|all]``.
+"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|quant|all]``.
 
 Prints, as Markdown tables, the device time of each kernel over the shapes of BASELINE configs 3 and 4 (N = 4; conv
 100x100x512, 200x200x256, 400x400x128, 800x800x64 with k = 3 and k = 1, plain and with the fused bias + GELU + MXFP8
@@ -117,6 +117,36 @@ def depthwise_sweep() -> None:
     check_status()
 
 
+def quantiser_sweep() -> None:
+    """The standalone quantisers and the max-pool quantiser: one pass over HBM each."""
+    from flashim_b200 import check_status, ops
+    from flashim_b200.backends.sm100 import kernels
+
+    hbm, _ = _peaks()
+    print("| quantiser | input | us | GB/s | % HBM peak |")
+    print("|---|---|---:|---:|---:|")
+    for n, c, size in ((4, 256, 200), (4, 128, 400), (4, 512, 100)):
+        nchw = torch.randn(n, c, size, size, device="cuda", dtype=BF16)
+        nhwc = nchw.permute(0, 2, 3, 1).contiguous()
+        exponent = torch.zeros(c // 32, dtype=torch.int8, device="cuda")
+        scale = torch.tensor(0.03, device="cuda")
+        view = nchw.permute(0, 2, 3, 1)
+        elements = n * c * size * size
+        cases = (
+            ("static MXFP8, row-major", 3 * elements, lambda: ops.quantize_mxfp8.get("sm100")(nhwc, exponent)),
+            ("static MXFP8, channels-first view", 3 * elements, lambda: ops.quantize_mxfp8.get("sm100")(view, exponent)),
+            ("dynamic MXFP8, row-major", (3 + 1 / 32) * elements, lambda: ops.quantize_mxfp8_dynamic.get("sm100")(nhwc)),
+            ("static INT8, row-major", 3 * elements, lambda: ops.quantize_int8.get("sm100")(nhwc, scale)),
+            ("static INT8, channels-first view", 3 * elements, lambda: ops.quantize_int8.get("sm100")(view, scale)),
+            ("MaxPool2d(2) -> INT8", 2.25 * elements, lambda: kernels.maxpool2_quantize_int8(nhwc, scale.reshape(1))),
+        )
+        for name, moved, fn in cases:
+            ms = graph_time_ms(fn)
+            gbs = moved / ms / 1e6
+            print(f"| {name} | bf16 {n}x{size}x{size}x{c} | {ms * 1e3:.1f} | {gbs:.0f} | {100 * gbs / hbm:.1f} |", flush=True)
+    check_status()
+
+
 def main() -> None:
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if not torch.cuda.is_available():
@@ -126,6 +156,9 @@ def main() -> None:
     if which in ("dw", "all"):
         print()
         depthwise_sweep()
+    if which in ("quant", "all"):
+        print()
+        quantiser_sweep()
 
 
 if __name__ == "__main__":

@@ -74,6 +74,24 @@ int fim_quantize_mxfp8_dynamic(const void* value, int dtype, void* out, void* sc
  * flashim/quant/formats/int8.py:24-26). */
 int fim_quantize_int8_static(const void* value, int dtype, const float* scale, void* out, long long count, void* stream);
 
+/* The two static quantisers reading the channels-last view of an NCHW-contiguous tensor: `value` is [batch, channels,
+ * pixels] in memory (pixels = H * W), `out` the packed NHWC codes [batch, pixels, ceil32(channels)] (MXFP8, padding
+ * channels zero) or [batch, pixels, channels] (INT8, channels % 16 == 0), 16-byte aligned. Bytes equal those of the
+ * row-major entry points on `value.permute(0, 2, 1)`.
+ * Replaces: the channels-first branch of ops.quantize_mxfp8 / ops.quantize_int8
+ * (flashim/backends/triton/quantize.py:217-246, 325-353). */
+int fim_quantize_mxfp8_static_nchw(const void* value, int dtype, const int8_t* exponent, void* out, int batch, int channels,
+                                   long long pixels, void* stream);
+int fim_quantize_int8_static_nchw(const void* value, int dtype, const float* scale, void* out, int batch, int channels,
+                                  long long pixels, void* stream);
+
+/* out[b, y, x, c] = int8(max over the 2x2 window of value[b, 2y.., 2x.., c] / *scale): MaxPool2d(2) of a bf16 NHWC tensor
+ * (16-byte aligned, channels % 8 == 0) and the static INT8 quantiser in one pass; `out` is int8 [batch, height / 2,
+ * width / 2, channels], 8-byte aligned; a trailing odd row / column is dropped.
+ * Replaces: the pooled output of ops.int8_conv2d_maxpool (flashim/ops/conv.py:209-222). */
+int fim_maxpool2_quantize_int8(const void* value, const float* scale, void* out, int batch, int height, int width, int channels,
+                               void* stream);
+
 /* ---- depthwise 5x5 (pad 2, stride 1) -------------------------------------------------------------------------- */
 
 /* out[b,y,x,c] = act(sum_{ky,kx} value[b,y+ky-2,x+kx-2,c] * weight[ky*5+kx, c] + bias[c]) with fp32 accumulation

@@ -34,7 +34,7 @@ __all__ = [
     "pack_int8_conv_weight", "gather_taps", "conv_out_size", "mx_matmul_fp32", "int8_matmul_int32",
     "mxfp8_conv2d", "int8_conv2d", "add_residual", "depthwise5x5_fp32", "depthwise5x5_relu_mxfp8",
     "depthwise5x5_relu_int8", "depthwise5x5_act_ext", "depthwise5x5_act_mxfp8_ext", "mxfp8_conv2d_ext",
-    "int8_conv2d_accumulators_ext", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
+    "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
     "dequantize_mx",
 ]
 
@@ -272,6 +272,14 @@ def int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, d
     if residual is not None:
         out = add_residual(out, residual, relu)
     return out if out_scale is None else quantize_int8(out, out_scale.float().reshape(()))
+
+
+def int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, out_scale):
+    """:func:`int8_conv2d` (bf16 output) and its ``MaxPool2d(2)`` quantised with ``out_scale``: ``(out, pooled int8
+    [B, Ho // 2, Wo // 2, Cout])``; a trailing odd row / column is dropped (flashim/ops/conv.py:209-222)."""
+    out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
+    pooled = F.max_pool2d(out.permute(0, 3, 1, 2).float(), 2).permute(0, 2, 3, 1).to(torch.bfloat16)
+    return out, quantize_int8(pooled, out_scale.float().reshape(()))
 
 
 def mxfp8_scaled_mm(a: Tensor, b_t: Tensor, a_scale: Tensor, b_scale: Tensor, bias: Tensor | None = None) -> Tensor:

@@ -210,6 +210,32 @@ def gemms() -> None:
     save("gemms", **arrays)
 
 
+def widening() -> None:
+    """Ops either side of the conv: int8_conv2d_maxpool (flashim/ops/conv.py:209-222) with even and odd output sizes, and
+    the static quantisers applied to the channels-last view of NCHW tensors (flashim/ops/quantize.py:80-100)."""
+    g = torch.Generator().manual_seed(23)
+    arrays = {}
+    for i, (b, h, w, cin, cout, k) in enumerate([(2, 8, 10, 32, 32, 3), (1, 9, 7, 64, 64, 3), (1, 6, 6, 32, 64, 1)]):
+        x = torch.randint(-127, 128, (b, h, w, cin), dtype=torch.int8, generator=g)
+        wt = torch.randint(-127, 128, (cout, k * k * cin), dtype=torch.int8, generator=g)
+        ws = torch.rand(cout, generator=g) * 2e-4 + 1e-5
+        bias = torch.randn(cout, generator=g).to(torch.bfloat16)
+        a_scale, out_scale = torch.tensor(0.03), torch.tensor(0.02 + 0.01 * i)
+        out, pooled = ops.int8_conv2d_maxpool.get("reference")(x, wt, a_scale, ws, bias, k, k, 1, 1, k // 2, k // 2, 1, 1,
+                                                               relu=bool(i != 1), out_scale=out_scale)
+        arrays.update({f"pool{i}_x": raw(x), f"pool{i}_w": raw(wt), f"pool{i}_ws": raw(ws), f"pool{i}_b": raw(bias),
+                       f"pool{i}_out": raw(out), f"pool{i}_pooled": raw(pooled), f"pool{i}_k": np.asarray(k)})
+    for i, shape in enumerate([(2, 48, 5, 7), (1, 3, 4, 4), (1, 64, 6, 3)]):
+        nchw = (torch.randn(*shape, generator=g) * 5).to(torch.bfloat16 if i else torch.float32)
+        view = nchw.permute(0, 2, 3, 1)
+        exponent = ref_mx.calibrate_block32_exponent(view)
+        q = ops.quantize_mxfp8.get("reference")(view, exponent)
+        arrays.update({f"cf{i}_x": raw(nchw), f"cf{i}_e": raw(exponent), f"cf{i}_q": raw(q.values)})
+        if shape[1] % 16 == 0:
+            arrays[f"cf{i}_i8"] = raw(ops.quantize_int8.get("reference")(view, torch.tensor(0.04)).values)
+    save("widening", **arrays)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     formats()
@@ -217,3 +243,4 @@ if __name__ == "__main__":
     depthwise()
     modules()
     gemms()
+    widening()

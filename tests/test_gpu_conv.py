@@ -220,6 +220,38 @@ def test_int8_conv2d_golden_and_chain(ops, golden):
         assert same_bytes(got.cpu(), want), f"int8 golden case {i}"
 
 
+@pytest.mark.parametrize("shape", [(2, 16, 20), (1, 17, 19), (3, 9, 8), (1, 2, 2), (1, 64, 66)])
+@pytest.mark.parametrize("cin,cout,k", [(64, 64, 3), (32, 96, 1), (128, 256, 3)])
+def test_int8_conv2d_maxpool(ops, shape, cin, cout, k):
+    """int8_conv2d_maxpool (flashim/ops/conv.py:209-222): the bf16 conv output and its 2x2 max pool as INT8 codes, both
+    byte-equal to the oracle; odd heights / widths drop the trailing row / column."""
+    b, h, w = shape
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(-127, 128, (b, h, w, cin), dtype=torch.int8, generator=g)
+    wt = torch.randint(-127, 128, (cout, k * k * cin), dtype=torch.int8, generator=g)
+    w_scale = torch.rand(cout, generator=g) * 2e-4 + 1e-5
+    bias = torch.randn(cout, generator=g).to(BF16)
+    a_scale, out_scale = torch.tensor(0.03), torch.tensor(0.025)
+    geometry = (k, k, 1, 1, k // 2, k // 2, 1, 1)
+    for relu in (True, False):
+        out, pooled = ops.int8_conv2d_maxpool.get("sm100")(*to_dev(x, wt, a_scale, w_scale, bias), *geometry, relu=relu,
+                                                           out_scale=to_dev(out_scale))
+        want_out, want_pooled = oracle.int8_conv2d_maxpool(x, wt, a_scale, w_scale, bias, *geometry, relu=relu, out_scale=out_scale)
+        assert same_bytes(out.cpu(), want_out)
+        assert pooled.dtype == torch.int8 and pooled.shape == want_pooled.shape
+        assert torch.equal(pooled.cpu(), want_pooled)
+
+
+def test_int8_conv2d_maxpool_golden(ops, golden):
+    g = golden("widening")
+    for i in range(3):
+        k = int(g(f"pool{i}_k"))
+        out, pooled = ops.int8_conv2d_maxpool.get("sm100")(
+            *to_dev(g(f"pool{i}_x"), g(f"pool{i}_w"), torch.tensor(0.03), g(f"pool{i}_ws"), g(f"pool{i}_b", BF16)), k, k, 1, 1,
+            k // 2, k // 2, 1, 1, relu=bool(i != 1), out_scale=to_dev(torch.tensor(0.02 + 0.01 * i)))
+        assert same_bytes(out.cpu(), g(f"pool{i}_out", BF16)) and torch.equal(pooled.cpu(), g(f"pool{i}_pooled")), f"case {i}"
+
+
 def test_baseline_config2(ops):
     """BASELINE config 2: bf16 NHWC [2, 100, 100, 256] from seed 1, 256 -> 256 3x3 pad 1, int32 sums bit-exact, bf16 out."""
     torch.manual_seed(1)

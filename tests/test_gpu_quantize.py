@@ -97,3 +97,70 @@ def test_empty_and_rejected_inputs(ops):
     assert out.values.shape == (0, 32)
     with pytest.raises(NoImplementation):  # CPU tensors never take a fallback
         ops.quantize_mxfp8(torch.zeros(4, 32, dtype=BF16), torch.zeros(1, dtype=torch.int8))
+
+
+@pytest.mark.parametrize("dtype", [BF16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 48, 9, 13), (1, 3, 5, 7), (3, 64, 16, 8), (1, 200, 11, 13), (2, 32, 1, 1),
+                                   (1, 128, 40, 37)])
+def test_static_mxfp8_reads_channels_first_in_place(ops, dtype, shape):
+    """``x.permute(0, 2, 3, 1)`` of an NCHW tensor is quantised without a layout copy (flashim
+    backends/triton/quantize.py:217-246): same bytes as the row-major path, ragged channels padded with zero codes."""
+    torch.manual_seed(1)
+    nchw = (torch.randn(*shape) * 6).to(dtype)
+    view = nchw.permute(0, 2, 3, 1)
+    assert not view.is_contiguous() or shape[1] == 1 or shape[2] * shape[3] == 1
+    e = oracle.static_block_exponent(view)
+    want = oracle.quantize_static_mx(view, e)
+    got = ops.quantize_mxfp8.get("sm100")(to_dev(nchw).permute(0, 2, 3, 1), to_dev(e))
+    assert got.values.shape == want.shape and got.logical_shape == tuple(view.shape)
+    assert got.values.is_contiguous() and same_bytes(got.values.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [BF16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 48, 9, 13), (1, 16, 5, 7), (3, 64, 16, 8), (1, 208, 11, 13), (1, 128, 40, 37)])
+def test_static_int8_reads_channels_first_in_place(ops, dtype, shape):
+    torch.manual_seed(2)
+    nchw = (torch.randn(*shape) * 3).to(dtype)
+    view = nchw.permute(0, 2, 3, 1)
+    scale = torch.tensor(0.037)
+    want = oracle.quantize_int8(view, scale)
+    got = ops.quantize_int8.get("sm100")(to_dev(nchw).permute(0, 2, 3, 1), to_dev(scale))
+    assert got.values.shape == want.shape and got.values.is_contiguous()
+    assert torch.equal(got.values.cpu(), want)
+
+
+def test_channels_first_quantisers_golden(ops, golden):
+    g = golden("widening")
+    for i in range(3):
+        nchw = g(f"cf{i}_x", BF16 if i else torch.float32)
+        got = ops.quantize_mxfp8.get("sm100")(to_dev(nchw).permute(0, 2, 3, 1), to_dev(g(f"cf{i}_e")))
+        assert same_bytes(got.values.cpu(), g(f"cf{i}_q", E4M3)), f"case {i}"
+        if nchw.shape[1] % 16 == 0:
+            got8 = ops.quantize_int8.get("sm100")(to_dev(nchw).permute(0, 2, 3, 1), to_dev(torch.tensor(0.04)))
+            assert torch.equal(got8.values.cpu(), g(f"cf{i}_i8")), f"int8 case {i}"
+
+
+def test_int8_division_free_rounding_equals_true_division(ops):
+    """The kernels reach round(value / scale) through a reciprocal and two fma refinement steps instead of a division:
+    every bf16 value under 300 scales (random, short decimals where exact ties occur, powers of two, all-ones
+    significands, tiny and huge) and random fp32 values must give the codes of the oracle's IEEE division."""
+    g = torch.Generator().manual_seed(11)
+    every_bf16 = torch.arange(-2**15, 2**15, dtype=torch.int32).to(torch.int16).view(BF16)
+    every_bf16 = every_bf16[~torch.isnan(every_bf16.float())]
+    scales = [0.03, 0.01, 0.1, 0.3, 0.05, 0.07, 1.0, 0.5, 0.25, 3.0, 1e-3, 7e-3, 1e-20, 1e-26, 1e-31, 1e20, 1e31,
+              float(torch.tensor(0x3F7FFFFF, dtype=torch.int32).view(torch.float32)),   # all-ones significand
+              float(torch.tensor(0x3CFFFFFF, dtype=torch.int32).view(torch.float32))]
+    scales += (torch.rand(140, generator=g) * 0.2 + 1e-4).tolist()
+    scales += torch.exp2(torch.rand(141, generator=g) * 40 - 30).tolist()
+    quantise = ops.quantize_int8.get("sm100")
+    x_dev = to_dev(every_bf16)
+    for s in scales:
+        scale = torch.tensor(s, dtype=torch.float32)
+        got = quantise(x_dev, to_dev(scale)).values.cpu()
+        want = oracle.quantize_int8(every_bf16, scale)
+        assert torch.equal(got, want), f"scale {s!r}: {int((got != want).sum())} codes differ"
+    wide = torch.randn(1 << 20, generator=g) * torch.exp2(torch.randint(-12, 10, (1 << 20,), generator=g).float())
+    wide_dev = to_dev(wide)
+    for s in scales[::15]:
+        scale = torch.tensor(s, dtype=torch.float32)
+        assert torch.equal(quantise(wide_dev, to_dev(scale)).values.cpu(), oracle.quantize_int8(wide, scale)), f"fp32, scale {s!r}"

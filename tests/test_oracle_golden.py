@@ -245,3 +245,23 @@ def test_gemm_ops_match_reference_outputs(golden):
         args = (g(f"li{i}_a"), g(f"li{i}_w"), torch.tensor(0.02), g(f"li{i}_ws"), g(f"li{i}_b", BF16))
         assert same_bytes(oracle.int8_linear(*args, relu=bool(i & 1)), g(f"li{i}_out", BF16)), f"int8_linear case {i}"
         assert same_bytes(oracle.int8_linear(*args, residual=g(f"li{i}_res", BF16)), g(f"li{i}_out_res", BF16))
+
+
+def test_widening_ops_match_reference_outputs(golden):
+    """int8_conv2d_maxpool (flashim/ops/conv.py:209-222) and the static quantisers on the channels-last view of NCHW
+    tensors (flashim/ops/quantize.py:80-100) against outputs of the reference itself."""
+    g = golden("widening")
+    for i in range(3):
+        k = int(g(f"pool{i}_k"))
+        out, pooled = oracle.int8_conv2d_maxpool(
+            g(f"pool{i}_x"), g(f"pool{i}_w"), torch.tensor(0.03), g(f"pool{i}_ws"), g(f"pool{i}_b", BF16), k, k, 1, 1,
+            k // 2, k // 2, 1, 1, relu=bool(i != 1), out_scale=torch.tensor(0.02 + 0.01 * i))
+        assert same_bytes(out, g(f"pool{i}_out", BF16)), f"conv output, case {i}"
+        assert torch.equal(pooled, g(f"pool{i}_pooled")), f"pooled codes, case {i}"
+        nchw = g(f"cf{i}_x", BF16 if i else torch.float32)
+        view = nchw.permute(0, 2, 3, 1)
+        exponent = g(f"cf{i}_e")
+        assert torch.equal(oracle.static_block_exponent(view), exponent)
+        assert same_bytes(oracle.quantize_static_mx(view, exponent), g(f"cf{i}_q", E4M3))
+        if nchw.shape[1] % 16 == 0:
+            assert torch.equal(oracle.quantize_int8(view, torch.tensor(0.04)), g(f"cf{i}_i8"))
