@@ -250,6 +250,26 @@ def _(value, scale):
     return value.new_empty((b, h // 2, w // 2, c), dtype=torch.int8)
 
 
+@torch.library.custom_op("flashim_b200::romav2_refiner_heads", mutates_args=())
+def romav2_refiner_heads_launch(z: Tensor, weight: Tensor, bias: Tensor, prev_warp: Tensor, prev_confidence: Tensor,
+                                inv_norm_x: float, inv_norm_y: float) -> tuple[Tensor, Tensor]:
+    """``z`` is the NHWC memory ``[B, h, w, C]`` (bf16) of the channels-last feature map."""
+    b, h, w, c = z.shape
+    warp = torch.empty((b, h, w, 2), device=z.device, dtype=torch.float32)
+    confidence = torch.empty((b, h, w, 4), device=z.device, dtype=torch.float32)
+    code = _native.library().fim_romav2_refiner_heads(
+        z.data_ptr(), weight.data_ptr(), bias.data_ptr(), prev_warp.data_ptr(), prev_confidence.data_ptr(),
+        prev_confidence.shape[-1], warp.data_ptr(), confidence.data_ptr(), b * h * w, c, inv_norm_x, inv_norm_y, _stream(z))
+    _finish(code, f"romav2_refiner_heads {tuple(z.shape)}", z.device)
+    return warp, confidence
+
+
+@romav2_refiner_heads_launch.register_fake
+def _(z, weight, bias, prev_warp, prev_confidence, inv_norm_x, inv_norm_y):
+    b, h, w, _ = z.shape
+    return z.new_empty((b, h, w, 2), dtype=torch.float32), z.new_empty((b, h, w, 4), dtype=torch.float32)
+
+
 def _channels_first_view(value: Tensor) -> bool:
     """``value`` is ``x.permute(0, 2, 3, 1)`` of an NCHW-contiguous ``x`` and not itself row-major — the case FlashIM's
     quantisers read in place (flashim/backends/triton/quantize.py:237-239)."""
@@ -576,6 +596,24 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         @ops.depthwise5x5_act_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_act_when)
         def depthwise5x5_act_mxfp8(value, weight, bias, act="gelu"):
             return dw5x5_mxfp8(_nhwc(value), weight, bias, act_code[act], True)
+
+    if hasattr(ops, "romav2_refiner_heads"):
+        def heads_when(z, weight, bias, prev_warp, prev_confidence, refine_init):
+            # the conditions of FlashIM's own fused implementation (flashim/backends/triton/romav2.py:313-322)
+            return (
+                have() and _cuda(z, weight, bias, prev_warp, prev_confidence) and z.ndim == 4 and z.dtype == torch.bfloat16
+                and z.is_contiguous(memory_format=torch.channels_last) and z.shape[1] % 8 == 0 and z.shape[1] <= 512
+                and tuple(weight.shape[:2]) == (6, z.shape[1]) and weight.numel() == 6 * z.shape[1] and bias.numel() == 6
+                and prev_confidence.shape[-1] in (1, 4) and prev_warp.shape[-1] == 2
+                and prev_warp.dtype == torch.float32 and prev_confidence.dtype == torch.float32 and z.numel() > 0
+            )
+
+        @ops.romav2_refiner_heads.register("sm100", device=spec, requires=dw_requires, priority=3, when=heads_when)
+        def romav2_refiner_heads(z, weight, bias, prev_warp, prev_confidence, refine_init):
+            _, _, h, w = z.shape
+            return romav2_refiner_heads_launch(
+                z.permute(0, 2, 3, 1), weight.reshape(6, -1).float().contiguous(), bias.float().contiguous(),
+                prev_warp.contiguous(), prev_confidence.contiguous(), 1.0 / (refine_init * w), 1.0 / (refine_init * h))
 
     # -- quantisers ---------------------------------------------------------------------------------------------------
     def quantize_when(value, scale_exponent):

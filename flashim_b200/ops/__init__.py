@@ -29,6 +29,11 @@ int8_conv2d_maxpool = Op("int8_conv2d_maxpool", doc="(x, weight, a_scale, w_scal
                          "out_scale) -> (bf16 [B, Ho, Wo, Cout], int8 [B, Ho/2, Wo/2, Cout]): int8_conv2d and its 2x2 max "
                          "pool quantised with out_scale (flashim/ops/conv.py:209-222)")
 
+romav2_refiner_heads = Op("romav2_refiner_heads", doc="(z [B, C, h, w] channels-last, weight [6, C], bias [6], prev_warp "
+                          "[B, h, w, 2], prev_confidence [B, h, w, 1 or 4], refine_init) -> (warp fp32 [B, h, w, 2], confidence "
+                          "fp32 [B, h, w, 4]): warp / confidence 1x1 heads, warp update and precision parameters "
+                          "(flashim/ops/romav2.py:95-120)")
+
 mxfp8_scaled_mm = Op("mxfp8_scaled_mm", doc="(a E4M3 [M, K], b_t E4M3 [K, N] (the transpose of a row-major [N, K]), a_scale, "
                      "b_scale swizzled E8M0, bias=None) -> bf16 [M, N]: the block-scaled GEMM the pointwise composites end "
                      "in (flashim/ops/gemm.py:40-52)")

@@ -1,4 +1,4 @@
-"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|quant|all]``.
+"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|quant|heads|all]``.
 
 Prints, as Markdown tables, the device time of each kernel over the shapes of BASELINE configs 3 and 4 (N = 4; conv
 100x100x512, 200x200x256, 400x400x128, 800x800x64 with k = 3 and k = 1, plain and with the fused bias + GELU + MXFP8
@@ -147,6 +147,25 @@ def quantiser_sweep() -> None:
     check_status()
 
 
+def heads_sweep() -> None:
+    """RoMaV2 refiner heads on the three levels of the refiner pyramid (8 images)."""
+    from flashim_b200 import check_status, ops
+
+    hbm, _ = _peaks()
+    print("| refiner heads input | us | GB/s | % HBM peak |")
+    print("|---|---:|---:|---:|")
+    for n, c, size in ((8, 512, 100), (8, 256, 200), (8, 128, 400)):
+        z = torch.randn(n, c, size, size, device="cuda", dtype=BF16).contiguous(memory_format=torch.channels_last)
+        weight, bias = torch.randn(6, c, device="cuda") * 0.1, torch.randn(6, device="cuda")
+        prev_warp = torch.rand(n, size, size, 2, device="cuda")
+        prev_conf = torch.randn(n, size, size, 4, device="cuda")
+        ms = graph_time_ms(lambda: ops.romav2_refiner_heads.get("sm100")(z, weight, bias, prev_warp, prev_conf, 4.0))
+        moved = n * size * size * (2 * c + 2 * (8 + 16))
+        gbs = moved / ms / 1e6
+        print(f"| bf16 {n}x{size}x{size}x{c} | {ms * 1e3:.1f} | {gbs:.0f} | {100 * gbs / hbm:.1f} |", flush=True)
+    check_status()
+
+
 def main() -> None:
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if not torch.cuda.is_available():
@@ -159,6 +178,9 @@ def main() -> None:
     if which in ("quant", "all"):
         print()
         quantiser_sweep()
+    if which in ("heads", "all"):
+        print()
+        heads_sweep()
 
 
 if __name__ == "__main__":

@@ -92,6 +92,22 @@ int fim_quantize_int8_static_nchw(const void* value, int dtype, const float* sca
 int fim_maxpool2_quantize_int8(const void* value, const float* scale, void* out, int batch, int height, int width, int channels,
                                void* stream);
 
+/* ---- RoMaV2 refiner heads -------------------------------------------------------------------------------------- */
+
+/* The 1x1 convolution of the refiner's last feature map to 2 displacement + 4 precision channels and what follows it:
+ *   out[o] = sum_c z[row, c] * weight[o, c] + bias[o]            (fp32, o = 0..5)
+ *   warp[row] = prev_warp[row] + (out[0] * inv_norm_x, out[1] * inv_norm_y)
+ *   l00 = softplus(out[3]) + 1e-6, l10 = out[4], l11 = softplus(out[5]) + 1e-6
+ *   confidence[row] = prev_confidence[row] (zero-padded to 4) + (out[2], l00^2, l00 * l10, l10^2 + l11^2)
+ * `z` bf16 [rows, channels] (the NHWC memory of a channels-last tensor, 16-byte aligned, channels % 8 == 0, <= 512),
+ * `weight` fp32 [6, channels], `bias` fp32 [6], `prev_warp` / `warp` fp32 [rows, 2], `prev_confidence` fp32
+ * [rows, prev_channels] with prev_channels 1 or 4, `confidence` fp32 [rows, 4]; inv_norm = 1 / (refine_init * (w, h)).
+ * Replaces: ops.romav2_refiner_heads (flashim/ops/romav2.py:95-120), Triton `_refiner_heads_kernel`
+ * (flashim/backends/triton/romav2.py:202-250). */
+int fim_romav2_refiner_heads(const void* z, const float* weight, const float* bias, const float* prev_warp,
+                             const float* prev_confidence, int prev_channels, float* warp, float* confidence, long long rows,
+                             int channels, float inv_norm_x, float inv_norm_y, void* stream);
+
 /* ---- depthwise 5x5 (pad 2, stride 1) -------------------------------------------------------------------------- */
 
 /* out[b,y,x,c] = act(sum_{ky,kx} value[b,y+ky-2,x+kx-2,c] * weight[ky*5+kx, c] + bias[c]) with fp32 accumulation

@@ -34,7 +34,7 @@ __all__ = [
     "pack_int8_conv_weight", "gather_taps", "conv_out_size", "mx_matmul_fp32", "int8_matmul_int32",
     "mxfp8_conv2d", "int8_conv2d", "add_residual", "depthwise5x5_fp32", "depthwise5x5_relu_mxfp8",
     "depthwise5x5_relu_int8", "depthwise5x5_act_ext", "depthwise5x5_act_mxfp8_ext", "mxfp8_conv2d_ext",
-    "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
+    "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "romav2_refiner_heads", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
     "dequantize_mx",
 ]
 
@@ -280,6 +280,21 @@ def int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, p
     out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
     pooled = F.max_pool2d(out.permute(0, 3, 1, 2).float(), 2).permute(0, 2, 3, 1).to(torch.bfloat16)
     return out, quantize_int8(pooled, out_scale.float().reshape(()))
+
+
+def romav2_refiner_heads(z, weight, bias, prev_warp, prev_confidence, refine_init):
+    """RoMaV2 refiner heads: fp32 1x1 conv of ``z [B, C, h, w]`` to 2 displacement + 4 precision channels,
+    ``warp = prev_warp + disp / (refine_init * (w, h))``, ``l00 = softplus(d1) + 1e-6``, ``l10 = d2``,
+    ``l11 = softplus(d3) + 1e-6``, ``confidence = prev_confidence (zero-padded to 4) + (d0, l00^2, l00 l10, l10^2 + l11^2)``;
+    fp32 ``[B, h, w, 2]`` and ``[B, h, w, 4]`` (flashim/ops/romav2.py:95-120)."""
+    _, _, h, w = z.shape
+    out = F.conv2d(z.float(), weight.float().reshape(6, -1)[:, :, None, None], bias.float()).permute(0, 2, 3, 1)
+    warp = prev_warp + out[..., :2] / (refine_init * torch.tensor([w, h], dtype=prev_warp.dtype))
+    d = out[..., 2:]
+    l00, l10, l11 = F.softplus(d[..., 1]) + 1e-6, d[..., 2], F.softplus(d[..., 3]) + 1e-6
+    delta = torch.stack([d[..., 0], l00 * l00, l00 * l10, l10 * l10 + l11 * l11], dim=-1)
+    previous = prev_confidence if prev_confidence.shape[-1] == 4 else F.pad(prev_confidence, (0, 3))
+    return warp, previous + delta
 
 
 def mxfp8_scaled_mm(a: Tensor, b_t: Tensor, a_scale: Tensor, b_scale: Tensor, bias: Tensor | None = None) -> Tensor:

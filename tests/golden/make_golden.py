@@ -233,6 +233,15 @@ def widening() -> None:
         arrays.update({f"cf{i}_x": raw(nchw), f"cf{i}_e": raw(exponent), f"cf{i}_q": raw(q.values)})
         if shape[1] % 16 == 0:
             arrays[f"cf{i}_i8"] = raw(ops.quantize_int8.get("reference")(view, torch.tensor(0.04)).values)
+    for i, (b, c, h, w, prev_c) in enumerate([(2, 64, 7, 9, 1), (1, 128, 5, 6, 4), (1, 32, 3, 3, 4)]):
+        z = torch.randn(b, c, h, w, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        weight, bias = torch.randn(6, c, generator=g) * 0.3, torch.randn(6, generator=g)
+        prev_warp = torch.rand(b, h, w, 2, generator=g) * 2 - 1
+        prev_conf = torch.randn(b, h, w, prev_c, generator=g)
+        warp, conf = ops.romav2_refiner_heads.get("reference")(z, weight, bias, prev_warp, prev_conf, 4.0)
+        arrays.update({f"heads{i}_z": raw(z.permute(0, 2, 3, 1)), f"heads{i}_w": raw(weight), f"heads{i}_b": raw(bias),
+                       f"heads{i}_pw": raw(prev_warp), f"heads{i}_pc": raw(prev_conf), f"heads{i}_warp": raw(warp),
+                       f"heads{i}_conf": raw(conf)})
     save("widening", **arrays)
 
 

@@ -265,3 +265,12 @@ def test_widening_ops_match_reference_outputs(golden):
         assert same_bytes(oracle.quantize_static_mx(view, exponent), g(f"cf{i}_q", E4M3))
         if nchw.shape[1] % 16 == 0:
             assert torch.equal(oracle.quantize_int8(view, torch.tensor(0.04)), g(f"cf{i}_i8"))
+
+
+def test_refiner_heads_match_reference_outputs(golden):
+    """romav2_refiner_heads (flashim/ops/romav2.py:95-120): same torch operations, so the fp32 outputs are identical."""
+    g = golden("widening")
+    for i in range(3):
+        z = g(f"heads{i}_z", BF16).permute(0, 3, 1, 2)
+        warp, conf = oracle.romav2_refiner_heads(z, g(f"heads{i}_w"), g(f"heads{i}_b"), g(f"heads{i}_pw"), g(f"heads{i}_pc"), 4.0)
+        assert torch.equal(warp, g(f"heads{i}_warp")) and torch.equal(conf, g(f"heads{i}_conf")), f"case {i}"
