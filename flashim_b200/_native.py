@@ -66,6 +66,7 @@ SIGNATURES: dict[str, tuple] = {
     "fim_quantize_mxfp8_static_nchw": (_I, [_P, _I, _P, _P, _I, _I, _L, _P]),
     "fim_quantize_int8_static_nchw": (_I, [_P, _I, _P, _P, _I, _I, _L, _P]),
     "fim_maxpool2_quantize_int8": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
+    "fim_romav2_refiner_input": (_I, [_P, _P, _P, _P, _P, ctypes.c_float, ctypes.c_float, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
     "fim_romav2_refiner_heads": (_I, [_P, _P, _P, _P, _P, _I, _P, _P, _L, _I, ctypes.c_float, ctypes.c_float, _P]),
     "fim_dw5x5_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "fim_dw5x5_mxfp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P]),

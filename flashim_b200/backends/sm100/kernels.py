@@ -250,6 +250,28 @@ def _(value, scale):
     return value.new_empty((b, h // 2, w // 2, c), dtype=torch.int8)
 
 
+@torch.library.custom_op("flashim_b200::romav2_refiner_input", mutates_args=())
+def romav2_refiner_input_launch(f_a: Tensor, f_b: Tensor, warp: Tensor, emb_weight: Tensor, emb_bias: Tensor, scale_x: float,
+                                scale_y: float, radius: int, pair: int) -> Tensor:
+    """Returns the NHWC memory ``[B, h, w, 2P + E + K]`` (bf16)."""
+    b, h, w, features = f_a.shape
+    embedding = emb_weight.shape[0]
+    k = (2 * radius + 1) ** 2 if radius >= 0 else 0
+    out = torch.empty((b, h, w, 2 * features + embedding + k), device=f_a.device, dtype=torch.bfloat16)
+    code = _native.library().fim_romav2_refiner_input(
+        f_a.data_ptr(), f_b.data_ptr(), warp.data_ptr(), emb_weight.data_ptr(), emb_bias.data_ptr(), scale_x, scale_y,
+        out.data_ptr(), b, h, w, features, embedding, radius, pair, _stream(f_a))
+    _finish(code, f"romav2_refiner_input {tuple(f_a.shape)} r={radius}", f_a.device)
+    return out
+
+
+@romav2_refiner_input_launch.register_fake
+def _(f_a, f_b, warp, emb_weight, emb_bias, scale_x, scale_y, radius, pair):
+    b, h, w, features = f_a.shape
+    k = (2 * radius + 1) ** 2 if radius >= 0 else 0
+    return f_a.new_empty((b, h, w, 2 * features + emb_weight.shape[0] + k), dtype=torch.bfloat16)
+
+
 @torch.library.custom_op("flashim_b200::romav2_refiner_heads", mutates_args=())
 def romav2_refiner_heads_launch(z: Tensor, weight: Tensor, bias: Tensor, prev_warp: Tensor, prev_confidence: Tensor,
                                 inv_norm_x: float, inv_norm_y: float) -> tuple[Tensor, Tensor]:
@@ -596,6 +618,25 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         @ops.depthwise5x5_act_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_act_when)
         def depthwise5x5_act_mxfp8(value, weight, bias, act="gelu"):
             return dw5x5_mxfp8(_nhwc(value), weight, bias, act_code[act], True)
+
+    if hasattr(ops, "romav2_refiner_input"):
+        def input_when(f_a, f_b, warp, emb_weight, emb_bias, scale_factor, radius, pair=0):
+            # the conditions of FlashIM's own fused implementation (flashim/backends/triton/romav2.py:292-303)
+            return (
+                have() and _cuda(f_a, f_b, warp, emb_weight, emb_bias) and f_a.ndim == 4
+                and f_a.dtype == f_b.dtype == warp.dtype == torch.float32 and f_a.is_contiguous() and f_b.is_contiguous()
+                and warp.is_contiguous() and f_a.shape == f_b.shape and f_a.shape[-1] % 4 == 0 and f_a.shape[-1] <= 256
+                and emb_weight.numel() == 2 * emb_weight.shape[0] and radius <= 3 and f_a.numel() > 0
+                and (pair == 0 or f_a.shape[0] == 2 * pair)
+            )
+
+        @ops.romav2_refiner_input.register("sm100", device=spec, requires=dw_requires, priority=3, when=input_when)
+        def romav2_refiner_input(f_a, f_b, warp, emb_weight, emb_bias, scale_factor, radius, pair=0):
+            scale = scale_factor.detach().float().cpu().tolist() if isinstance(scale_factor, Tensor) else list(scale_factor)
+            rows = romav2_refiner_input_launch(
+                f_a, f_b, warp, emb_weight.reshape(emb_weight.shape[0], 2).float().contiguous(), emb_bias.float().contiguous(),
+                float(scale[0]), float(scale[1]), int(radius), int(pair))
+            return rows.permute(0, 3, 1, 2)
 
     if hasattr(ops, "romav2_refiner_heads"):
         def heads_when(z, weight, bias, prev_warp, prev_confidence, refine_init):

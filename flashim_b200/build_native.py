@@ -15,7 +15,7 @@ import sys
 from pathlib import Path
 
 PACKAGE = Path(__file__).resolve().parent
-SOURCES = ("quantize.cu", "depthwise.cu", "conv.cu", "refiner_heads.cu")
+SOURCES = ("quantize.cu", "depthwise.cu", "conv.cu", "refiner_heads.cu", "refiner_input.cu")
 HEADERS = ("common.cuh",)
 INCLUDE = PACKAGE.parent / "include"
 OUTPUT = PACKAGE / "_lib" / "libflashim_sm100.so"

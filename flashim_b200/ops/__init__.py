@@ -29,6 +29,9 @@ int8_conv2d_maxpool = Op("int8_conv2d_maxpool", doc="(x, weight, a_scale, w_scal
                          "out_scale) -> (bf16 [B, Ho, Wo, Cout], int8 [B, Ho/2, Wo/2, Cout]): int8_conv2d and its 2x2 max "
                          "pool quantised with out_scale (flashim/ops/conv.py:209-222)")
 
+romav2_refiner_input = Op("romav2_refiner_input", doc="(f_a, f_b [B, h, w, P] fp32, warp [B, h, w, 2], emb_weight [E, 2(, 1, 1)], "
+                          "emb_bias [E], scale_factor [2], radius, pair=0) -> bf16 channels-last [B, 2P + E + K, h, w]: "
+                          "[f_a, f_b at the warp, displacement embedding, local correlation] (flashim/ops/romav2.py:36-66)")
 romav2_refiner_heads = Op("romav2_refiner_heads", doc="(z [B, C, h, w] channels-last, weight [6, C], bias [6], prev_warp "
                           "[B, h, w, 2], prev_confidence [B, h, w, 1 or 4], refine_init) -> (warp fp32 [B, h, w, 2], confidence "
                           "fp32 [B, h, w, 4]): warp / confidence 1x1 heads, warp update and precision parameters "

@@ -108,6 +108,22 @@ int fim_romav2_refiner_heads(const void* z, const float* weight, const float* bi
                              const float* prev_confidence, int prev_channels, float* warp, float* confidence, long long rows,
                              int channels, float inv_norm_x, float inv_norm_y, void* stream);
 
+/* The refiner's input row per pixel of A, bf16 [batch, height, width, 2 * features + embedding + K] (the NHWC memory of a
+ * channels-last tensor), K = (2 * radius + 1)^2 or 0 for radius < 0:
+ *   [0, P)            f_a
+ *   [P, 2P)           f_b sampled bilinearly at warp (x, y in [-1, 1], align_corners = False, zeros outside)
+ *   [2P, 2P + E)      emb_weight[e, 0] * scale_x * dx + emb_weight[e, 1] * scale_y * dy + emb_bias[e], (dx, dy) = warp - the
+ *                     pixel's own normalised coordinates
+ *   [2P + E, .. + K)  sum_c f_a[c] / sqrt(P) * f_b sampled at warp + ((kx - r) * 2 / width, (ky - r) * 2 / height), k = ky * (2r + 1) + kx
+ * `f_a`, `f_b` fp32 [batch, height, width, features] (16-byte aligned, features % 4 == 0, <= 256), `warp` fp32 [.., 2],
+ * `emb_weight` fp32 [embedding, 2], `emb_bias` fp32 [embedding], radius <= 3. pair > 0: batch == 2 * pair and image i is
+ * matched with image (i + pair) % batch of `f_a` (`f_b` is ignored).
+ * Replaces: ops.romav2_refiner_input (flashim/ops/romav2.py:36-66), Triton `refiner_input`
+ * (flashim/backends/triton/romav2.py). */
+int fim_romav2_refiner_input(const float* f_a, const float* f_b, const float* warp, const float* emb_weight, const float* emb_bias,
+                             float scale_x, float scale_y, void* out, int batch, int height, int width, int features,
+                             int embedding, int radius, int pair, void* stream);
+
 /* ---- depthwise 5x5 (pad 2, stride 1) -------------------------------------------------------------------------- */
 
 /* out[b,y,x,c] = act(sum_{ky,kx} value[b,y+ky-2,x+kx-2,c] * weight[ky*5+kx, c] + bias[c]) with fp32 accumulation

@@ -34,7 +34,7 @@ __all__ = [
     "pack_int8_conv_weight", "gather_taps", "conv_out_size", "mx_matmul_fp32", "int8_matmul_int32",
     "mxfp8_conv2d", "int8_conv2d", "add_residual", "depthwise5x5_fp32", "depthwise5x5_relu_mxfp8",
     "depthwise5x5_relu_int8", "depthwise5x5_act_ext", "depthwise5x5_act_mxfp8_ext", "mxfp8_conv2d_ext",
-    "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "romav2_refiner_heads", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
+    "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "romav2_refiner_input", "romav2_refiner_heads", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
     "dequantize_mx",
 ]
 
@@ -280,6 +280,33 @@ def int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, p
     out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
     pooled = F.max_pool2d(out.permute(0, 3, 1, 2).float(), 2).permute(0, 2, 3, 1).to(torch.bfloat16)
     return out, quantize_int8(pooled, out_scale.float().reshape(()))
+
+
+def romav2_refiner_input(f_a, f_b, warp, emb_weight, emb_bias, scale_factor, radius, pair=0):
+    """RoMaV2 refiner input, bf16 channels-last ``[B, 2P + E + K, h, w]`` from fp32 ``f_a`` / ``f_b [B, h, w, P]`` and
+    ``warp [B, h, w, 2]``: ``f_a``; ``f_b`` sampled at the warp (bilinear, zeros padding, ``align_corners=False``); the 1x1
+    conv ``[E, 2]`` of ``scale_factor * (warp - identity grid)``; and, for ``radius >= 0``, the dot products of
+    ``f_a / sqrt(P)`` with ``f_b`` sampled on the ``(2r+1)^2`` window of one-pixel steps around the warp, ``k = ky (2r+1) +
+    kx``. ``pair > 0``: image ``i`` of ``f_a`` is matched with image ``(i + pair) % (2 pair)`` of ``f_a``
+    (flashim/ops/romav2.py:36-66, flashim/ops/correlation.py:13-39)."""
+    if pair > 0:
+        f_b = torch.roll(f_a, shifts=pair, dims=0)
+    b, h, w, p = f_a.shape
+    a, other = f_a.permute(0, 3, 1, 2), f_b.permute(0, 3, 1, 2)
+    sample = lambda grid: F.grid_sample(other, grid, mode="bilinear", padding_mode="zeros", align_corners=False)  # noqa: E731
+    gy, gx = torch.meshgrid(torch.linspace(-1 + 1 / h, 1 - 1 / h, h), torch.linspace(-1 + 1 / w, 1 - 1 / w, w), indexing="ij")
+    displacement = (warp - torch.stack((gx, gy), dim=-1)).permute(0, 3, 1, 2)
+    embedding = F.conv2d(scale_factor[None, :, None, None] * displacement, emb_weight.reshape(-1, 2, 1, 1), emb_bias)
+    parts = [a, sample(warp), embedding]
+    if radius >= 0:
+        steps = 2 * radius + 1
+        oy, ox = torch.meshgrid(torch.linspace(-2 * radius / h, 2 * radius / h, steps),
+                                torch.linspace(-2 * radius / w, 2 * radius / w, steps), indexing="ij")
+        offsets = torch.stack((ox, oy), dim=-1).reshape(-1, 2)                       # [K, 2], x first
+        coords = (warp[:, :, :, None, :] + offsets).reshape(b, h, w * steps * steps, 2)
+        sampled = sample(coords).reshape(b, p, h, w, steps * steps)
+        parts.append(((a[..., None] / p**0.5) * sampled).sum(dim=1).permute(0, 3, 1, 2))
+    return torch.cat(parts, dim=1).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
 
 
 def romav2_refiner_heads(z, weight, bias, prev_warp, prev_confidence, refine_init):

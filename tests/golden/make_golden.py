@@ -242,6 +242,14 @@ def widening() -> None:
         arrays.update({f"heads{i}_z": raw(z.permute(0, 2, 3, 1)), f"heads{i}_w": raw(weight), f"heads{i}_b": raw(bias),
                        f"heads{i}_pw": raw(prev_warp), f"heads{i}_pc": raw(prev_conf), f"heads{i}_warp": raw(warp),
                        f"heads{i}_conf": raw(conf)})
+    for i, (b, h, w, p, e, radius, pair) in enumerate([(2, 6, 7, 32, 16, 3, 0), (2, 5, 4, 64, 8, 1, 1), (1, 4, 5, 16, 4, -1, 0)]):
+        f_a, f_b = torch.randn(b, h, w, p, generator=g), torch.randn(b, h, w, p, generator=g)
+        warp = torch.rand(b, h, w, 2, generator=g) * 2.6 - 1.3  # partly outside the image
+        emb_w, emb_b = torch.randn(e, 2, 1, 1, generator=g), torch.randn(e, generator=g)
+        out = ops.romav2_refiner_input.get("reference")(f_a, f_b, warp, emb_w, emb_b, torch.tensor([3.0, 2.0]), radius, pair)
+        arrays.update({f"rin{i}_fa": raw(f_a), f"rin{i}_fb": raw(f_b), f"rin{i}_warp": raw(warp), f"rin{i}_ew": raw(emb_w),
+                       f"rin{i}_eb": raw(emb_b), f"rin{i}_out": raw(out.permute(0, 2, 3, 1)),
+                       f"rin{i}_cfg": np.asarray([radius, pair])})
     save("widening", **arrays)
 
 

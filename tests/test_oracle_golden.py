@@ -274,3 +274,15 @@ def test_refiner_heads_match_reference_outputs(golden):
         z = g(f"heads{i}_z", BF16).permute(0, 3, 1, 2)
         warp, conf = oracle.romav2_refiner_heads(z, g(f"heads{i}_w"), g(f"heads{i}_b"), g(f"heads{i}_pw"), g(f"heads{i}_pc"), 4.0)
         assert torch.equal(warp, g(f"heads{i}_warp")) and torch.equal(conf, g(f"heads{i}_conf")), f"case {i}"
+
+
+def test_refiner_input_matches_reference_outputs(golden):
+    """romav2_refiner_input (flashim/ops/romav2.py:36-66) incl. local correlation, stacked directions and warps that leave
+    the image: the oracle batches the window samples differently, the bf16 bytes are the same."""
+    g = golden("widening")
+    for i in range(3):
+        radius, pair = (int(v) for v in g(f"rin{i}_cfg"))
+        out = oracle.romav2_refiner_input(g(f"rin{i}_fa"), g(f"rin{i}_fb"), g(f"rin{i}_warp"), g(f"rin{i}_ew"), g(f"rin{i}_eb"),
+                                          torch.tensor([3.0, 2.0]), radius, pair)
+        assert out.is_contiguous(memory_format=torch.channels_last)
+        assert same_bytes(out.permute(0, 2, 3, 1), g(f"rin{i}_out", BF16)), f"case {i}"
