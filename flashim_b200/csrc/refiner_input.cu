@@ -47,9 +47,10 @@ __global__ void __launch_bounds__(32 * kInputWarps) refiner_input_kernel(const I
 
   for (long long pixel = blockIdx.x * static_cast<long long>(kInputWarps) + warp_id; pixel < pixels;
        pixel += static_cast<long long>(gridDim.x) * kInputWarps) {
-    const int x = static_cast<int>(pixel % p.width);
-    const int y = static_cast<int>((pixel / p.width) % p.height);
-    const int b = static_cast<int>(pixel / (static_cast<long long>(p.width) * p.height));
+    const unsigned flat = static_cast<unsigned>(pixel);  // the host refuses more than 2**31 pixels
+    const int x = static_cast<int>(flat % static_cast<unsigned>(p.width));
+    const int y = static_cast<int>((flat / static_cast<unsigned>(p.width)) % static_cast<unsigned>(p.height));
+    const int b = static_cast<int>(flat / (static_cast<unsigned>(p.width) * static_cast<unsigned>(p.height)));
     const int b_other = p.pair > 0 ? (b + p.batch - p.pair) % p.batch : b;  // f_b = roll(f_a, pair) along the batch
     const float* other = p.f_b + static_cast<long long>(b_other) * p.height * p.width * P;
     __nv_bfloat16* out = p.out + pixel * C;
@@ -133,6 +134,53 @@ __global__ void __launch_bounds__(32 * kInputWarps) refiner_input_kernel(const I
   }
 }
 
+// Without a correlation window (radius < 0, RoMaV2's full-resolution refiner with 12 features) a pixel is little work:
+// eight lanes share one, so a warp handles four pixels at a time.
+__global__ void __launch_bounds__(256) refiner_input_plain_kernel(const InputParams p) {
+  const int P = p.features, E = p.embedding, C = 2 * P + E;
+  const unsigned pixels = static_cast<unsigned>(p.batch) * p.height * p.width;
+  const int sub = threadIdx.x & 7;
+  for (unsigned pixel = blockIdx.x * 32u + (threadIdx.x >> 3); pixel < pixels; pixel += gridDim.x * 32u) {
+    const int x = static_cast<int>(pixel % static_cast<unsigned>(p.width));
+    const int y = static_cast<int>((pixel / static_cast<unsigned>(p.width)) % static_cast<unsigned>(p.height));
+    const int b = static_cast<int>(pixel / (static_cast<unsigned>(p.width) * static_cast<unsigned>(p.height)));
+    const int b_other = p.pair > 0 ? (b + p.batch - p.pair) % p.batch : b;
+    const float* other = p.f_b + static_cast<long long>(b_other) * p.height * p.width * P;
+    __nv_bfloat16* out = p.out + static_cast<long long>(pixel) * C;
+    const float2 at = __ldg(reinterpret_cast<const float2*>(p.warp) + pixel);
+    const float ix = ((at.x + 1.0f) * p.width - 1.0f) * 0.5f, iy = ((at.y + 1.0f) * p.height - 1.0f) * 0.5f;
+    const float fx0 = floorf(ix), fy0 = floorf(iy);
+    const float tx = ix - fx0, ty = iy - fy0;
+    const float w_nw = (1.0f - tx) * (1.0f - ty), w_ne = tx * (1.0f - ty), w_sw = (1.0f - tx) * ty, w_se = tx * ty;
+    const int x0 = static_cast<int>(fminf(fmaxf(fx0, -16.0f), static_cast<float>(p.width) + 16.0f));
+    const int y0 = static_cast<int>(fminf(fmaxf(fy0, -16.0f), static_cast<float>(p.height) + 16.0f));
+    const bool finite = fabsf(ix) < 1e9f && fabsf(iy) < 1e9f;
+    const bool north = finite && y0 >= 0 && y0 < p.height, south = finite && y0 + 1 >= 0 && y0 + 1 < p.height;
+    const bool west = x0 >= 0 && x0 < p.width, east = x0 + 1 >= 0 && x0 + 1 < p.width;
+    const float* base = other + (static_cast<long long>(y0) * p.width + x0) * P;
+    const long long down = static_cast<long long>(p.width) * P;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 4 * sub; c < P; c += 32) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p.f_a + static_cast<long long>(pixel) * P + c));
+      const float4 nw = north && west ? __ldg(reinterpret_cast<const float4*>(base + c)) : zero;
+      const float4 ne = north && east ? __ldg(reinterpret_cast<const float4*>(base + P + c)) : zero;
+      const float4 sw = south && west ? __ldg(reinterpret_cast<const float4*>(base + down + c)) : zero;
+      const float4 se = south && east ? __ldg(reinterpret_cast<const float4*>(base + down + P + c)) : zero;
+      store_bf16(out + c, a.x), store_bf16(out + c + 1, a.y), store_bf16(out + c + 2, a.z), store_bf16(out + c + 3, a.w);
+      store_bf16(out + P + c, nw.x * w_nw + ne.x * w_ne + sw.x * w_sw + se.x * w_se);
+      store_bf16(out + P + c + 1, nw.y * w_nw + ne.y * w_ne + sw.y * w_sw + se.y * w_se);
+      store_bf16(out + P + c + 2, nw.z * w_nw + ne.z * w_ne + sw.z * w_sw + se.z * w_se);
+      store_bf16(out + P + c + 3, nw.w * w_nw + ne.w * w_ne + sw.w * w_sw + se.w * w_se);
+    }
+    const float dx = p.scale_x * (at.x - (-1.0f + (2.0f * x + 1.0f) / p.width));
+    const float dy = p.scale_y * (at.y - (-1.0f + (2.0f * y + 1.0f) / p.height));
+    for (int e = sub; e < E; e += 8) {
+      const float2 weight = __ldg(reinterpret_cast<const float2*>(p.emb_weight) + e);
+      store_bf16(out + 2 * P + e, fmaf(weight.y, dy, weight.x * dx) + __ldg(p.emb_bias + e));
+    }
+  }
+}
+
 }  // namespace
 }  // namespace fim
 
@@ -157,6 +205,13 @@ extern "C" int fim_romav2_refiner_input(const float* f_a, const float* f_b, cons
   p.scale_x = scale_x, p.scale_y = scale_y;
   p.root_features = static_cast<float>(sqrt(static_cast<double>(features)));
   const long long pixels = static_cast<long long>(batch) * height * width;
+  if (pixels >= 0x7fffffffLL) return kUnsupported;
+  if (radius < 0) {
+    const long long plain_blocks = (pixels + 31) / 32;
+    refiner_input_plain_kernel<<<static_cast<unsigned>(plain_blocks < 148LL * 32 ? plain_blocks : 148LL * 32), 256, 0,
+                                 static_cast<cudaStream_t>(stream)>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   const long long blocks = (pixels + kInputWarps - 1) / kInputWarps;
   const unsigned grid = static_cast<unsigned>(blocks < 148LL * 16 ? blocks : 148LL * 16);
   refiner_input_kernel<<<grid, 32 * kInputWarps, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -1,4 +1,4 @@
-"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|quant|heads|all]``.
+"""Shape sweep of the conv and depthwise kernels: ``python -m flashim_b200.sweep [conv|dw|quant|heads|input|all]``.
 
 Prints, as Markdown tables, the device time of each kernel over the shapes of BASELINE configs 3 and 4 (N = 4; conv
 100x100x512, 200x200x256, 400x400x128, 800x800x64 with k = 3 and k = 1, plain and with the fused bias + GELU + MXFP8
@@ -166,6 +166,27 @@ def heads_sweep() -> None:
     check_status()
 
 
+def input_sweep() -> None:
+    """RoMaV2 refiner input on the three refiner configurations (flashim/models/romav2/refiner.py:38-42), 8 images of a
+    560 x 560 pair at strides 4 / 2 / 1; warps = identity + noise of about one pixel."""
+    from flashim_b200 import check_status, ops
+
+    print("| refiner input | us | algorithmic GB/s |")
+    print("|---|---:|---:|")
+    for n, size, p, e, radius in ((8, 140, 192, 79, 3), (8, 280, 48, 23, 1), (8, 560, 12, 8, -1)):
+        f_a, f_b = torch.randn(n, size, size, p, device="cuda"), torch.randn(n, size, size, p, device="cuda")
+        line = torch.linspace(-1, 1, size, device="cuda")
+        gy, gx = torch.meshgrid(line, line, indexing="ij")
+        warp = (torch.stack((gx, gy), -1)[None] + torch.randn(n, size, size, 2, device="cuda") * (2.0 / size)).contiguous()
+        emb_w, emb_b = torch.randn(e, 2, device="cuda"), torch.randn(e, device="cuda")
+        scale = torch.tensor([3.0, 2.0])
+        ms = graph_time_ms(lambda: ops.romav2_refiner_input.get("sm100")(f_a, f_b, warp, emb_w, emb_b, scale, radius, 0))
+        k = (2 * radius + 1) ** 2 if radius >= 0 else 0
+        moved = n * size * size * (2 * p * 4 + 8 + (2 * p + e + k) * 2)
+        print(f"| {n}x{size}x{size}, P={p}, E={e}, r={radius} | {ms * 1e3:.1f} | {moved / ms / 1e6:.0f} |", flush=True)
+    check_status()
+
+
 def main() -> None:
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     if not torch.cuda.is_available():
@@ -181,6 +202,9 @@ def main() -> None:
     if which in ("heads", "all"):
         print()
         heads_sweep()
+    if which in ("input", "all"):
+        print()
+        input_sweep()
 
 
 if __name__ == "__main__":
