@@ -456,14 +456,14 @@ DEFAULT_WORKLOAD = "stack"
 # captures summarised under profiles/ (file named beside each figure); None where no capture exists.
 NCU_TRAFFIC: dict[str, float] = {
     # dw5x5_kernel depthwise + GELU -> MXFP8 on 8 x 400 x 400 x 128 (the launch the stack's roofline times), same shape for
-    # every --pairs >= 4: profiles/depthwise_mxfp8_refiner_level_400x400x128.md (418.54 MB read + 153.63 MB written)
-    "refiner-stack": 572.17e6,
+    # every --pairs >= 4: profiles/depthwise_mxfp8_refiner_level_400x400x128.md (418.53 MB read + 154.40 MB written)
+    "refiner-stack": 572.93e6,
     # profiles/conv_mxfp8_3x3_100x100x512.md (22.99 MB read; the 20 MB output is still in L2 when the kernel ends)
-    "mxfp8-conv-100x100x512-k3": 23.01e6,
+    "mxfp8-conv-100x100x512-k3": 23.05e6,
     # profiles/conv_int8_3x3_100x100x256.md
-    "int8-conv-100x100x256-k3": 5.80e6,
-    # profiles/depthwise_gelu_bf16_4x200x200x256.md (90.63 MB read + 36.52 MB written; the rest of the output in L2)
-    "depthwise5x5-gelu-4x200x200x256": 127.15e6,
+    "int8-conv-100x100x256-k3": 5.79e6,
+    # profiles/depthwise_gelu_bf16_4x200x200x256.md (88.71 MB read + 36.21 MB written; the rest of the output in L2)
+    "depthwise5x5-gelu-4x200x200x256": 124.92e6,
 }
 
 
