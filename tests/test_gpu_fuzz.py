@@ -100,3 +100,32 @@ def test_random_depthwise(ops, shape):
     want8 = oracle.depthwise5x5_relu_int8(x, w, b, scale)
     delta = (got8.int() - want8.int()).abs()
     assert int(delta.max()) <= 1 and float((delta > 0).float().mean()) < 5e-3
+
+
+def _widening_shapes(seed: int, count: int):
+    rng = random.Random(seed)
+    for _ in range(count):
+        yield rng.choice([1, 2, 3]), 16 * rng.randint(1, 18), rng.randint(1, 40), rng.randint(1, 40)
+
+
+@pytest.mark.parametrize("shape", list(_widening_shapes(31, 12)), ids=lambda s: "b%d_c%d_%dx%d" % s)
+def test_random_channels_first_quantisers_and_pool(ops, shape):
+    """Random NCHW shapes (pixel counts with and without the 4-pixel alignment of the vector loads, channel counts that end
+    inside a 64-channel tile) through the in-place quantisers, and the same tensor through the max-pool quantiser."""
+    b, c, h, w = shape
+    g = torch.Generator().manual_seed(hash(shape) & 0xFFFF)
+    nchw = (torch.randn(b, c, h, w, generator=g) * 4).to(BF16)
+    view = nchw.permute(0, 2, 3, 1)
+    e = oracle.static_block_exponent(view)
+    scale = torch.tensor(0.031)
+    device_view = to_dev(nchw).permute(0, 2, 3, 1)
+    assert same_bytes(ops.quantize_mxfp8.get("sm100")(device_view, to_dev(e)).values.cpu(), oracle.quantize_static_mx(view, e))
+    assert torch.equal(ops.quantize_int8.get("sm100")(device_view, to_dev(scale)).values.cpu(), oracle.quantize_int8(view, scale))
+    from flashim_b200.backends.sm100 import kernels
+
+    nhwc = view.contiguous()
+    pooled = kernels.maxpool2_quantize_int8(to_dev(nhwc), to_dev(scale.reshape(1)))
+    want = oracle.quantize_int8(F.max_pool2d(nchw.float(), 2).permute(0, 2, 3, 1).to(BF16), scale) if h > 1 and w > 1 else None
+    assert pooled.shape == (b, h // 2, w // 2, c)
+    if want is not None:
+        assert torch.equal(pooled.cpu(), want)
