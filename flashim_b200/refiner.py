@@ -87,20 +87,44 @@ class RefinerStack(nn.Module):
     """``forward(pyramid)``: a list of bf16 NHWC tensors (one per level, the same batch of direction-images) -> the list of
     head outputs. ``chunk`` images are processed at a time to bound the intermediate tensors."""
 
-    def __init__(self, levels=LEVELS, blocks: int = 4, seed: int = 4, chunk: int = 8) -> None:
+    def __init__(self, levels=LEVELS, blocks: int = 4, seed: int = 4, chunk: int = 8, lanes: int = 1) -> None:
         super().__init__()
         generator = torch.Generator().manual_seed(seed)
         self.level_shapes = tuple(levels)
         self.chunk = chunk
+        self.lanes = lanes
         self.levels = nn.ModuleList(RefinerLevel(c, blocks, generator) for _, c in levels)
+        self._side: dict = {}
 
     @torch.inference_mode()
     def forward(self, pyramid: list[Tensor]) -> list[Tensor]:
-        outputs = []
+        """Chunks are independent. With ``lanes > 1`` they alternate between that many streams (forked from and joined to
+        the current one, also inside a graph capture), so that the prologue of one chunk's kernel overlaps the tail of the
+        other's; the results are the same bytes."""
+        device = pyramid[0].device
+        lanes = self.lanes if device.type == "cuda" else 1
+        if lanes > 1:
+            main = torch.cuda.current_stream(device)
+            if device not in self._side:
+                self._side[device] = [torch.cuda.Stream(device) for _ in range(lanes - 1)]
+            streams = [main, *self._side[device][: lanes - 1]]
+            for stream in streams[1:]:
+                stream.wait_stream(main)
+        outputs, turn = [], 0
         for level, x in zip(self.levels, pyramid):
-            parts = [level(x[i: i + self.chunk]) for i in range(0, x.shape[0], self.chunk)]
-            outputs.append(parts[0] if len(parts) == 1 else torch.cat(parts))
-        return outputs
+            parts = []
+            for i in range(0, x.shape[0], self.chunk):
+                if lanes > 1:
+                    with torch.cuda.stream(streams[turn % lanes]):
+                        parts.append(level(x[i: i + self.chunk]))
+                    turn += 1
+                else:
+                    parts.append(level(x[i: i + self.chunk]))
+            outputs.append(parts)
+        if lanes > 1:
+            for stream in streams[1:]:
+                main.wait_stream(stream)
+        return [parts[0] if len(parts) == 1 else torch.cat(parts) for parts in outputs]
 
     def flops_per_image(self) -> float:
         """Algorithmic FLOPs of one direction-image through every level (1x1 convs: 2*C_in*C_out per pixel;
@@ -116,7 +140,8 @@ class RefinerStack(nn.Module):
 def _load(config: RunConfig) -> nn.Module:
     arch = config.arch
     levels = tuple(tuple(level) for level in arch.get("levels", LEVELS))
-    model = RefinerStack(levels, int(arch.get("blocks", 4)), int(arch.get("seed", 4)), int(arch.get("chunk", 8)))
+    model = RefinerStack(levels, int(arch.get("blocks", 4)), int(arch.get("seed", 4)), int(arch.get("chunk", 8)),
+                         int(arch.get("lanes", 2)))
     return model.to(config.device or "cuda").eval()
 
 
