@@ -69,12 +69,32 @@ def test_ops_without_a_reference_raise_instead_of_falling_back():
     assert "the call is on cpu" in report["sm100"] and report["reference"].startswith("none shipped")
 
 
+def test_widened_ops_decline_cpu_calls_and_say_why():
+    z = torch.zeros(1, 64, 4, 4, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    heads = (z, torch.zeros(6, 64), torch.zeros(6), torch.zeros(1, 4, 4, 2), torch.zeros(1, 4, 4, 1), 4.0)
+    with pytest.raises(NoImplementation, match="ships no fallback"):
+        ops.romav2_refiner_heads(*heads)
+    assert "the call is on cpu" in ops.romav2_refiner_heads.explain(*heads)["sm100"]
+    features = torch.zeros(1, 4, 4, 16)
+    with pytest.raises(NoImplementation):
+        ops.romav2_refiner_input(features, features, torch.zeros(1, 4, 4, 2), torch.zeros(8, 2), torch.zeros(8), torch.ones(2), 1)
+    with pytest.raises(NoImplementation):
+        ops.int8_conv2d_maxpool(torch.zeros(1, 4, 4, 32, dtype=torch.int8), torch.zeros(32, 32, dtype=torch.int8), torch.ones(()),
+                                torch.ones(32), None, 1, 1, 1, 1, 0, 0, 1, 1, relu=True, out_scale=torch.ones(()))
+    from flashim_b200.backends.sm100.kernels import _channels_first_view
+
+    nchw = torch.zeros(2, 8, 3, 5)
+    assert _channels_first_view(nchw.permute(0, 2, 3, 1)) and not _channels_first_view(nchw.permute(0, 2, 3, 1).contiguous())
+    assert not _channels_first_view(nchw) and not _channels_first_view(torch.zeros(4, 8))
+
+
 def test_the_sm100_backend_registers_for_capability_10_only():
     b200 = Platform("cuda", 0, "B200", (10, 0), frozenset({Feature.TCGEN05, Feature.TMA, Feature.SM100A_KERNELS}), "sm_100")
     rtx = Platform("cuda", 0, "RTX", (12, 0), frozenset({Feature.TMA}), "sm_120")
     h100 = Platform("cuda", 0, "H100", (9, 0), frozenset({Feature.TMA, Feature.WGMMA}), "sm_90")
     for name in ("mxfp8_conv2d", "int8_conv2d", "depthwise5x5_relu_mxfp8", "depthwise5x5_relu_int8", "quantize_mxfp8",
-                 "quantize_int8", "mxfp8_conv2d_fused", "depthwise5x5_act"):
+                 "quantize_int8", "mxfp8_conv2d_fused", "depthwise5x5_act", "int8_conv2d_maxpool", "mxfp8_scaled_mm",
+                 "int8_linear", "romav2_refiner_input", "romav2_refiner_heads"):
         op = OPS[name]
         assert [i.name for i in op.candidates(b200)] == ["sm100"], name
         assert op.candidates(rtx) == [] and op.candidates(h100) == [], name
