@@ -8,13 +8,15 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 from pathlib import Path
 
 LIBRARY_NAME = "libflashim_sm100.so"
-LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / LIBRARY_NAME
+#: the in-tree build; ``FLASHIM_B200_LIBRARY`` names another build of the same sources (e.g. one with measurement probes)
+LIBRARY_PATH = Path(os.environ.get("FLASHIM_B200_LIBRARY") or Path(__file__).resolve().parent / "_lib" / LIBRARY_NAME)
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
-ACT = {"none": 0, "relu": 1, "gelu": 2}
+ACT = {"none": 0, "relu": 1, "gelu": 2, "relu_early": 3}
 OUT_BF16, OUT_F32, OUT_E4M3_STATIC, OUT_E4M3_DYNAMIC, OUT_INT8, OUT_INT32 = range(6)
 
 ERRORS = {
@@ -74,8 +76,13 @@ SIGNATURES: dict[str, tuple] = {
     "fim_mxfp8_conv2d": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_int8_conv2d": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_conv_plan": (_I, [ctypes.POINTER(ConvGeometry), _I, _I, ctypes.POINTER(ctypes.c_int * 6)]),
+    "fim_conv_schedule": (_I, [ctypes.POINTER(ConvGeometry), _I, _I, ctypes.POINTER(ctypes.c_int * 8)]),
+}
+
+#: the schedule overrides of ``include/flashim_sm100_tune.h`` (tests and measurements only)
+TUNE_SIGNATURES: dict[str, tuple] = {
     "fim_conv_tune": (None, [_I, _I, _I]),
-    "fim_dw_tune": (None, [_I]),
+    "fim_dw_tune": (None, [_I, _I]),
 }
 
 
@@ -88,7 +95,7 @@ def library() -> ctypes.CDLL:
             "support). flashim_b200 has no fallback implementation."
         )
     lib = ctypes.CDLL(str(LIBRARY_PATH))
-    for name, (restype, argtypes) in SIGNATURES.items():
+    for name, (restype, argtypes) in {**SIGNATURES, **TUNE_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if the library and the header disagree
         fn.restype, fn.argtypes = restype, argtypes
     return lib

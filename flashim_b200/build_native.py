@@ -33,13 +33,16 @@ def source_digest() -> str:
     h = hashlib.sha256(" ".join(FLAGS).encode())
     for name in (*SOURCES, *HEADERS):
         h.update((PACKAGE / "csrc" / name).read_bytes())
-    h.update((INCLUDE / "flashim_sm100.h").read_bytes())
+    for name in ("flashim_sm100.h", "flashim_sm100_tune.h"):
+        h.update((INCLUDE / name).read_bytes())
     return h.hexdigest()[:16]
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, output: Path = OUTPUT, defines: tuple[str, ...] = ()) -> Path:
+    """Build the library (``output`` and ``defines`` serve measurement builds, e.g. ``-DFIM_PROBE_BUILD=1``)."""
+    OUTPUT = output
     stamp = OUTPUT.with_suffix(".digest")
-    digest = source_digest()
+    digest = source_digest() + "".join(defines)
     if not force and OUTPUT.is_file() and stamp.is_file() and stamp.read_text().strip() == digest:
         return OUTPUT
     nvcc = nvcc_path()
@@ -47,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError("nvcc not found: cannot build the sm_100a kernels")
     OUTPUT.parent.mkdir(parents=True, exist_ok=True)
     temporary = OUTPUT.with_suffix(f".{os.getpid()}.tmp")
-    command = [nvcc, *FLAGS, f"-I{INCLUDE}", *(["-Xptxas", "-v"] if verbose else []), "-o", str(temporary),
+    command = [nvcc, *FLAGS, *defines, f"-I{INCLUDE}", *(["-Xptxas", "-v"] if verbose else []), "-o", str(temporary),
                *(str(PACKAGE / "csrc" / s) for s in SOURCES)]
     result = subprocess.run(command, capture_output=True, text=True, check=False)
     if result.returncode != 0:

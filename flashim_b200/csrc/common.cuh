@@ -547,7 +547,7 @@ __device__ __forceinline__ float gelu_fast(float x) {
   return lo;
 }
 
-constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2;
+constexpr int kActNone = 0, kActRelu = 1, kActGelu = 2, kActReluEarly = 3;
 __device__ __forceinline__ float activate(float x, int act) {
   if (act == kActRelu) return fmaxf(x, 0.0f);
   if (act == kActGelu) return gelu_erf(x);
@@ -560,6 +560,24 @@ __device__ __forceinline__ size_t swizzled_scale_offset(size_t row, int group, i
 }
 
 #endif  // __CUDACC__
+
+// ---- host: per-device facts ------------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+  int device = -1;
+  return cudaGetDevice(&device) == cudaSuccess ? device : -1;
+}
+// SMs of the current device (148 on a B200), asked once per device; persistent grids are sized from it.
+inline int sm_count() {
+  static int cached[kMaxDevices] = {};
+  const int device = current_device();
+  if (device < 0 || device >= kMaxDevices) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    cached[device] = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && n > 0 ? n : 148;
+  }
+  return cached[device];
+}
 
 // ---- host: tensor maps without linking libcuda ---------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -18,6 +18,7 @@
 // Rounding points follow FlashIM's torch reference: flashim/ops/conv.py:174-206,309-342 and flashim/ops/gemm.py:58-98.
 #include "common.cuh"
 #include "flashim_sm100.h"
+#include "flashim_sm100_tune.h"
 
 namespace fim {
 namespace {
@@ -57,8 +58,15 @@ struct ConvParams {
   uint8_t* out_scales;
   const float* out_scale;
   int* status;
-  int debug;  // timing experiments only: 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
+  int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
+
+// Measurement switches that make results invalid exist only in a build with -DFIM_PROBE_BUILD=1; the shipped kernels carry
+// no test of them.
+#ifndef FIM_PROBE_BUILD
+#define FIM_PROBE_BUILD 0
+#endif
+__device__ __forceinline__ int probe_flags(const ConvParams& p) { return FIM_PROBE_BUILD ? p.debug : 0; }
 
 struct SharedControl {
   uint64_t full[kMaxStages];
@@ -67,6 +75,7 @@ struct SharedControl {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int group_go[4][2];  // epilogue: did the accumulator of tile (parity) arrive? One decision per column group
 };
 
 constexpr int kMaxStaticScaleTiles = 16;  // input channels / 128 whose activation scales stay resident in tensor memory
@@ -84,6 +93,29 @@ __device__ __forceinline__ uint32_t idesc_i8(int block_n, int block_m = kTileM) 
   // S32 accumulator (2), signed 8-bit A and B (1), both K-major, M = block_m, N = block_n
   return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(block_n >> 3) << 17) |
          (static_cast<uint32_t>(block_m >> 4) << 24);
+}
+
+#include "gelu_table.inc"
+
+// GELU of two bf16 values in one word, as bf16: the erf form torch evaluates (x * 0.5 * (1 + erf(x / sqrt 2)) in fp32,
+// rounded to bf16), looked up instead of computed. `table` is the shared-memory copy of kGeluTable: per magnitude a
+// 16-bit delta for either sign; result magnitude = max(a + delta, 0), result sign = input sign. Magnitudes below
+// kGeluBase share entry 0 (half the value: the exponent drops by one; zero stays zero), those above the table share the
+// last entry (x itself for positive values, -0 for negative ones). Exact for every bf16 input except subnormals, which
+// become zero. Thirteen integer instructions per pair and no MUFU; the arithmetic form costs about forty.
+__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, uint32_t table) {
+  constexpr uint32_t kNegBase = ((0x10000u - static_cast<uint32_t>(kGeluBase - 1)) & 0xFFFFu) * 0x00010001u;
+  constexpr uint32_t kLast = static_cast<uint32_t>(kGeluEntries - 1) * 0x00010001u;
+  const uint32_t a = r & 0x7FFF7FFFu;
+  const uint32_t t = __viaddmin_s16x2_relu(a, kNegBase, kLast);  // clamp(a - (base - 1), 0, entries - 1) in each half
+  uint32_t w0, w1, negative;
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(table + ((t & 0xFFFFu) << 2)));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w1) : "r"(table + ((t >> 16) << 2)));
+  // byte 0 of `negative` = 0xFF when the low value is negative, byte 1 the same for the high value (sign replication of
+  // bytes 1 and 3); each byte steers two selector nibbles: bytes 2-3 of w0 / w1 (the delta for negative values) or 0-1
+  asm("prmt.b32 %0, %1, %2, 0x00B9;" : "=r"(negative) : "r"(r), "r"(0u));
+  const uint32_t delta = __byte_perm(w0, w1, (negative & 0x2222u) | 0x5410u);
+  return __viaddmax_s16x2(a, delta, 0u) | (r & 0x80008000u);
 }
 
 // ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
@@ -175,16 +207,12 @@ __device__ __forceinline__ void round_chunk(const ConvParams& p, const uint32_t 
 // output format.
 template <bool INT8>
 __device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[16], int n, size_t pixel, int b, int y, int x,
-                                             bool valid, uint32_t (&w)[16]) {
+                                             bool valid, uint32_t gelu_table, uint32_t (&w)[16]) {
   const bool has_res = p.residual != nullptr;
   if (p.act == kActGelu) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float lo, hi;
-      unpack2(gelu_fast2(bf16x2_to_f32x2(r[i])), lo, hi);
-      r[i] = pack_bf16(lo, hi);
-    }
-  } else if (p.act == kActRelu && !has_res) {
+    for (int i = 0; i < 16; ++i) r[i] = gelu_bf16x2(r[i], gelu_table);
+  } else if (p.act == kActReluEarly || (p.act == kActRelu && !has_res)) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) r[i] = bf16x2_max(r[i], 0u);
   }
@@ -334,6 +362,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
+  const uint32_t smem_gelu = smem_bias + p.tiles_n * BN * 4;                 // kGeluTable, when the epilogue applies GELU
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dynamic_a = !INT8 && p.act_scales != nullptr;
@@ -388,6 +417,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias + i * 4), "f"(value) : "memory");
     }
   }
+  if (p.act == kActGelu) {
+    for (int i = threadIdx.x; i < kGeluEntries; i += kThreads) {
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(smem_gelu + i * 4), "r"(kGeluTable[i]) : "memory");
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (PAIR) cluster_sync();  // the other CTA's barriers and static scale tiles exist before anything refers to them
@@ -401,7 +435,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     // ===== TMA producer =====
     if (lane == 0) {
       const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
-      const bool load_a = !(p.debug & 1), load_b = !(p.debug & 2);
+      const bool load_a = !(probe_flags(p) & 1), load_b = !(probe_flags(p) & 2);
       uint32_t s = 0, phase = 0;
       bool alive = true;
       int last_n0 = -1;
@@ -503,7 +537,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
       const int k_iters = taps * p.k_chunks;
-      const bool copy_scales = !INT8 && !(p.debug & 8);
+      const bool copy_scales = !INT8 && !(probe_flags(p) & 8);
       if (!INT8 && !dynamic_a) {
         // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
         const int tiles = (p.cin + 127) / 128;
@@ -622,7 +656,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
     const uint32_t panels = smem_out + group * p.panels_per_half * panel_bytes;
-    const bool store = !(p.debug & 4);
+    const bool store = !(probe_flags(p) & 4);
     constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = worker; tile < p.total_tiles; tile += workers, ++tile_it) {
@@ -648,7 +682,19 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                                                           n_first));
         }
       }
-      if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.debug & 32 ? 0u : 200u)) break;
+      // One warp of the group waits for the accumulator (sleeping between polls: the main loop of a tile takes
+      // microseconds) and publishes whether it arrived; the four warps then take the same decision, so none of them can
+      // be left alone at a named barrier below when a wait runs out. The word alternates with the tile parity: the
+      // deciding warp cannot be two tiles ahead of a sibling, which it meets at this barrier every tile.
+      volatile int* go = &ctl.group_go[group][tile_it & 1u];
+      if (quarter == 0) {
+        const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, 200u);
+        if (lane == 0) *go = arrived ? 1 : 0;
+        __syncwarp();
+      }
+      named_barrier(bar_id, 128);
+      if (*go == 0) break;
+      mbar_try_addr(tfull0 + 8 * acc, acc_phase);  // the phase is complete: this observes it for this warp too
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
       // Drain: every chunk of this warp is read, biased and rounded to bf16x2 words first (16 registers per chunk), and
@@ -717,7 +763,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const int n = n0 + group * kGroupColumns + g * 32;
           if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
-          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, w);
+          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, smem_gelu, w);
           const uint32_t panel = take_panel();
           stage_row<16>(panel, row, p.out_elem, w);
           send_panel(panel, n);
@@ -770,7 +816,7 @@ int out_elem_bytes(int out_mode) {
   }
 }
 
-int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_flat, int out_elem, Plan* plan) {
+int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan) {
   if (g.batch <= 0 || g.height <= 0 || g.width <= 0 || g.cin <= 0 || g.cout <= 0) return kBadArgument;
   if (g.cin % 32 || g.cout % 32) return kUnsupported;
   if (g.stride_h != 1 || g.stride_w != 1) return kUnsupported;
@@ -831,16 +877,55 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
   const int epilogue_groups = bn >= 128 ? 4 : 2;
-  const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes;
+  const int gelu_bytes = gelu ? (kGeluEntries * 4 + 15) / 16 * 16 : 0;
+  const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
   pl.smem = static_cast<size_t>(fixed) + static_cast<size_t>(pl.stages) * stage_bytes;
-  const int sms = g_max_ctas > 0 && g_max_ctas < 148 ? g_max_ctas : 148;
+  const int device_sms = sm_count();
+  const int sms = g_max_ctas > 0 && g_max_ctas < device_sms ? g_max_ctas : device_sms;
   pl.ctas = pl.total_tiles < sms ? pl.total_tiles : sms;
   if (pl.pair) pl.ctas = 2 * (pl.total_tiles < sms / 2 ? pl.total_tiles : sms / 2);
   *plan = pl;
   return kOk;
+}
+
+// What the persistent CTAs walk: the tile list (with the last partial round cut into half-width tiles when that halves
+// its duration), the tile order and how many K iterations keep their weight scales resident in tensor memory.
+struct Schedule {
+  int total_tiles, full_tiles, resident_k, n_major;
+};
+
+Schedule make_schedule(const FimConvGeometry& g, const Plan& pl, bool int8, bool per_pixel) {
+  Schedule sc;
+  sc.total_tiles = pl.total_tiles, sc.full_tiles = pl.total_tiles, sc.resident_k = 0, sc.n_major = 0;
+  if (pl.block_n == 256 && !pl.pair && pl.total_tiles > pl.ctas) {
+    // the last round of the persistent CTAs: when at most half of them would have a tile, two half-width tiles each
+    // finish it in half the time
+    const int rest = pl.total_tiles % pl.ctas;
+    if (rest > 0 && 2 * rest <= pl.ctas && !(g_debug_flags & 16)) {
+      sc.full_tiles = pl.total_tiles - rest;
+      sc.total_tiles = sc.full_tiles + 2 * rest;
+    }
+  }
+  if (!int8 && pl.block_k == 128 && !(g_debug_flags & 256)) {
+    // Tensor-memory columns left after the accumulators, the per-stage scale sets and the activation scales hold the
+    // weight scales of the first K iterations for as long as consecutive tiles of a CTA share their output channels.
+    // That needs the row tiles of one channel tile to follow each other, which re-reads the activations once per channel
+    // tile: fine when they stay in L2 or the layer is compute-bound, not for a wide memory-bound layer.
+    const int sfb_columns = pl.block_n < 128 ? 4 : pl.block_n / 32;
+    const int sfa_columns = 4 * (per_pixel ? pl.stages : (g.cin + 127) / 128);
+    const int room = 512 - acc_stages(pl.block_n) * pl.block_n - pl.stages * sfb_columns - sfa_columns;
+    const int k_iters = g.kh * g.kw * (g.cin / pl.block_k);
+    const long long activation_bytes = static_cast<long long>(g.batch) * g.height * g.width * g.cin;
+    const bool cheap_reread = pl.tiles_n == 1 || k_iters >= 8 || activation_bytes <= (48LL << 20);
+    if (room >= sfb_columns && cheap_reread) {
+      sc.resident_k = room / sfb_columns < k_iters ? room / sfb_columns : k_iters;
+      sc.n_major = 1;
+    }
+  }
+  return sc;
 }
 
 struct ConvMaps {
@@ -849,12 +934,14 @@ struct ConvMaps {
 
 template <bool INT8, int BN, int BK, bool PAIR>
 int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory opt-in is a per-device attribute of the function: set once per device and instantiation
+  static bool configured[kMaxDevices] = {};
+  const int device = current_device();
+  if (device < 0 || device >= kMaxDevices || !configured[device]) {
     const cudaError_t e =
         cudaFuncSetAttribute(conv_kernel<INT8, BN, BK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
   if (PAIR) {
     cudaLaunchConfig_t config = {};
@@ -896,12 +983,11 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   if (g == nullptr || ep == nullptr) return kBadArgument;
   if (g->batch == 0 || g->height == 0 || g->width == 0) return kOk;
   if (x == nullptr || weight == nullptr || out == nullptr) return kBadArgument;
-  if (ep->act < 0 || ep->act > 2 || ep->out_mode < 0 || ep->out_mode > 5) return kBadArgument;
+  if (ep->act < 0 || ep->act > 3 || ep->out_mode < 0 || ep->out_mode > 5) return kBadArgument;
   if (int8) {
     if (ep->out_mode != FIM_OUT_INT32 && (a_scale == nullptr || w_scale == nullptr)) return kBadArgument;
     if (ep->out_mode != FIM_OUT_BF16 && ep->out_mode != FIM_OUT_INT8 && ep->out_mode != FIM_OUT_INT32) return kBadArgument;
     if (ep->out_mode == FIM_OUT_INT8 && ep->out_scale == nullptr) return kBadArgument;
-    if (ep->act == FIM_ACT_GELU) return kUnsupported;
   } else {
     if (weight_scales == nullptr || (act_exponent == nullptr) == (act_scales == nullptr)) return kBadArgument;
     if (ep->out_mode == FIM_OUT_INT8 || ep->out_mode == FIM_OUT_INT32) return kBadArgument;
@@ -919,7 +1005,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   Plan pl;
   {
     Plan probe;
-    const int rc0 = make_plan(*g, int8, act_scales != nullptr, true, out_elem, &probe);
+    const int rc0 = make_plan(*g, int8, act_scales != nullptr, true, out_elem, ep->act == FIM_ACT_GELU, &probe);
     if (rc0 != kOk) return rc0;
     if (probe.flat && ep->residual != nullptr) {
       const long long c = ep->res_stride[3], xs = ep->res_stride[2], ys = ep->res_stride[1], bs = ep->res_stride[0];
@@ -927,45 +1013,21 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
       if (!dense) allow_flat = false;
     }
   }
-  const int rc = make_plan(*g, int8, act_scales != nullptr, allow_flat, out_elem, &pl);
+  const int rc = make_plan(*g, int8, act_scales != nullptr, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl);
   if (rc != kOk) return rc;
 
+  const Schedule sc = make_schedule(*g, pl, int8, act_scales != nullptr);
   ConvParams p;
   p.cin = g->cin, p.cout = g->cout;
   p.out_h = pl.out_h, p.out_w = pl.out_w;
   p.kh = g->kh, p.kw = g->kw, p.pad_h = g->pad_h, p.pad_w = g->pad_w, p.dil_h = g->dil_h, p.dil_w = g->dil_w;
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
-  p.total_tiles = pl.total_tiles;
-  p.full_tiles = pl.total_tiles;
+  p.total_tiles = sc.total_tiles;
+  p.full_tiles = sc.full_tiles;
   p.batch = pl.flat ? 1 : g->batch;
-  if (pl.block_n == 256 && !pl.pair && pl.total_tiles > pl.ctas) {
-    // the last round of the persistent CTAs: when at most half of them would have a tile, two half-width tiles each
-    // finish it in half the time
-    const int rest = pl.total_tiles % pl.ctas;
-    if (rest > 0 && 2 * rest <= pl.ctas && !(g_debug_flags & 16)) {
-      p.full_tiles = pl.total_tiles - rest;
-      p.total_tiles = p.full_tiles + 2 * rest;
-    }
-  }
   p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages, p.panels_per_half = pl.panels_per_half;
   p.row_tiles = pl.total_tiles / pl.tiles_n;
-  p.resident_k = 0, p.n_major = 0;
-  if (!int8 && pl.block_k == 128 && !(g_debug_flags & 256)) {
-    // Tensor-memory columns left after the accumulators, the per-stage scale sets and the activation scales hold the
-    // weight scales of the first K iterations for as long as consecutive tiles of a CTA share their output channels.
-    // That needs the row tiles of one channel tile to follow each other, which re-reads the activations once per channel
-    // tile: fine when they stay in L2 or the layer is compute-bound, not for a wide memory-bound layer.
-    const int sfb_columns = pl.block_n < 128 ? 4 : pl.block_n / 32;
-    const int sfa_columns = 4 * (act_scales != nullptr ? pl.stages : (g->cin + 127) / 128);
-    const int room = 512 - acc_stages(pl.block_n) * pl.block_n - pl.stages * sfb_columns - sfa_columns;
-    const int k_iters = g->kh * g->kw * (g->cin / pl.block_k);
-    const long long activation_bytes = static_cast<long long>(g->batch) * g->height * g->width * g->cin;
-    const bool cheap_reread = pl.tiles_n == 1 || k_iters >= 8 || activation_bytes <= (48LL << 20);
-    if (room >= sfb_columns && cheap_reread) {
-      p.resident_k = room / sfb_columns < k_iters ? room / sfb_columns : k_iters;
-      p.n_major = 1;
-    }
-  }
+  p.resident_k = sc.resident_k, p.n_major = sc.n_major;
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;
@@ -1071,14 +1133,25 @@ extern "C" int fim_int8_conv2d(const void* x, const void* weight, const float* a
 extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]) {
   if (geometry == nullptr || plan == nullptr) return kBadArgument;
   Plan pl;
-  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, &pl);
+  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, false, &pl);
   if (rc != kOk) return rc;
   plan[0] = pl.tile_h, plan[1] = pl.tile_w, plan[2] = pl.block_n, plan[3] = pl.block_k, plan[4] = pl.stages, plan[5] = pl.ctas;
   return kOk;
 }
 
-extern "C" void fim_conv_tune(int block_n, int max_ctas, int debug_flags) {
+extern "C" int fim_conv_schedule(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int schedule[8]) {
+  if (geometry == nullptr || schedule == nullptr) return kBadArgument;
+  Plan pl;
+  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, false, &pl);
+  if (rc != kOk) return rc;
+  const Schedule sc = make_schedule(*geometry, pl, int8 != 0, per_pixel_scales != 0);
+  schedule[0] = pl.total_tiles, schedule[1] = sc.full_tiles, schedule[2] = sc.total_tiles, schedule[3] = pl.ctas;
+  schedule[4] = pl.pair ? 1 : 0, schedule[5] = sc.resident_k, schedule[6] = sc.n_major, schedule[7] = acc_stages(pl.block_n);
+  return kOk;
+}
+
+extern "C" void fim_conv_tune(int block_n, int max_ctas, int flags) {
   g_forced_block_n = block_n;
   g_max_ctas = max_ctas;
-  g_debug_flags = debug_flags;
+  g_debug_flags = flags;
 }

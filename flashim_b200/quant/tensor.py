@@ -42,6 +42,18 @@ def scale_exponent_from_amax(amax: Tensor) -> Tensor:
     return exponent.clamp_(-127.0, 127.0).to(torch.int8)
 
 
+def calibrate_block32_exponent(value: Tensor) -> Tensor:
+    """Static per-32-channel exponents of an activation ``[..., C]``: the largest magnitude of each block of 32 channels
+    over every row (a trailing ragged block is zero-padded), through :func:`scale_exponent_from_amax`; int8 ``[Cp / 32]``
+    (the helper of flashim/quant/formats/mx.py:41-47, as the calibrator uses it, flashim/quant/calibration.py:122-128)."""
+    channels = value.shape[-1]
+    rows = value.reshape(-1, channels).float()
+    padded = padded_channels(channels)
+    if padded != channels:
+        rows = torch.nn.functional.pad(rows, (0, padded - channels))
+    return scale_exponent_from_amax(rows.abs().reshape(-1, padded // BLOCK, BLOCK).amax(dim=(0, 2)))
+
+
 def exponent_to_e8m0(exponent: Tensor) -> Tensor:
     """int8 exponents -> the biased bytes E8M0 stores (uint8, bias 127)."""
     return (exponent.to(torch.int16) + 127).to(torch.uint8)

@@ -36,6 +36,7 @@ extern "C" {
 #define FIM_ACT_NONE 0
 #define FIM_ACT_RELU 1
 #define FIM_ACT_GELU 2
+#define FIM_ACT_RELU_EARLY 3 /* conv epilogues: ReLU before the residual add (the order of flashim/ops/gemm.py:87-98) */
 
 /* What the conv epilogue writes. */
 #define FIM_OUT_BF16 0         /* bf16 [B,Ho,Wo,Cout] */
@@ -145,10 +146,6 @@ int fim_dw5x5_mxfp8(const void* value, const void* weight, const float* bias, vo
 int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias, const float* scale, void* out, int batch,
                         int height, int width, int channels, int* status, void* stream);
 
-/* Measurement hook for the following depthwise launches of this process (0 = off); results are invalid when set:
- * 1: skip the FMAs, 2: skip the epilogue, 4: skip the loads and the waits for them. */
-void fim_dw_tune(int debug_flags);
-
 /* ---- implicit-GEMM conv2d on tcgen05 tensor cores ----------------------------------------------------------- */
 
 typedef struct FimConvGeometry {
@@ -161,7 +158,7 @@ typedef struct FimConvEpilogue {
   const void* residual;      /* bf16, addressed with the four element strides below, or NULL */
   long long res_stride[4];   /* batch, row, column, channel */
   int res_channels;          /* channels present in `residual` (<= cout) */
-  int act;                   /* FIM_ACT_* */
+  int act;                   /* FIM_ACT_*: GELU is applied before the residual add, ReLU after it */
   int out_mode;              /* FIM_OUT_* */
   const int8_t* out_exponent;/* FIM_OUT_E4M3_STATIC: int8 [cout/32] */
   void* out_scales;          /* FIM_OUT_E4M3_DYNAMIC: E8M0 bytes, swizzled 128x4 layout over rows = B*Ho*Wo */
@@ -172,7 +169,8 @@ typedef struct FimConvEpilogue {
  * pixel and tap) or per pixel (`act_scales_swizzled`: E8M0 bytes in the 128x4 swizzled layout over rows = B*H*W; 1x1
  * stride-1 unpadded convs only); weight E4M3 [cout, kh*kw*cin]; `weight_scales_swizzled`: E8M0 bytes of the
  * [cout, kh*kw*cin/32] exponents in the 128x4 swizzled layout. fp32 accumulation in tensor memory, epilogue
- * bias -> bf16 -> act -> residual -> requantisation as `epilogue` selects.
+ * bias -> bf16 rounding -> GELU -> residual add (one more bf16 rounding) -> ReLU -> requantisation, as `epilogue` selects:
+ * GELU acts before the residual is added, ReLU after it (relu(out + residual), flashim/ops/conv.py:198-203).
  * Replaces ops.mxfp8_conv2d (flashim/ops/conv.py:309-342; kernel flashim/backends/triton/conv.py:1122-1192) and, with
  * per-pixel scales, ops.mxfp8_scaled_mm (flashim/ops/gemm.py:40-52). */
 int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const void* act_scales_swizzled, const void* weight,
@@ -189,13 +187,11 @@ int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, con
  * {tile_rows, tile_cols, block_n, block_k, stages, ctas}. Returns 0 or FIM_ERR_UNSUPPORTED. */
 int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]);
 
-/* Tuning and measurement hooks for the following conv launches of this process (all 0 = automatic / off):
- * `block_n` forces the output-channel tile (64 / 128 / 256); `max_ctas` caps the persistent grid; `debug_flags` is for
- * timing experiments: bits 1, 2, 4, 8 make results invalid (skip activation loads / weight loads / stores / scale copies);
- * 16 keeps the last partial round of tiles at full width, 32 makes the epilogue warps poll without back-off, 64 disables
- * CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; default for INT8 with 256-wide tiles), 128
- * enables them for MXFP8 too. Results stay valid under 16-128. */
-void fim_conv_tune(int block_n, int max_ctas, int debug_flags);
+/* The work list of the persistent CTAs for a geometry (for reports and tests): writes {tiles, full_width_tiles,
+ * tiles_after_the_tail_split, ctas, cta_pairs (0 / 1), resident_k_iterations, channel_tile_major_order (0 / 1),
+ * accumulator_buffers}. The last partial round of tiles runs as half-width tiles when at most half of the CTAs would
+ * otherwise have work in it: then tiles_after_the_tail_split > tiles. Returns 0 or FIM_ERR_UNSUPPORTED. */
+int fim_conv_schedule(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int schedule[8]);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,29 @@
+/* Schedule overrides of libflashim_sm100.so for tests and measurements. Not part of the product ABI: nothing here is
+ * needed to use the library, and a caller that never touches these gets the automatic choices. The settings are
+ * process-wide and not synchronised: set them from the thread that launches.
+ *
+ * No counterpart in the FlashIM reference (its kernels take their tile sizes from Triton autotune configs). */
+#ifndef FLASHIM_SM100_TUNE_H_
+#define FLASHIM_SM100_TUNE_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Overrides for the following conv launches of this process (all 0 = automatic): `block_n` forces the output-channel
+ * tile (64 / 128 / 256); `max_ctas` caps the persistent grid, so that a small problem makes every CTA walk many tiles;
+ * `flags` selects between schedules that all produce the same bits: 16 keeps the last partial round of tiles at full
+ * width, 64 disables CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; default for INT8 with
+ * 256-wide tiles), 128 enables them for MXFP8 too, 256 reloads the weight scales for every tile instead of keeping the
+ * first K iterations resident in tensor memory. A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
+ * bits 1, 2, 4, 8 (skip activation loads / weight loads / stores / scale copies), which make results invalid. */
+void fim_conv_tune(int block_n, int max_ctas, int flags);
+
+/* Depthwise launches: `variant` selects the thread layout (0 = automatic). A probe build also honours, in `probe_flags`,
+ * 1: skip the FMAs, 2: skip the epilogue, 4: skip the loads and the waits for them (results invalid). */
+void fim_dw_tune(int variant, int probe_flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHIM_SM100_TUNE_H_ */

@@ -40,3 +40,36 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
 
 def code_mismatch(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a.cpu().contiguous().view(torch.uint8) != b.cpu().contiguous().view(torch.uint8)).float().mean())
+
+
+class conv_schedule:
+    """Context manager around the schedule overrides of ``include/flashim_sm100_tune.h``: force the output-channel tile,
+    cap the persistent grid (so a small problem makes every CTA walk many tiles) and pick between schedules that must
+    all give the same bits."""
+
+    def __init__(self, block_n: int = 0, max_ctas: int = 0, flags: int = 0) -> None:
+        self.args = (block_n, max_ctas, flags)
+
+    def __enter__(self):
+        from flashim_b200 import _native
+
+        self.lib = _native.library()
+        self.lib.fim_conv_tune(*self.args)
+        return self
+
+    def __exit__(self, *exc):
+        self.lib.fim_conv_tune(0, 0, 0)
+
+    def schedule(self, geometry, int8: bool = False, per_pixel: bool = False) -> dict:
+        """``fim_conv_schedule`` for (batch, height, width, cin, cout, kh, kw, pad, dilation) under the current overrides."""
+        import ctypes
+
+        from flashim_b200 import _native
+
+        b, h, w, cin, cout, kh, kw, pad, dil = geometry
+        g = _native.ConvGeometry(b, h, w, cin, cout, kh, kw, 1, 1, pad, pad, dil, dil)
+        out = (ctypes.c_int * 8)()
+        code = self.lib.fim_conv_schedule(ctypes.byref(g), int(int8), int(per_pixel), ctypes.byref(out))
+        assert code == 0, code
+        keys = ("tiles", "full_tiles", "split_tiles", "ctas", "pairs", "resident_k", "n_major", "accumulators")
+        return dict(zip(keys, list(out)))

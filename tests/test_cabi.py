@@ -11,10 +11,11 @@ from flashim_b200 import _native
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = (ROOT / "include" / "flashim_sm100.h").read_text()
+TUNE_HEADER = (ROOT / "include" / "flashim_sm100_tune.h").read_text()
 
 
-def _declared() -> list[str]:
-    return sorted(set(re.findall(r"^\s*(?:int|void)\s+(fim_\w+)\s*\(", HEADER, flags=re.M)))
+def _declared(text: str = HEADER) -> list[str]:
+    return sorted(set(re.findall(r"^\s*(?:int|void)\s+(fim_\w+)\s*\(", text, flags=re.M)))
 
 
 def test_library_is_built_and_exports_the_header():
@@ -24,13 +25,16 @@ def test_library_is_built_and_exports_the_header():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/flashim_sm100.h but not exported"
     assert sorted(_native.SIGNATURES) == names  # the ctypes table covers exactly the header
+    tune = _declared(TUNE_HEADER)
+    assert sorted(_native.TUNE_SIGNATURES) == tune and all(hasattr(lib, name) for name in tune)
+    assert not set(tune) & set(names)  # the schedule overrides are not part of the product header
     assert lib.fim_abi_version() == int(re.search(r"#define FIM_ABI_VERSION (\d+)", HEADER).group(1))
 
 
 def test_header_cites_the_reference_interface_of_every_entry_point():
     blocks = re.split(r"\n(?=/\*)", HEADER)
     for name in _declared():
-        if name in ("fim_abi_version", "fim_conv_plan", "fim_conv_tune", "fim_dw_tune"):
+        if name in ("fim_abi_version", "fim_conv_plan", "fim_conv_schedule"):
             continue
         block = next(b for b in blocks if re.search(rf"\b{name}\s*\(", b))
         assert "flashim/" in block, f"{name}: the comment must cite the reference interface it replaces"

@@ -346,3 +346,52 @@ def test_mxfp8_scaled_mm_and_int8_linear_golden(ops, golden):
     # what the kernel does not cover is declined, not approximated
     a8, w8, s, ws, b = to_dev(g("li0_a"), g("li0_w"), torch.tensor(0.02), g("li0_ws"), g("li0_b", BF16))
     assert ops.int8_linear.explain(a8, w8, s, ws, b, gelu=True)["sm100"] != "selected"
+
+
+# -- GELU in the epilogue ------------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("scale", [0.02, 0.3, 2.0, 40.0])
+def test_epilogue_gelu_is_torch_gelu_of_the_rounded_sum(ops, scale):
+    """The epilogue looks GELU up in a table of torch's own erf-form results for every bf16 value. Against the kernel's
+    plain bf16 output the GELU output must therefore be torch's, bit for bit, whatever the magnitude of the sums (tiny
+    values halve, large positive ones pass, large negative ones vanish); against the oracle it stays within one bf16 ulp
+    wherever the two pre-activation roundings agree."""
+    from flashim_b200.quant import swizzle_scales
+
+    x, ce, wq, we, bias = _mx_operands(2, 21, 23, 128, 256, 3, 3, seed=12)
+    bias = (bias.float() * scale).to(BF16)
+    we = (we.int() + int(torch.tensor(scale).log2().round())).clamp(-100, 100).to(torch.int8)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    fast = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(x, ce, wq, swizzle_scales(we), bias)
+    plain = fast(*xd, *geometry, act="none").cpu()
+    got = fast(*xd, *geometry, act="gelu").cpu()
+    assert same_bytes(got, F.gelu(plain.float()).to(BF16))
+    want_plain = oracle.mxfp8_conv2d_ext(x, ce, wq, we, bias, *geometry)
+    want = oracle.mxfp8_conv2d_ext(x, ce, wq, we, bias, *geometry, act="gelu")
+    agree = bf16_ulp_distance(plain, want_plain) == 0
+    assert float(agree.float().mean()) > 0.9
+    assert same_bytes(got[agree], want[agree])
+    assert rel_l2(got, want) < 1e-3
+
+
+def test_int8_epilogue_gelu_and_early_relu(ops):
+    """INT8 conv with the GELU epilogue (the order of flashim/ops/gemm.py:87-98: scales + bias -> bf16 -> GELU ->
+    residual): bit-equal to torch's GELU of the kernel's exact plain output plus the residual."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randint(-127, 128, (2, 17, 19, 64), dtype=torch.int8, generator=g)
+    w = torch.randint(-127, 128, (96, 9 * 64), dtype=torch.int8, generator=g)
+    a_scale, w_scale = torch.tensor(0.004), torch.rand(96, generator=g) * 0.002 + 0.0002
+    bias = torch.randn(96, generator=g).to(BF16)
+    res = torch.randn(2, 17, 19, 96, generator=g).to(BF16)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    plain = oracle.int8_conv2d(x, w, a_scale, w_scale, bias, *geometry)
+    from flashim_b200.backends.sm100.kernels import int8_conv2d_launch
+    from flashim_b200 import _native
+
+    xd, wd, sd, wsd, bd, rd = to_dev(x, w, a_scale.reshape(1), w_scale, bias, res)
+    got = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, _native.ACT["gelu"], _native.OUT_BF16)
+    assert same_bytes(got.cpu(), res + F.gelu(plain.float()).to(BF16))
+    early = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, _native.ACT["relu_early"], _native.OUT_BF16)
+    assert same_bytes(early.cpu(), res + F.relu(plain))

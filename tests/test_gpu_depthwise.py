@@ -125,3 +125,43 @@ def test_layout_handling(ops):
     _assert_bf16_close(got, want)
     assert "sm100" in ops.depthwise5x5_act.explain(*to_dev(x, w, b), "relu")
     assert ops.depthwise5x5_act.explain(*to_dev(x, w, b), "relu")["sm100"] == "selected"
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
+def test_every_thread_layout_gives_the_same_results(ops, variant):
+    """The kernel is compiled for several thread layouts (columns per lane x warps per CTA); the launcher picks one by
+    image width. Each is forced in turn: dense outputs must be the bits of the automatic choice (the FMA order per
+    element is the same), quantised outputs too."""
+    from flashim_b200 import _native
+
+    lib = _native.library()
+    x, w, b = _inputs(2, 192, 37, 45, seed=7, wscale=0.2)
+    xd, wd, bd = to_dev(x, w, b)
+    scale = to_dev(torch.tensor(0.03))
+    want = {
+        "gelu": ops.depthwise5x5_act.get("sm100")(xd, wd, bd, "gelu"),
+        "mx": ops.depthwise5x5_act_mxfp8.get("sm100")(xd, wd, bd, "gelu"),
+        "relu_mx": ops.depthwise5x5_relu_mxfp8.get("sm100")(xd, wd, bd),
+        "int8": ops.depthwise5x5_relu_int8.get("sm100")(xd, wd, bd, scale),
+    }
+    _assert_bf16_close(want["gelu"], oracle.depthwise5x5_act_ext(x, w, b, "gelu"), oracle.depthwise5x5_fp32(x, w, b).permute(0, 2, 3, 1))
+    try:
+        lib.fim_dw_tune(variant, 0)
+        assert same_bytes(ops.depthwise5x5_act.get("sm100")(xd, wd, bd, "gelu"), want["gelu"])
+        q, s = ops.depthwise5x5_act_mxfp8.get("sm100")(xd, wd, bd, "gelu")
+        assert same_bytes(q, want["mx"][0]) and same_bytes(s, want["mx"][1])
+        q, s = ops.depthwise5x5_relu_mxfp8.get("sm100")(xd, wd, bd)
+        assert same_bytes(q, want["relu_mx"][0]) and same_bytes(s.view(torch.uint8), want["relu_mx"][1].view(torch.uint8))
+        assert same_bytes(ops.depthwise5x5_relu_int8.get("sm100")(xd, wd, bd, scale), want["int8"])
+    finally:
+        lib.fim_dw_tune(0, 0)
+
+
+def test_gelu_mxfp8_against_the_oracle(ops):
+    """Depthwise + GELU quantised straight from fp32: E8M0 bytes equal the oracle's but for block maxima within rounding of
+    a 448 * 2**k edge, and fewer than one code in a thousand differs."""
+    x, w, b = _inputs(2, 128, 40, 52, seed=4, wscale=0.2)
+    q, s = ops.depthwise5x5_act_mxfp8.get("sm100")(*to_dev(x, w, b), "gelu")
+    q_ref, e_ref = oracle.depthwise5x5_act_mxfp8_ext(x, w, b, "gelu")
+    assert float((s.cpu() != oracle.swizzle_32_4_4(e_ref)).float().mean()) < 1e-4
+    assert code_mismatch(q, q_ref) < 1e-3
