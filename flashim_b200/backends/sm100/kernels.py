@@ -147,6 +147,7 @@ def _(pixels, weight, bias, scale):
 
 @torch.library.custom_op("flashim_b200::quantize_mxfp8_static", mutates_args=())
 def quantize_mxfp8_static(value: Tensor, exponent: Tensor) -> Tensor:
+    value = _aligned(value)
     channels = value.shape[-1]
     rows = value.numel() // channels
     out = torch.empty((*value.shape[:-1], padded_channels(channels)), device=value.device, dtype=E4M3)
@@ -163,6 +164,7 @@ def _(value, exponent):
 
 @torch.library.custom_op("flashim_b200::quantize_mxfp8_dynamic", mutates_args=())
 def quantize_mxfp8_dynamic(value: Tensor, swizzled: bool) -> tuple[Tensor, Tensor]:
+    value = _aligned(value)
     channels = value.shape[-1]
     rows = value.numel() // channels
     out = torch.empty(value.shape, device=value.device, dtype=E4M3)
@@ -188,6 +190,7 @@ def _(value, swizzled):
 
 @torch.library.custom_op("flashim_b200::quantize_int8_static", mutates_args=())
 def quantize_int8_static(value: Tensor, scale: Tensor) -> Tensor:
+    value = _aligned(value)
     out = torch.empty(value.shape, device=value.device, dtype=torch.int8)
     code = _native.library().fim_quantize_int8_static(
         value.data_ptr(), _IN_DTYPES[value.dtype], scale.data_ptr(), out.data_ptr(), value.numel(), _stream(value))
@@ -306,13 +309,21 @@ _OUT_DTYPES = {
 }
 
 
-def _out_size(size: int, k: int, p: int, d: int) -> int:
-    return size + 2 * p - d * (k - 1)
+def _out_size(size: int, k: int, p: int, d: int, s: int = 1) -> int:
+    return (size + 2 * p - d * (k - 1) - 1) // s + 1
 
 
-def _geometry(x: Tensor, cout: int, kh, kw, ph, pw, dh, dw) -> _native.ConvGeometry:
+def _geometry(x: Tensor, cout: int, kh, kw, sh, sw, ph, pw, dh, dw) -> _native.ConvGeometry:
     b, h, w, cin = x.shape
-    return _native.ConvGeometry(b, h, w, cin, cout, kh, kw, 1, 1, ph, pw, dh, dw)
+    return _native.ConvGeometry(b, h, w, cin, cout, kh, kw, sh, sw, ph, pw, dh, dw)
+
+
+def _aligned(t: Tensor | None) -> Tensor | None:
+    """``t`` itself when its storage starts on a 16-byte boundary (what TMA and the 128-bit loads need), else a copy:
+    alignment is fixed up here, in the wrapper, not tested in ``when`` (flashim/backends/cuda/conv.py:59-60 does the same)."""
+    if t is None or t.data_ptr() % 16 == 0:
+        return t
+    return t.clone()
 
 
 def _epilogue(bias, residual, act: int, out_mode: int, out_exponent=None, out_scales=None, out_scale=None):
@@ -332,30 +343,31 @@ def _epilogue(bias, residual, act: int, out_mode: int, out_exponent=None, out_sc
 def mxfp8_conv2d_launch(
     x: Tensor, act_exponent: Tensor | None, act_scales: Tensor | None, weight: Tensor, weight_scales: Tensor,
     bias: Tensor | None, residual: Tensor | None, out_exponent: Tensor | None,
-    kh: int, kw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
+    kh: int, kw: int, sh: int, sw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
 ) -> tuple[Tensor, Tensor]:
+    x, weight, weight_scales, bias, act_scales = (_aligned(t) for t in (x, weight, weight_scales, bias, act_scales))
     b, h, w, _ = x.shape
     cout = weight.shape[0]
-    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
     out = torch.empty((b, ho, wo, cout), device=x.device, dtype=_OUT_DTYPES[out_mode])
     if out_mode == _native.OUT_E4M3_DYNAMIC:
         out_scales = _swizzled_scale_buffer(b * ho * wo, cout // BLOCK, x.device)
     else:
         out_scales = torch.empty(0, device=x.device, dtype=torch.uint8)
-    geometry = _geometry(x, cout, kh, kw, ph, pw, dh, dw)
+    geometry = _geometry(x, cout, kh, kw, sh, sw, ph, pw, dh, dw)
     epilogue = _epilogue(bias, residual, act, out_mode, out_exponent, out_scales if out_scales.numel() else None)
     code = _native.library().fim_mxfp8_conv2d(
         x.data_ptr(), _ptr(act_exponent), _ptr(act_scales), weight.data_ptr(), weight_scales.data_ptr(),
         ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
-    _finish(code, f"mxfp8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw}", x.device)
+    _finish(code, f"mxfp8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw} s{sh}x{sw}", x.device)
     return out, out_scales
 
 
 @mxfp8_conv2d_launch.register_fake
-def _(x, act_exponent, act_scales, weight, weight_scales, bias, residual, out_exponent, kh, kw, ph, pw, dh, dw, act, out_mode):
+def _(x, act_exponent, act_scales, weight, weight_scales, bias, residual, out_exponent, kh, kw, sh, sw, ph, pw, dh, dw, act, out_mode):
     b, h, w, _ = x.shape
     cout = weight.shape[0]
-    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
     n = swizzled_scale_bytes(b * ho * wo, cout // BLOCK) if out_mode == _native.OUT_E4M3_DYNAMIC else 0
     return x.new_empty((b, ho, wo, cout), dtype=_OUT_DTYPES[out_mode]), x.new_empty((n,), dtype=torch.uint8)
 
@@ -363,26 +375,68 @@ def _(x, act_exponent, act_scales, weight, weight_scales, bias, residual, out_ex
 @torch.library.custom_op("flashim_b200::int8_conv2d", mutates_args=())
 def int8_conv2d_launch(
     x: Tensor, weight: Tensor, a_scale: Tensor | None, w_scale: Tensor | None, bias: Tensor | None, residual: Tensor | None,
-    out_scale: Tensor | None, kh: int, kw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
+    out_scale: Tensor | None, kh: int, kw: int, sh: int, sw: int, ph: int, pw: int, dh: int, dw: int, act: int, out_mode: int,
 ) -> Tensor:
+    x, weight, w_scale, bias = (_aligned(t) for t in (x, weight, w_scale, bias))
     b, h, w, _ = x.shape
     cout = weight.shape[0]
-    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
     out = torch.empty((b, ho, wo, cout), device=x.device, dtype=_OUT_DTYPES[out_mode])
-    geometry = _geometry(x, cout, kh, kw, ph, pw, dh, dw)
+    geometry = _geometry(x, cout, kh, kw, sh, sw, ph, pw, dh, dw)
     epilogue = _epilogue(bias, residual, act, out_mode, out_scale=out_scale)
     code = _native.library().fim_int8_conv2d(
         x.data_ptr(), weight.data_ptr(), _ptr(a_scale), _ptr(w_scale), ctypes.byref(geometry), ctypes.byref(epilogue),
         out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
-    _finish(code, f"int8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw}", x.device)
+    _finish(code, f"int8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw} s{sh}x{sw}", x.device)
     return out
 
 
 @int8_conv2d_launch.register_fake
-def _(x, weight, a_scale, w_scale, bias, residual, out_scale, kh, kw, ph, pw, dh, dw, act, out_mode):
+def _(x, weight, a_scale, w_scale, bias, residual, out_scale, kh, kw, sh, sw, ph, pw, dh, dw, act, out_mode):
     b, h, w, _ = x.shape
-    ho, wo = _out_size(h, kh, ph, dh), _out_size(w, kw, pw, dw)
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
     return x.new_empty((b, ho, wo, weight.shape[0]), dtype=_OUT_DTYPES[out_mode])
+
+
+@torch.library.custom_op("flashim_b200::bf16_conv2d", mutates_args=())
+def bf16_conv2d_launch(x: Tensor, weight: Tensor, bias: Tensor | None, residual: Tensor | None, kh: int, kw: int, sh: int, sw: int,
+                       ph: int, pw: int, dh: int, dw: int, act: int) -> Tensor:
+    """bf16 NHWC ``x`` and bf16 ``weight [Cout, kh*kw*Cin]`` -> bf16 NHWC (fp32 accumulation on the tensor cores)."""
+    x, weight, bias = (_aligned(t) for t in (x, weight, bias))
+    b, h, w, _ = x.shape
+    cout = weight.shape[0]
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
+    out = torch.empty((b, ho, wo, cout), device=x.device, dtype=torch.bfloat16)
+    geometry = _geometry(x, cout, kh, kw, sh, sw, ph, pw, dh, dw)
+    epilogue = _epilogue(bias, residual, act, _native.OUT_BF16)
+    code = _native.library().fim_bf16_conv2d(
+        x.data_ptr(), weight.data_ptr(), ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(),
+        status_word(x.device).data_ptr(), _stream(x))
+    _finish(code, f"bf16_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw}", x.device)
+    return out
+
+
+@bf16_conv2d_launch.register_fake
+def _(x, weight, bias, residual, kh, kw, sh, sw, ph, pw, dh, dw, act):
+    b, h, w, _ = x.shape
+    return x.new_empty((b, _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw), weight.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("flashim_b200::gelu_quantize_mxfp8", mutates_args=())
+def gelu_quantize_launch(value: Tensor, input_bias: Tensor | None, exponent: Tensor) -> Tensor:
+    """bf16 ``[..., C]`` (C % 32 == 0) -> E4M3: erf GELU of ``value + input_bias`` in fp32, bf16 rounding, static quantiser."""
+    value = _aligned(value)
+    channels = value.shape[-1]
+    out = torch.empty(value.shape, device=value.device, dtype=E4M3)
+    code = _native.library().fim_gelu_quantize_mxfp8(
+        value.data_ptr(), _ptr(input_bias), exponent.data_ptr(), out.data_ptr(), value.numel() // channels, channels, _stream(value))
+    _finish(code, f"gelu_quantize_mxfp8 {tuple(value.shape)}", value.device)
+    return out
+
+
+@gelu_quantize_launch.register_fake
+def _(value, input_bias, exponent):
+    return value.new_empty(value.shape, dtype=E4M3)
 
 
 # ---- weight-scale layout cache (ops whose signature carries plain int8 exponents) ----------------------------------------
@@ -413,7 +467,7 @@ def _cuda(*tensors) -> bool:
 
 
 def _conv_geometry_ok(x, cout, k_total, kh, kw, sh, sw, ph, pw, dh, dw) -> bool:
-    if x.ndim != 4 or not x.is_contiguous() or (sh, sw) != (1, 1):
+    if x.ndim != 4 or not x.is_contiguous() or not (1 <= sh <= 4 and 1 <= sw <= 4):
         return False
     cin = x.shape[-1]
     return cin % 32 == 0 and cout % 32 == 0 and k_total == kh * kw * cin and min(kh, kw, dh, dw) >= 1 and min(ph, pw) >= 0
@@ -470,7 +524,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         exponent = None if out_exponent is None else out_exponent.to(device=x.device, dtype=torch.int8).contiguous()
         out, _ = mxfp8_conv2d_launch(
             x, channel_exponent.contiguous(), None, weight, swizzled_weight_scales(weight_exponent),
-            None if bias is None else bias.contiguous(), residual, exponent, kh, kw, ph, pw, dh, dw,
+            None if bias is None else bias.contiguous(), residual, exponent, kh, kw, sh, sw, ph, pw, dh, dw,
             act_code["relu" if relu else "none"], mode)
         return out
 
@@ -482,7 +536,9 @@ def register(ops=None, device_spec=None, feature=None) -> None:
             and x.dtype == E4M3 and weight.dtype == E4M3 and weight.is_contiguous() and weight_scales.dtype == torch.uint8
             and _conv_geometry_ok(x, weight.shape[0], weight.shape[1], kh, kw, sh, sw, ph, pw, dh, dw)
             and act in act_code and _residual_ok(residual, weight.shape[0])
-            and (not per_pixel or (kh, kw, ph, pw) == (1, 1, 0, 0))
+            and (not per_pixel or ((kh, kw, sh, sw, ph, pw) == (1, 1, 1, 1, 0, 0) and act_scale.numel() == swizzled_scale_bytes(
+                x.numel() // x.shape[-1], x.shape[-1] // BLOCK)))
+            and weight_scales.numel() == swizzled_scale_bytes(weight.shape[0], weight.shape[1] // BLOCK)
             and (per_pixel or (act_scale.dtype == torch.int8 and tuple(act_scale.shape) == (x.shape[-1] // 32,)))
             and (out_exponent is None) + (not dynamic_out) + (not out_fp32) >= 2
         )
@@ -500,7 +556,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
                 mode = _native.OUT_BF16 if out_exponent is None else _native.OUT_E4M3_STATIC
             out, scales = mxfp8_conv2d_launch(
                 x, None if per_pixel else act_scale, act_scale if per_pixel else None, weight, weight_scales, bias, residual,
-                out_exponent, kh, kw, ph, pw, dh, dw, act_code[act], mode)
+                out_exponent, kh, kw, sh, sw, ph, pw, dh, dw, act_code[act], mode)
             return (out, scales) if dynamic_out else out
 
     def int8_when(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, residual=None,
@@ -520,7 +576,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         scale = None if out_scale is None else out_scale.to(device=x.device, dtype=torch.float32).reshape(1)
         return int8_conv2d_launch(
             x, weight, a_scale.float().reshape(1), w_scale.float().contiguous(), None if bias is None else bias.contiguous(),
-            residual, scale, kh, kw, ph, pw, dh, dw, act_code["relu" if relu else "none"],
+            residual, scale, kh, kw, sh, sw, ph, pw, dh, dw, act_code["relu" if relu else "none"],
             _native.OUT_BF16 if out_scale is None else _native.OUT_INT8)
 
     if hasattr(ops, "int8_conv2d_maxpool"):
@@ -544,7 +600,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
 
         @ops.int8_conv2d_accumulators.register("sm100", device=spec, requires=requires, priority=3, when=acc_when)
         def int8_conv2d_accumulators(x, weight, kh, kw, sh, sw, ph, pw, dh, dw):
-            return int8_conv2d_launch(x, weight, None, None, None, None, None, kh, kw, ph, pw, dh, dw, 0, _native.OUT_INT32)
+            return int8_conv2d_launch(x, weight, None, None, None, None, None, kh, kw, sh, sw, ph, pw, dh, dw, 0, _native.OUT_INT32)
 
     # -- GEMMs: a 1x1 conv over a one-row image of M pixels -------------------------------------------------------------
     if hasattr(ops, "mxfp8_scaled_mm"):
@@ -564,7 +620,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
             m, k = a.shape
             out, _ = mxfp8_conv2d_launch(
                 a.view(1, 1, m, k), None, a_scale.view(torch.uint8).reshape(-1), b_t.t(), b_scale.view(torch.uint8).reshape(-1),
-                None if bias is None else bias.contiguous(), None, None, 1, 1, 0, 0, 1, 1, act_code["none"], _native.OUT_BF16)
+                None if bias is None else bias.contiguous(), None, None, 1, 1, 1, 1, 0, 0, 1, 1, act_code["none"], _native.OUT_BF16)
             return out.view(m, -1)
 
     if hasattr(ops, "int8_linear"):
@@ -573,21 +629,102 @@ def register(ops=None, device_spec=None, feature=None) -> None:
                 have() and _cuda(a, weight, a_scale, w_scale, bias, residual) and a.dim() == 2 and weight.dim() == 2
                 and a.dtype == torch.int8 and weight.dtype == torch.int8 and a.is_contiguous() and weight.is_contiguous()
                 and a.shape[1] == weight.shape[1] and a.shape[1] % 32 == 0 and weight.shape[0] % 32 == 0 and a.shape[0] > 0
-                and a_scale.numel() == 1 and w_scale.numel() == weight.shape[0] and not gelu
+                and a_scale.numel() == 1 and w_scale.numel() == weight.shape[0]
+                and not (relu and gelu)  # ReLU then GELU: not an epilogue the kernel has
                 and (bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == weight.shape[0]))
-                # the conv epilogue applies ReLU after the residual, the linear before it: both at once are not covered
-                and (residual is None or (not relu and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+                and (residual is None or (residual.dtype == torch.bfloat16 and residual.is_contiguous()
                                           and tuple(residual.shape) == (a.shape[0], weight.shape[0])))
             )
 
         @ops.int8_linear.register("sm100", device=spec, requires=requires, priority=3, when=int8_linear_when)
         def int8_linear(a, weight, a_scale, w_scale, bias, *, relu=False, gelu=False, residual=None):
+            # the linear's order is ReLU -> bf16 -> GELU -> residual (flashim/ops/gemm.py:87-98): its ReLU comes before the
+            # residual, the conv's after it, hence the epilogue's own activation code
             m, k = a.shape
+            act = "gelu" if gelu else ("relu_early" if relu else "none")
             out = int8_conv2d_launch(
                 a.view(1, 1, m, k), weight, a_scale.float().reshape(1), w_scale.float().contiguous(),
                 None if bias is None else bias.contiguous(), None if residual is None else residual.view(1, 1, m, -1), None,
-                1, 1, 0, 0, 1, 1, act_code["relu" if relu else "none"], _native.OUT_BF16)
+                1, 1, 1, 1, 0, 0, 1, 1, act_code[act], _native.OUT_BF16)
             return out.view(m, -1)
+
+    # -- static MXFP8 linear, GELU -> quantise, the GELU MLP (flashim/ops/gemm.py:58-72,146-157, ops/quantize.py:62-74) ------
+    def _linear(values, scale_exponent, bias, weight_values, weight_exponent):
+        rows, k = values.shape
+        out, _ = mxfp8_conv2d_launch(
+            values.view(1, 1, rows, k), scale_exponent.contiguous(), None, weight_values, swizzled_weight_scales(weight_exponent),
+            None if bias is None else bias.to(torch.bfloat16).contiguous(), None, None, 1, 1, 1, 1, 0, 0, 1, 1,
+            act_code["none"], _native.OUT_BF16)
+        return out.view(rows, -1)
+
+    def _linear_operands_ok(values, exponent, w, we) -> bool:
+        return (
+            have() and all(isinstance(t, Tensor) for t in (values, exponent, w, we)) and _cuda(values, exponent, w, we)
+            and values.dtype == E4M3 and w.dtype == E4M3 and values.is_contiguous() and w.is_contiguous()
+            and values.shape[-1] == w.shape[1] and w.shape[1] % 32 == 0 and w.shape[0] % 32 == 0 and values.numel() > 0
+            and exponent.dtype == torch.int8 and tuple(exponent.shape) == (w.shape[1] // 32,)
+            and we.dtype == torch.int8 and tuple(we.shape) == (w.shape[0], w.shape[1] // 32)
+        )
+
+    def _quantized_ok(activation, weight) -> bool:
+        return _linear_operands_ok(getattr(activation, "values", None), getattr(activation, "scale_exponent", None),
+                                   getattr(weight, "values", None), getattr(weight, "scale_exponent", None))
+
+    def _bias_exact_in_bf16(bias, n) -> bool:
+        """The epilogue adds a bf16 bias (widened to fp32); a bias of another dtype is taken only if bf16 holds it exactly."""
+        if bias is None:
+            return True
+        if not (isinstance(bias, Tensor) and bias.is_cuda and bias.numel() == n):
+            return False
+        return bias.dtype == torch.bfloat16 or bool((bias.to(torch.bfloat16).to(bias.dtype) == bias).all())
+
+    if hasattr(ops, "mxfp8_linear"):
+        def linear_when(activation, bias, weight):
+            return _quantized_ok(activation, weight) and _bias_exact_in_bf16(bias, weight.values.shape[0])
+
+        @ops.mxfp8_linear.register("sm100", device=spec, requires=requires, priority=3, when=linear_when)
+        def mxfp8_linear(activation, bias, weight):
+            values = activation.values.reshape(-1, activation.values.shape[-1])
+            return _linear(values, activation.scale_exponent, bias, weight.values, weight.scale_exponent)
+
+    if hasattr(ops, "gelu_quantize"):
+        def gelu_quantize_when(value, scale_exponent, approximate="none", *, input_bias=None):
+            return (
+                have() and approximate == "none" and _cuda(value, scale_exponent, input_bias) and value.dtype == torch.bfloat16
+                and value.is_contiguous() and value.ndim >= 2 and value.shape[-1] % 32 == 0 and value.numel() > 0
+                and tuple(scale_exponent.shape) == (value.shape[-1] // 32,)
+                and (input_bias is None or input_bias.numel() == value.shape[-1])
+            )
+
+        @ops.gelu_quantize.register("sm100", device=spec, requires=dw_requires_early(feature), priority=3, when=gelu_quantize_when)
+        def gelu_quantize(value, scale_exponent, approximate="none", *, input_bias=None):
+            exponent = (scale_exponent if scale_exponent.dtype == torch.int8 else scale_exponent.to(torch.int8)).contiguous()
+            bias = None if input_bias is None else input_bias.float().contiguous()
+            qt = getattr(ops, "QuantizedTensor", None) or _quantized_tensor_type(ops)
+            return qt(gelu_quantize_launch(value, bias, exponent), exponent if scale_exponent.dtype != torch.int8 else scale_exponent,
+                      tuple(value.shape))
+
+    if hasattr(ops, "mxfp8_gelu_mlp"):
+        def mlp_when(x, w1, b1, hidden_exponent, w2):
+            if not (_quantized_ok(x, w1) and isinstance(hidden_exponent, Tensor) and isinstance(b1, Tensor)):
+                return False
+            hidden = w1.values.shape[0]
+            return (
+                hidden_exponent.is_cuda and tuple(hidden_exponent.shape) == (hidden // 32,) and b1.is_cuda and b1.numel() == hidden
+                and isinstance(getattr(w2, "values", None), Tensor) and w2.values.is_cuda and w2.values.dtype == E4M3
+                and w2.values.is_contiguous() and w2.values.shape[1] == hidden and w2.values.shape[0] % 32 == 0
+                and tuple(w2.scale_exponent.shape) == (w2.values.shape[0], hidden // 32) and w2.scale_exponent.dtype == torch.int8
+            )
+
+        @ops.mxfp8_gelu_mlp.register("sm100", device=spec, requires=requires, priority=3, when=mlp_when)
+        def mxfp8_gelu_mlp(x, w1, b1, hidden_exponent, w2):
+            # three launches with the reference's rounding points: the first product rounds to bf16 before b1 is added,
+            # GELU runs in fp32 on that sum, and the second product has no bias
+            values = x.values.reshape(-1, x.values.shape[-1])
+            hidden = _linear(values, x.scale_exponent, None, w1.values, w1.scale_exponent)
+            exponent = hidden_exponent.to(torch.int8).contiguous()
+            activated = gelu_quantize_launch(hidden, b1.float().contiguous(), exponent)
+            return _linear(activated, exponent, None, w2.values, w2.scale_exponent)
 
     # -- depthwise ---------------------------------------------------------------------------------------------------
     dw_requires = [feature.TMA] + ([feature.SM100A_KERNELS] if hasattr(feature, "SM100A_KERNELS") else [])
@@ -618,6 +755,70 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         @ops.depthwise5x5_act_mxfp8.register("sm100", device=spec, requires=dw_requires, priority=3, when=dw_act_when)
         def depthwise5x5_act_mxfp8(value, weight, bias, act="gelu"):
             return dw5x5_mxfp8(_nhwc(value), weight, bias, act_code[act], True)
+
+    # -- depthwise-separable blocks (flashim/ops/conv.py:67-138) ---------------------------------------------------------
+    if hasattr(ops, "depthwise5x5_relu_pointwise"):
+        def dwpw_when(value, dw_weight, dw_bias, pw_weight, pw_bias):
+            c = value.shape[1] if isinstance(value, Tensor) and value.ndim == 4 else 0
+            return (
+                have() and _cuda(value, dw_weight, dw_bias, pw_weight, pw_bias) and c % 32 == 0 and c > 0
+                and value.dtype in (torch.bfloat16, torch.float32, torch.float16)
+                and tuple(dw_weight.shape) == (25, c) and dw_weight.dtype == torch.bfloat16 and dw_weight.is_contiguous()
+                and tuple(dw_bias.shape) == (c,) and pw_weight.ndim == 2 and pw_weight.shape[1] == c
+                and pw_weight.shape[0] % 32 == 0 and pw_weight.dtype == torch.bfloat16 and pw_weight.is_contiguous()
+                and pw_bias.dtype == torch.bfloat16 and pw_bias.numel() == pw_weight.shape[0]
+            )
+
+        @ops.depthwise5x5_relu_pointwise.register("sm100", device=spec, requires=requires, priority=3, when=dwpw_when)
+        def depthwise5x5_relu_pointwise(value, dw_weight, dw_bias, pw_weight, pw_bias):
+            # two launches: the depthwise kernel writes its ReLU output once as bf16 (the rounding point of the reference),
+            # the pointwise product is a bf16 tensor-core GEMM over the pixels with the bias in its epilogue
+            hidden = dw5x5_bf16(_nhwc(value), dw_weight, dw_bias.float().contiguous(), act_code["relu"])
+            out = bf16_conv2d_launch(hidden, pw_weight, pw_bias.contiguous(), None, 1, 1, 1, 1, 0, 0, 1, 1, act_code["none"])
+            return out.permute(0, 3, 1, 2)
+
+    if hasattr(ops, "depthwise5x5_relu_pointwise_mxfp8"):
+        def dwpw_mx_when(value, dw_weight, dw_bias, pw_weight, pw_scale_swizzled, pw_scale_u8, pw_bias):
+            c = value.shape[1] if isinstance(value, Tensor) and value.ndim == 4 else 0
+            return (
+                dw_when(value, dw_weight, dw_bias) and _cuda(pw_weight, pw_scale_swizzled, pw_bias) and pw_weight.dtype == E4M3
+                and pw_weight.ndim == 2 and pw_weight.shape[1] == c and pw_weight.shape[0] % 32 == 0 and pw_weight.is_contiguous()
+                and pw_scale_swizzled.element_size() == 1
+                and pw_scale_swizzled.numel() == swizzled_scale_bytes(pw_weight.shape[0], c // BLOCK)
+                and (pw_bias is None or (pw_bias.dtype == torch.bfloat16 and pw_bias.numel() == pw_weight.shape[0]))
+            )
+
+        @ops.depthwise5x5_relu_pointwise_mxfp8.register("sm100", device=spec, requires=requires, priority=3, when=dwpw_mx_when)
+        def depthwise5x5_relu_pointwise_mxfp8(value, dw_weight, dw_bias, pw_weight, pw_scale_swizzled, pw_scale_u8, pw_bias):
+            # the producer's swizzled E8M0 tiles are what the GEMM's tensor-memory copies read: no re-layout in between
+            b, c, h, w = value.shape
+            q, scales = dw5x5_mxfp8(_nhwc(value), dw_weight, dw_bias, act_code["relu"], True)
+            out, _ = mxfp8_conv2d_launch(
+                q.view(1, 1, b * h * w, c), None, scales, pw_weight, pw_scale_swizzled.view(torch.uint8).reshape(-1),
+                None if pw_bias is None else pw_bias.contiguous(), None, None, 1, 1, 1, 1, 0, 0, 1, 1, act_code["none"],
+                _native.OUT_BF16)
+            return out.view(b, h, w, -1).permute(0, 3, 1, 2)
+
+    if hasattr(ops, "depthwise5x5_relu_pointwise_int8"):
+        def dwpw_i8_when(value, dw_weight, dw_bias, pw_weight, pw_wscale, pw_bias, scale):
+            c = value.shape[1] if isinstance(value, Tensor) and value.ndim == 4 else 0
+            return (
+                dw_when(value, dw_weight, dw_bias) and _cuda(pw_weight, pw_wscale, pw_bias, scale) and scale.numel() == 1
+                and pw_weight.dtype == torch.int8 and pw_weight.ndim == 2 and pw_weight.shape[1] == c
+                and pw_weight.shape[0] % 32 == 0 and pw_weight.is_contiguous() and pw_wscale.numel() == pw_weight.shape[0]
+                and (pw_bias is None or (pw_bias.dtype == torch.bfloat16 and pw_bias.numel() == pw_weight.shape[0]))
+            )
+
+        @ops.depthwise5x5_relu_pointwise_int8.register("sm100", device=spec, requires=requires, priority=3, when=dwpw_i8_when)
+        def depthwise5x5_relu_pointwise_int8(value, dw_weight, dw_bias, pw_weight, pw_wscale, pw_bias, scale):
+            b, c, h, w = value.shape
+            scale32 = scale.float().reshape(1)
+            q = dw5x5_relu_int8(_nhwc(value), dw_weight, dw_bias, scale32)
+            out = int8_conv2d_launch(
+                q.view(1, 1, b * h * w, c), pw_weight, scale32, pw_wscale.float().contiguous(),
+                None if pw_bias is None else pw_bias.contiguous(), None, None, 1, 1, 1, 1, 0, 0, 1, 1, act_code["none"],
+                _native.OUT_BF16)
+            return out.view(b, h, w, -1).permute(0, 3, 1, 2)
 
     if hasattr(ops, "romav2_refiner_input"):
         def input_when(f_a, f_b, warp, emb_weight, emb_bias, scale_factor, radius, pair=0):
@@ -660,7 +861,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
     def quantize_when(value, scale_exponent):
         return (
             have() and _cuda(value, scale_exponent) and value.ndim >= 2 and value.dtype in _IN_DTYPES
-            and ((value.is_contiguous() and value.data_ptr() % 16 == 0) or (_channels_first_view(value) and value.numel() > 0))
+            and (value.is_contiguous() or (_channels_first_view(value) and value.numel() > 0))
             and tuple(scale_exponent.shape) == (padded_channels(value.shape[-1]) // 32,)
         )
 
@@ -677,7 +878,7 @@ def register(ops=None, device_spec=None, feature=None) -> None:
         return qt(values, exponent, tuple(value.shape))
 
     def quantize_int8_when(value, scale, *, channel_scale=None):
-        row_major = value.is_contiguous() and value.data_ptr() % 16 == 0
+        row_major = value.is_contiguous()
         channels_first = _channels_first_view(value) and value.numel() > 0 and value.shape[-1] % 16 == 0
         return (have() and channel_scale is None and _cuda(value, scale) and value.dtype in _IN_DTYPES
                 and (row_major or channels_first) and scale.numel() == 1)
@@ -692,11 +893,16 @@ def register(ops=None, device_spec=None, feature=None) -> None:
     if hasattr(ops, "quantize_mxfp8_dynamic"):
         def dynamic_when(value):
             return (have() and _cuda(value) and value.dtype in _IN_DTYPES and value.is_contiguous()
-                    and value.shape[-1] % 32 == 0 and value.data_ptr() % 16 == 0)
+                    and value.shape[-1] % 32 == 0)
 
         @ops.quantize_mxfp8_dynamic.register("sm100", device=spec, requires=dw_requires, priority=3, when=dynamic_when)
         def quantize_mxfp8_dynamic_impl(value):
             return quantize_mxfp8_dynamic(value, True)
+
+
+def dw_requires_early(feature):
+    """Features of the kernels that use no tensor-core instruction."""
+    return [feature.TMA] + ([feature.SM100A_KERNELS] if hasattr(feature, "SM100A_KERNELS") else [])
 
 
 def _quantized_tensor_type(ops):

@@ -133,6 +133,26 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, vo
   if (mbar_try_addr(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, code, heed_abort, backoff_ns);
 }
+// The same wait with its polling loop inlined: for kernels whose warps change their register allowance (setmaxnreg),
+// where a function shared by regions with different allowances cannot be allocated.
+__device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                 uint32_t backoff_ns = 0) {
+  if (mbar_try_addr(bar, parity)) return true;
+  const uint64_t start = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_addr(bar, parity)) return true;
+    if (backoff_ns != 0) __nanosleep(backoff_ns);
+    if ((++spins & 31u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
 __device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -305,6 +325,14 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d, uint64_t a, uint64_t b, ui
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -609,7 +637,8 @@ inline CUtensorMapSwizzle swizzle_for_bytes(int inner_bytes) {
 // Tiled tensor map over `rank` dimensions (innermost first). `strides_bytes` has rank-1 entries (dimension 0 is dense).
 inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const uint64_t* dims,
                            const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
-                           CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
+                           CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           const uint32_t* element_strides = nullptr) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return kNoDriver;
   cuuint64_t d[5], s[4];
@@ -617,7 +646,7 @@ inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank,
   for (int i = 0; i < rank; ++i) {
     d[i] = dims[i];
     b[i] = box[i];
-    e[i] = 1;
+    e[i] = element_strides != nullptr ? element_strides[i] : 1;
     if (i + 1 < rank) s[i] = strides_bytes[i];
   }
   const CUresult r = fn(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -31,7 +31,7 @@ constexpr int kSmemLimit = 226 * 1024;
 
 struct ConvParams {
   int cin, cout, out_h, out_w;
-  int kh, kw, pad_h, pad_w, dil_h, dil_w;
+  int kh, kw, pad_h, pad_w, dil_h, dil_w, stride_h, stride_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
   int row_tiles;   // row tiles (of a CTA pair: pairs of them) per output-channel tile
   int n_major;     // tile order: 1 = all row tiles of an output-channel tile before the next (keeps weight scales resident)
@@ -58,6 +58,7 @@ struct ConvParams {
   uint8_t* out_scales;
   const float* out_scale;
   int* status;
+  uint32_t poll_backoff_ns;  // sleep between polls of the epilogue's wait for an accumulator
   int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
 
@@ -116,6 +117,12 @@ __device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, uint32_t table) {
   asm("prmt.b32 %0, %1, %2, 0x00B9;" : "=r"(negative) : "r"(r), "r"(0u));
   const uint32_t delta = __byte_perm(w0, w1, (negative & 0x2222u) | 0x5410u);
   return __viaddmax_s16x2(a, delta, 0u) | (r & 0x80008000u);
+}
+
+__device__ __forceinline__ uint32_t idesc_bf16(int block_n, int block_m = kTileM) {
+  // F32 accumulator (1), BF16 A and B (1), both K-major, M = block_m, N = block_n (kind::f16)
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(block_n >> 3) << 17) |
+         (static_cast<uint32_t>(block_m >> 4) << 24);
 }
 
 // ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
@@ -327,12 +334,18 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
 // 2/3 of the operand bytes per MMA through its shared memory, which is what bounds the single-CTA form. Barriers: the
 // stage's "full" barrier lives in the leader and counts both CTAs' bytes; "empty" and "accumulator full" exist in both
 // CTAs and the leader's commits arrive on both; "accumulator empty" lives in the leader and collects both epilogues.
-template <bool INT8, int BN, int BK, bool PAIR>
+// FMT: 0 = block-scaled MXFP8, 1 = INT8, 2 = BF16 (plain kind::f16 MMAs on 2-byte elements; every size below is in bytes
+// of K, so a BF16 layer is a conv over 2 * Cin "channels" of one byte without scales).
+constexpr int kFmtMx = 0, kFmtI8 = 1, kFmtBf16 = 2;
+
+template <int FMT, int BN, int BK, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
             const __grid_constant__ CUtensorMap sfa_map, const ConvParams p) {
   static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
+  constexpr bool INT8 = FMT == kFmtI8;
+  constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
   constexpr int kAccStages = acc_stages(BN);
   constexpr int kScaleTilesB = scale_tiles_b(BN);
   constexpr int kKSteps = BK / 32;
@@ -344,7 +357,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   // then the resident weight scales (kSfbColumns per K iteration, kept while consecutive tiles share their channels)
   const uint32_t sfa_column = kSfbColumn + static_cast<uint32_t>(p.stages) * kSfbColumns;
   const uint32_t resident_column =
-      sfa_column + 4u * static_cast<uint32_t>(!INT8 && p.act_scales != nullptr ? p.stages : (p.cin + 127) / 128);
+      sfa_column + 4u * static_cast<uint32_t>(SCALED && p.act_scales != nullptr ? p.stages : (p.cin + 127) / 128);
   constexpr int kEpiGroups = BN >= 128 ? 4 : 2;          // column groups of the epilogue, four warps (one per lane quarter) each
   constexpr int kChunksPerWarp = BN / (32 * kEpiGroups); // 32-column chunks each epilogue warp owns
 
@@ -365,7 +378,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_gelu = smem_bias + p.tiles_n * BN * 4;                 // kGeluTable, when the epilogue applies GELU
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool dynamic_a = !INT8 && p.act_scales != nullptr;
+  const bool dynamic_a = SCALED && p.act_scales != nullptr;
   const int taps = p.kh * p.kw;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                   // 0: the CTA that issues the MMAs
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);  // tile walker index
@@ -395,7 +408,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       tmem_relinquish();
     }
   }
-  if (warp == 2 && !INT8 && !dynamic_a) {
+  if (warp == 2 && SCALED && !dynamic_a) {
     // static activation scales: one 512-byte tile per 128 input channels, the same 4 bytes in all 128 rows
     const int tiles = (p.cin + 127) / 128;
     const int groups = p.cin / 32;
@@ -447,14 +460,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int tx = m % p.tiles_x; m /= p.tiles_x;
         const int ty = m % p.tiles_y;
         const int b = m / p.tiles_y;
-        const int x0 = tx * p.tile_w - p.pad_w, y0 = ty * p.tile_h - p.pad_h;
+        const int x0 = tx * p.tile_w * p.stride_w - p.pad_w, y0 = ty * p.tile_h * p.stride_h - p.pad_h;
         // the weight tile arrives in boxes of kWeightBoxRows rows (a 256-wide tile is two boxes, its half one)
         const int b_parts = PAIR ? 1 : width / kWeightBoxRows;
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         // a pair's barrier (in the leader) counts the bytes of both CTAs, which load the same amounts
         const uint32_t operand_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? static_cast<uint32_t>(PAIR ? width / 2 : width) * BK : 0u) +
                                        (dynamic_a ? 512u : 0u);
-        const uint32_t sfb_bytes = INT8 ? 0u : scale_tiles * 512u;
+        const uint32_t sfb_bytes = SCALED ? scale_tiles * 512u : 0u;
         // weight scales of the first resident_k iterations are already in tensor memory when the tile before this one
         // had the same output channels
         const bool fresh = n0 != last_n0;
@@ -476,7 +489,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 break;
               }
               const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
-              const bool load_sfb = !INT8 && (fresh || k0 >= p.resident_k * BK);
+              const bool load_sfb = SCALED && (fresh || k0 >= p.resident_k * BK);
               const uint32_t tx_bytes = (PAIR ? 2u : 1u) * (operand_bytes + (load_sfb ? sfb_bytes : 0u));
               if (!PAIR || rank == 0) {
                 if (tx_bytes != 0) {
@@ -488,7 +501,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               if (PAIR) {
                 if (load_a) tma_load_4d_pair(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
                 if (load_b) tma_load_2d_pair(smem_b + s * kBBytes, &weight_map, bar, k0, n0 + static_cast<int>(rank) * (BN / 2));
-                if (!INT8) {
+                if (SCALED) {
                   // scale tiles through their tensor maps (128 words of 4 bytes per tile): only a tiled load can count
                   // on a barrier in the other CTA
                   const int w_tile = k0 >> 7;
@@ -515,7 +528,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                   }
                 }
               }
-              if (!INT8) {
+              if (SCALED) {
                 const int w_tile = k0 >> 7;
 #pragma unroll
                 for (int i = 0; i < kScaleTilesB; ++i) {
@@ -537,8 +550,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
       const int k_iters = taps * p.k_chunks;
-      const bool copy_scales = !INT8 && !(probe_flags(p) & 8);
-      if (!INT8 && !dynamic_a) {
+      const bool copy_scales = SCALED && !(probe_flags(p) & 8);
+      if (SCALED && !dynamic_a) {
         // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
         const int tiles = (p.cin + 127) / 128;
         for (int t = 0; t < tiles; ++t) {
@@ -560,7 +573,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const uint32_t d_tmem = tmem + acc * BN;
         int m_tile, n0, width;
         decode_tile<BN>(p, tile, m_tile, n0, width);
-        const uint32_t idesc = INT8 ? idesc_i8(width, PAIR ? 256 : kTileM) : idesc_mxf8(width, PAIR ? 256 : kTileM);
+        const uint32_t idesc = INT8 ? idesc_i8(width, PAIR ? 256 : kTileM)
+                                    : (SCALED ? idesc_mxf8(width, PAIR ? 256 : kTileM) : idesc_bf16(width, PAIR ? 256 : kTileM));
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         const bool fresh = n0 != last_n0;  // the resident weight scales belong to other output channels
         last_n0 = n0;
@@ -614,6 +628,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               } else {
                 tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
               }
+            } else if (!SCALED) {
+              tc_mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
             } else {
               const uint32_t scaled = idesc | ((a_id + k) << 29) | ((b_id + k) << 4);
               if (PAIR) {
@@ -688,7 +704,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       // deciding warp cannot be two tiles ahead of a sibling, which it meets at this barrier every tile.
       volatile int* go = &ctl.group_go[group][tile_it & 1u];
       if (quarter == 0) {
-        const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, 200u);
+        const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.poll_backoff_ns);
         if (lane == 0) *go = arrived ? 1 : 0;
         __syncwarp();
       }
@@ -816,17 +832,20 @@ int out_elem_bytes(int out_mode) {
   }
 }
 
-int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan) {
+int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan) {
+  // `g.cin` counts bytes of K per tap here (a BF16 layer arrives with its channel count doubled)
+  const bool int8 = fmt == kFmtI8, scaled = fmt == kFmtMx;
   if (g.batch <= 0 || g.height <= 0 || g.width <= 0 || g.cin <= 0 || g.cout <= 0) return kBadArgument;
   if (g.cin % 32 || g.cout % 32) return kUnsupported;
-  if (g.stride_h != 1 || g.stride_w != 1) return kUnsupported;
+  if (g.stride_h < 1 || g.stride_w < 1) return kBadArgument;
+  if (g.stride_h > 4 || g.stride_w > 4) return kUnsupported;
   if (g.kh < 1 || g.kw < 1 || g.dil_h < 1 || g.dil_w < 1 || g.pad_h < 0 || g.pad_w < 0) return kBadArgument;
-  const int out_h = g.height + 2 * g.pad_h - g.dil_h * (g.kh - 1);
-  const int out_w = g.width + 2 * g.pad_w - g.dil_w * (g.kw - 1);
-  if (out_h <= 0 || out_w <= 0) return kBadArgument;
-  const bool pointwise = g.kh == 1 && g.kw == 1 && g.pad_h == 0 && g.pad_w == 0;
+  const int span_h = g.height + 2 * g.pad_h - g.dil_h * (g.kh - 1), span_w = g.width + 2 * g.pad_w - g.dil_w * (g.kw - 1);
+  if (span_h <= 0 || span_w <= 0) return kBadArgument;
+  const int out_h = (span_h - 1) / g.stride_h + 1, out_w = (span_w - 1) / g.stride_w + 1;
+  const bool pointwise = g.kh == 1 && g.kw == 1 && g.pad_h == 0 && g.pad_w == 0 && g.stride_h == 1 && g.stride_w == 1;
   if (per_pixel && !(pointwise && allow_flat)) return kUnsupported;
-  if (!int8 && !per_pixel && (g.cin + 127) / 128 > kMaxStaticScaleTiles) return kUnsupported;
+  if (scaled && !per_pixel && (g.cin + 127) / 128 > kMaxStaticScaleTiles) return kUnsupported;
   Plan pl;
   pl.out_h = out_h, pl.out_w = out_w;
   pl.block_k = g.cin % 128 == 0 ? 128 : (g.cin % 64 == 0 ? 64 : 32);
@@ -836,7 +855,8 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
   if (g_forced_block_n == 256 && g.cout > 128) bn = 256;
   if (g_forced_block_n == 128 && g.cout > 64) bn = 128;
   if (g_forced_block_n == 64) bn = 64;
-  if (bn == 64 && g.cout > 64 && !int8) bn = 128;  // a 64-wide tile may only start at column 0 of its scale tile
+  if (fmt == kFmtBf16 && bn == 256) bn = 128;  // BF16 layers on this path are narrow pointwise products
+  if (bn == 64 && g.cout > 64 && scaled) bn = 128;  // a 64-wide tile may only start at column 0 of its scale tile
   pl.block_n = bn;
   pl.flat = pointwise && allow_flat;
   if (pl.flat) {
@@ -850,6 +870,7 @@ int make_plan(const FimConvGeometry& g, bool int8, bool per_pixel, bool allow_fl
     pl.tile_h = 1, pl.tile_w = kTileM;
     for (int tw = 4; tw <= kTileM; ++tw) {
       const int th = kTileM / tw;
+      if (tw * g.stride_w > 256 || th * g.stride_h > 256) continue;  // a TMA box spans at most 256 positions per dimension
       const double covered = static_cast<double>(ceil_div(out_w, tw)) * ceil_div(out_h, th) * kTileM;
       const double eff = static_cast<double>(out_w) * out_h / covered;
       if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > pl.tile_w)) {
@@ -932,14 +953,14 @@ struct ConvMaps {
   CUtensorMap act, weight, out, sfb, sfa;
 };
 
-template <bool INT8, int BN, int BK, bool PAIR>
+template <int FMT, int BN, int BK, bool PAIR>
 int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
   // the shared-memory opt-in is a per-device attribute of the function: set once per device and instantiation
   static bool configured[kMaxDevices] = {};
   const int device = current_device();
   if (device < 0 || device >= kMaxDevices || !configured[device]) {
     const cudaError_t e =
-        cudaFuncSetAttribute(conv_kernel<INT8, BN, BK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        cudaFuncSetAttribute(conv_kernel<FMT, BN, BK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
@@ -954,40 +975,50 @@ int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaS
     attribute.val.clusterDim.x = 2, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<INT8, BN, BK, PAIR>, maps.act, maps.weight, maps.out, maps.sfb,
+    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR>, maps.act, maps.weight, maps.out, maps.sfb,
                                                maps.sfa, p));
   }
-  conv_kernel<INT8, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, p);
+  conv_kernel<FMT, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, p);
   return static_cast<int>(cudaGetLastError());
 }
 
-template <bool INT8, int BN>
+template <int FMT, int BN>
 int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
-  if constexpr (BN == 256) {
+  if constexpr (BN == 256 && FMT != kFmtBf16) {
     if (pl.pair) {
-      if (pl.block_k == 128) return launch_conv<INT8, BN, 128, true>(maps, p, pl, stream);
-      if (pl.block_k == 64) return launch_conv<INT8, BN, 64, true>(maps, p, pl, stream);
-      return launch_conv<INT8, BN, 32, true>(maps, p, pl, stream);
+      if (pl.block_k == 128) return launch_conv<FMT, BN, 128, true>(maps, p, pl, stream);
+      if (pl.block_k == 64) return launch_conv<FMT, BN, 64, true>(maps, p, pl, stream);
+      return launch_conv<FMT, BN, 32, true>(maps, p, pl, stream);
     }
   }
-  if (pl.block_k == 128) return launch_conv<INT8, BN, 128, false>(maps, p, pl, stream);
-  if (pl.block_k == 64) return launch_conv<INT8, BN, 64, false>(maps, p, pl, stream);
-  return launch_conv<INT8, BN, 32, false>(maps, p, pl, stream);
+  if (pl.block_k == 128) return launch_conv<FMT, BN, 128, false>(maps, p, pl, stream);
+  if (pl.block_k == 64) return launch_conv<FMT, BN, 64, false>(maps, p, pl, stream);
+  return launch_conv<FMT, BN, 32, false>(maps, p, pl, stream);
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* act_scales, const void* weight,
-             const void* weight_scales, const float* a_scale, const float* w_scale, const FimConvGeometry* g,
+int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act_scales, const void* weight,
+             const void* weight_scales, const float* a_scale, const float* w_scale, const FimConvGeometry* geometry,
              const FimConvEpilogue* ep, void* out, int* status, void* stream) {
-  if (g == nullptr || ep == nullptr) return kBadArgument;
-  if (g->batch == 0 || g->height == 0 || g->width == 0) return kOk;
+  const bool int8 = fmt == kFmtI8;
+  if (geometry == nullptr || ep == nullptr) return kBadArgument;
+  if (geometry->batch == 0 || geometry->height == 0 || geometry->width == 0) return kOk;
   if (x == nullptr || weight == nullptr || out == nullptr) return kBadArgument;
   if (ep->act < 0 || ep->act > 3 || ep->out_mode < 0 || ep->out_mode > 5) return kBadArgument;
+  // the kernel counts K in bytes: a BF16 layer is a layer of 2 * Cin one-byte channels
+  FimConvGeometry bytes = *geometry;
+  if (fmt == kFmtBf16) {
+    if (geometry->cin % 16) return kUnsupported;
+    bytes.cin = 2 * geometry->cin;
+  }
+  const FimConvGeometry* g = &bytes;
   if (int8) {
     if (ep->out_mode != FIM_OUT_INT32 && (a_scale == nullptr || w_scale == nullptr)) return kBadArgument;
     if (ep->out_mode != FIM_OUT_BF16 && ep->out_mode != FIM_OUT_INT8 && ep->out_mode != FIM_OUT_INT32) return kBadArgument;
     if (ep->out_mode == FIM_OUT_INT8 && ep->out_scale == nullptr) return kBadArgument;
+  } else if (fmt == kFmtBf16) {
+    if (ep->out_mode != FIM_OUT_BF16 && ep->out_mode != FIM_OUT_F32) return kBadArgument;
   } else {
     if (weight_scales == nullptr || (act_exponent == nullptr) == (act_scales == nullptr)) return kBadArgument;
     if (ep->out_mode == FIM_OUT_INT8 || ep->out_mode == FIM_OUT_INT32) return kBadArgument;
@@ -1005,7 +1036,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   Plan pl;
   {
     Plan probe;
-    const int rc0 = make_plan(*g, int8, act_scales != nullptr, true, out_elem, ep->act == FIM_ACT_GELU, &probe);
+    const int rc0 = make_plan(*g, fmt, act_scales != nullptr, true, out_elem, ep->act == FIM_ACT_GELU, &probe);
     if (rc0 != kOk) return rc0;
     if (probe.flat && ep->residual != nullptr) {
       const long long c = ep->res_stride[3], xs = ep->res_stride[2], ys = ep->res_stride[1], bs = ep->res_stride[0];
@@ -1013,14 +1044,15 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
       if (!dense) allow_flat = false;
     }
   }
-  const int rc = make_plan(*g, int8, act_scales != nullptr, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl);
+  const int rc = make_plan(*g, fmt, act_scales != nullptr, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl);
   if (rc != kOk) return rc;
 
-  const Schedule sc = make_schedule(*g, pl, int8, act_scales != nullptr);
+  const Schedule sc = make_schedule(*g, pl, fmt != kFmtMx, act_scales != nullptr);
   ConvParams p;
   p.cin = g->cin, p.cout = g->cout;
   p.out_h = pl.out_h, p.out_w = pl.out_w;
   p.kh = g->kh, p.kw = g->kw, p.pad_h = g->pad_h, p.pad_w = g->pad_w, p.dil_h = g->dil_h, p.dil_w = g->dil_w;
+  p.stride_h = g->stride_h, p.stride_w = g->stride_w;
   p.tile_h = pl.tile_h, p.tile_w = pl.tile_w, p.tiles_x = pl.tiles_x, p.tiles_y = pl.tiles_y, p.tiles_n = pl.tiles_n;
   p.total_tiles = sc.total_tiles;
   p.full_tiles = sc.full_tiles;
@@ -1045,6 +1077,7 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
   p.out_scale = ep->out_scale;
   p.status = status;
   p.debug = g_debug_flags;
+  p.poll_backoff_ns = (g_debug_flags & 32) ? 0u : 200u;
 
   // tensor maps: activations [B, H, W, Cin] and outputs [B, Ho, Wo, Cout * elem bytes] (a flat 1x1 conv sees one row of
   // B*H*W pixels), weights [Cout, K]
@@ -1064,8 +1097,12 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
                               static_cast<uint64_t>(in_b)};
     const uint64_t strides[3] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w) * g->cin,
                                  static_cast<uint64_t>(in_h) * in_w * g->cin};
-    const uint32_t box[4] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.tile_w), static_cast<uint32_t>(pl.tile_h), 1};
-    const int rcm = make_tensor_map(&act_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x, dims, strides, box, swizzle_for_bytes(pl.block_k));
+    // a strided conv reads every stride-th pixel of a box stride times as wide: the copy lands densely in shared memory
+    const uint32_t box[4] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.tile_w * g->stride_w),
+                             static_cast<uint32_t>(pl.tile_h * g->stride_h), 1};
+    const uint32_t steps[4] = {1, static_cast<uint32_t>(g->stride_w), static_cast<uint32_t>(g->stride_h), 1};
+    const int rcm = make_tensor_map(&act_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x, dims, strides, box, swizzle_for_bytes(pl.block_k),
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, steps);
     if (rcm != kOk) return rcm;
   }
   {
@@ -1103,13 +1140,18 @@ int run_conv(bool int8, const void* x, const int8_t* act_exponent, const void* a
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int8) {
-    if (pl.block_n == 64) return launch_conv_k<true, 64>(maps, p, pl, s);
-    if (pl.block_n == 128) return launch_conv_k<true, 128>(maps, p, pl, s);
-    return launch_conv_k<true, 256>(maps, p, pl, s);
+    if (pl.block_n == 64) return launch_conv_k<kFmtI8, 64>(maps, p, pl, s);
+    if (pl.block_n == 128) return launch_conv_k<kFmtI8, 128>(maps, p, pl, s);
+    return launch_conv_k<kFmtI8, 256>(maps, p, pl, s);
   }
-  if (pl.block_n == 64) return launch_conv_k<false, 64>(maps, p, pl, s);
-  if (pl.block_n == 128) return launch_conv_k<false, 128>(maps, p, pl, s);
-  return launch_conv_k<false, 256>(maps, p, pl, s);
+  if (fmt == kFmtBf16) {
+    if (pl.block_n == 64) return launch_conv_k<kFmtBf16, 64>(maps, p, pl, s);
+    if (pl.block_n == 128) return launch_conv_k<kFmtBf16, 128>(maps, p, pl, s);
+    return kUnsupported;
+  }
+  if (pl.block_n == 64) return launch_conv_k<kFmtMx, 64>(maps, p, pl, s);
+  if (pl.block_n == 128) return launch_conv_k<kFmtMx, 128>(maps, p, pl, s);
+  return launch_conv_k<kFmtMx, 256>(maps, p, pl, s);
 }
 
 }  // namespace
@@ -1120,20 +1162,25 @@ using namespace fim;
 extern "C" int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const void* act_scales_swizzled, const void* weight,
                                 const void* weight_scales_swizzled, const FimConvGeometry* geometry,
                                 const FimConvEpilogue* epilogue, void* out, int* status, void* stream) {
-  return run_conv(false, x, act_exponent, act_scales_swizzled, weight, weight_scales_swizzled, nullptr, nullptr, geometry, epilogue,
+  return run_conv(kFmtMx, x, act_exponent, act_scales_swizzled, weight, weight_scales_swizzled, nullptr, nullptr, geometry, epilogue,
                   out, status, stream);
 }
 
 extern "C" int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, const float* w_scale,
                                const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status,
                                void* stream) {
-  return run_conv(true, x, nullptr, nullptr, weight, nullptr, a_scale, w_scale, geometry, epilogue, out, status, stream);
+  return run_conv(kFmtI8, x, nullptr, nullptr, weight, nullptr, a_scale, w_scale, geometry, epilogue, out, status, stream);
+}
+
+extern "C" int fim_bf16_conv2d(const void* x, const void* weight, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue,
+                               void* out, int* status, void* stream) {
+  return run_conv(kFmtBf16, x, nullptr, nullptr, weight, nullptr, nullptr, nullptr, geometry, epilogue, out, status, stream);
 }
 
 extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]) {
   if (geometry == nullptr || plan == nullptr) return kBadArgument;
   Plan pl;
-  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, false, &pl);
+  const int rc = make_plan(*geometry, int8 != 0 ? kFmtI8 : kFmtMx, per_pixel_scales != 0, true, 2, false, &pl);
   if (rc != kOk) return rc;
   plan[0] = pl.tile_h, plan[1] = pl.tile_w, plan[2] = pl.block_n, plan[3] = pl.block_k, plan[4] = pl.stages, plan[5] = pl.ctas;
   return kOk;
@@ -1142,7 +1189,7 @@ extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_
 extern "C" int fim_conv_schedule(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int schedule[8]) {
   if (geometry == nullptr || schedule == nullptr) return kBadArgument;
   Plan pl;
-  const int rc = make_plan(*geometry, int8 != 0, per_pixel_scales != 0, true, 2, false, &pl);
+  const int rc = make_plan(*geometry, int8 != 0 ? kFmtI8 : kFmtMx, per_pixel_scales != 0, true, 2, false, &pl);
   if (rc != kOk) return rc;
   const Schedule sc = make_schedule(*geometry, pl, int8 != 0, per_pixel_scales != 0);
   schedule[0] = pl.total_tiles, schedule[1] = sc.full_tiles, schedule[2] = sc.total_tiles, schedule[3] = pl.ctas;

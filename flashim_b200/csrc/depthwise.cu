@@ -10,9 +10,9 @@
 //
 // What bounds it is the fp32 pipe (25 FMAs per element, plus the polynomial of the GELU) and, next to it, the issue slots
 // of everything else. Two things keep the pipe fed: (1) every warp computes - there is no producer warp holding
-// registers; lane 0 of warp 0 issues the TMA copy of the chunk COLS-independent stages ahead whenever it hands a chunk
-// back - so that with COLS = 2 sixteen warps fit on an SM at 128 registers, four per scheduler, and the latency of one
-// warp's shared-memory reads and shuffles hides behind the FMAs of the others; (2) the epilogue is written for issue
+// registers; lane 0 of warp 0 issues the TMA copy four chunks ahead whenever it hands a chunk back - so that three CTAs
+// of four warps fit on an SM at 168 registers and the latency of one warp's shared-memory reads and shuffles hides
+// behind the FMAs of the others; (2) the epilogue is written for issue
 // slots: the five rows of a chunk are one straight-line block (accumulator slots, shared-memory offsets and weights are
 // all compile-time), barriers are touched once per chunk, a fresh accumulator starts with a multiply instead of being
 // zeroed, GELU is one MUFU and a Horner polynomial with immediate operands per value, and the MX block maximum over 16
@@ -403,22 +403,20 @@ struct Variant {
   int cols, warps, ctas_per_sm;
 };
 constexpr Variant kVariants[] = {
-    {2, 8, 2},  // 1: 16 columns, 16 warps per SM at 128 registers
-    {2, 5, 3},  // 2: 10 columns, 15 warps per SM
-    {2, 4, 4},  // 3: 8 columns, 16 warps per SM
-    {4, 4, 3},  // 4: 16 columns, 12 warps per SM at 168 registers
-    {4, 5, 2},  // 5: 20 columns, 10 warps per SM
-    {2, 6, 2},  // 6: 12 columns, 12 warps per SM with registers to spare
+    {4, 4, 3},  // 1: 16 columns, 12 warps per SM at 168 registers
+    {4, 5, 2},  // 2: 20 columns, 10 warps per SM
+    {2, 8, 2},  // 3: 16 columns, 16 warps per SM at 128 registers (two columns per lane)
 };
 constexpr int kVariantCount = sizeof(kVariants) / sizeof(kVariants[0]);
 
 int pick_variant(int width) {
   if (g_dw_variant >= 1 && g_dw_variant <= kVariantCount) return g_dw_variant - 1;
   // Measured on 100- to 400-pixel-wide images with every epilogue: four columns per lane on three CTAs of four warps is the
-  // fastest layout throughout (the two-column layouts hold more warps but spend more instructions per element; 20-column
-  // tiles fit 100 and 200 columns exactly yet lose more to the fifth warp doubling up on one scheduler).
+  // fastest layout throughout. Two columns per lane hold sixteen warps on an SM but spend more instructions per element
+  // (dw -> MXFP8 on 8 x 400 x 400 x 128: 463 us against 369 us); 20-column tiles fit 100 and 200 columns exactly yet lose
+  // more to the fifth warp doubling up on one scheduler.
   (void)width;
-  return 3;
+  return 0;
 }
 
 template <int MODE, int COLS, int WARPS, int MIN_CTAS>
@@ -507,10 +505,7 @@ int launch(const void* value, const void* weight, const float* bias, void* out, 
   const unsigned grid = static_cast<unsigned>(want < resident ? want : resident);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (variant.cols == 2 && variant.warps == 8) e = launch_kernel<MODE, 2, 8, 2>(map, p, act, grid, s);
-  else if (variant.cols == 2 && variant.warps == 5) e = launch_kernel<MODE, 2, 5, 3>(map, p, act, grid, s);
-  else if (variant.cols == 2 && variant.warps == 6) e = launch_kernel<MODE, 2, 6, 2>(map, p, act, grid, s);
-  else if (variant.cols == 2) e = launch_kernel<MODE, 2, 4, 4>(map, p, act, grid, s);
+  if (variant.cols == 2) e = launch_kernel<MODE, 2, 8, 2>(map, p, act, grid, s);
   else if (variant.warps == 4) e = launch_kernel<MODE, 4, 4, 3>(map, p, act, grid, s);
   else e = launch_kernel<MODE, 4, 5, 2>(map, p, act, grid, s);
   return static_cast<int>(e);

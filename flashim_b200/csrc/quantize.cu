@@ -299,6 +299,34 @@ int launch_nchw(const void* value, int dtype, const int8_t* exponent, const floa
   return static_cast<int>(cudaGetLastError());
 }
 
+
+// GELU (erf form, evaluated in fp32) of a bf16 matrix plus an optional per-column bias, rounded to bf16, then the static
+// block-32 quantiser: out = e4m3(sat(bf16(gelu(float(v) + bias)) / 2**e)). 16 elements per thread; channels % 32 == 0.
+__global__ void __launch_bounds__(kThreads) gelu_quantize_mx_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ bias,
+                                                                    const int8_t* __restrict__ exps, uint8_t* __restrict__ out,
+                                                                    long long rows, int channels) {
+  const int chunks = channels / 16;
+  const long long total = rows * chunks;
+  for (long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * kThreads) {
+    const long long row = i / chunks;
+    const int c0 = static_cast<int>(i - row * chunks) * 16;
+    float v[16];
+    load16<__nv_bfloat16>(in + row * channels + c0, v);
+    const float inv = exp2_int(-static_cast<int>(exps[c0 >> 5]));
+    float q[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float x = bias != nullptr ? v[j] + __ldg(bias + c0 + j) : v[j];
+      q[j] = bf16_round(gelu_erf(x)) * inv;
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = e4m3x4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+    *reinterpret_cast<uint4*>(out + row * channels + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace
 }  // namespace fim
 
@@ -387,5 +415,16 @@ extern "C" int fim_maxpool2_quantize_int8(const void* value, const float* scale,
   const long long work = static_cast<long long>(batch) * (height / 2) * (width / 2) * (channels / 8);
   maxpool2_int8_kernel<<<grid_for(work, 16), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(value), scale, static_cast<uint2*>(out), batch, height, width, channels);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fim_gelu_quantize_mxfp8(const void* value, const float* input_bias, const int8_t* exponent, void* out, long long rows,
+                                       int channels, void* stream) {
+  if (rows == 0 && channels > 0) return kOk;
+  if (value == nullptr || exponent == nullptr || out == nullptr || rows < 0 || channels <= 0) return kBadArgument;
+  if (channels % 32) return kBadLayout;
+  if (!aligned16(value) || !aligned16(out)) return kBadLayout;
+  gelu_quantize_mx_kernel<<<grid_for(rows * (channels / 16), 16), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(value), input_bias, exponent, static_cast<uint8_t*>(out), rows, channels);
   return static_cast<int>(cudaGetLastError());
 }

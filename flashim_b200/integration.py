@@ -25,7 +25,9 @@ def register_into_flashim() -> list[str]:
     from flashim_b200.backends.sm100 import kernels
 
     names = ["mxfp8_conv2d", "int8_conv2d", "depthwise5x5_relu_mxfp8", "depthwise5x5_relu_int8", "quantize_mxfp8",
-             "quantize_int8", "mxfp8_scaled_mm", "int8_linear", "int8_conv2d_maxpool", "romav2_refiner_heads", "romav2_refiner_input"]
+             "quantize_int8", "mxfp8_scaled_mm", "int8_linear", "int8_conv2d_maxpool", "romav2_refiner_heads", "romav2_refiner_input",
+             "mxfp8_linear", "mxfp8_gelu_mlp", "gelu_quantize", "depthwise5x5_relu_pointwise", "depthwise5x5_relu_pointwise_mxfp8",
+             "depthwise5x5_relu_pointwise_int8"]
     if not _DONE:
         kernels.register(their_ops, DeviceSpec, Feature)
         _DONE = True

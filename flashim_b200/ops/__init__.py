@@ -43,6 +43,22 @@ mxfp8_scaled_mm = Op("mxfp8_scaled_mm", doc="(a E4M3 [M, K], b_t E4M3 [K, N] (th
 int8_linear = Op("int8_linear", doc="(a int8 [M, K], weight int8 [N, K], a_scale, w_scale, bias, *, relu, gelu, residual) -> "
                  "bf16 [M, N] (flashim/ops/gemm.py:82-98)")
 
+mxfp8_linear = Op("mxfp8_linear", doc="(activation QuantizedTensor [rows, K], bias [N] or None, weight QuantizedWeight [N, K]) -> "
+                  "bf16 [rows, N]: static MXFP8 linear (flashim/ops/gemm.py:58-72)")
+gelu_quantize = Op("gelu_quantize", doc="(value bf16 [..., C], scale_exponent, approximate='none', *, input_bias=None) -> "
+                   "QuantizedTensor: quantize_static(GELU(value [+ input_bias])) (flashim/ops/quantize.py:62-74)")
+mxfp8_gelu_mlp = Op("mxfp8_gelu_mlp", doc="(x QuantizedTensor, w1 QuantizedWeight, b1, hidden_exponent, w2 QuantizedWeight) -> bf16 "
+                    "[rows, N2]: linear, GELU(+ b1), static requantisation, linear (flashim/ops/gemm.py:146-157)")
+depthwise5x5_relu_pointwise = Op("depthwise5x5_relu_pointwise", doc="(value [B, C, H, W], dw_weight bf16 [25, C], dw_bias [C], pw_weight "
+                                 "bf16 [N, C], pw_bias bf16 [N]) -> bf16 channels-last [B, N, H, W]: the bf16 refiner block "
+                                 "(flashim/ops/conv.py:67-87)")
+depthwise5x5_relu_pointwise_mxfp8 = Op("depthwise5x5_relu_pointwise_mxfp8", doc="(value, dw_weight, dw_bias, pw_weight E4M3 [N, K], "
+                                       "pw_scale_swizzled, pw_scale_u8, pw_bias) -> bf16 [B, N, H, W]: depthwise5x5_relu_mxfp8 then "
+                                       "mxfp8_scaled_mm (flashim/ops/conv.py:93-113)")
+depthwise5x5_relu_pointwise_int8 = Op("depthwise5x5_relu_pointwise_int8", doc="(value, dw_weight, dw_bias, pw_weight int8 [N, K], "
+                                      "pw_wscale, pw_bias, scale) -> bf16 [B, N, H, W]: depthwise5x5_relu_int8 then int8_linear "
+                                      "(flashim/ops/conv.py:119-138)")
+
 # -- extensions --------------------------------------------------------------------------------------------------------
 quantize_mxfp8_dynamic = Op("quantize_mxfp8_dynamic", doc="(value [..., C]) -> (E4M3 [..., C], swizzled E8M0 bytes): "
                             "per-(row, 32) dynamic MXFP8, the quantiser of flashim/quant/formats/mx.py:50-60 as an op")

@@ -93,6 +93,14 @@ int fim_quantize_int8_static_nchw(const void* value, int dtype, const float* sca
 int fim_maxpool2_quantize_int8(const void* value, const float* scale, void* out, int batch, int height, int width, int channels,
                                void* stream);
 
+/* out = e4m3(sat(bf16(GELU(float(value) + input_bias)) / 2**exponent[c / 32])): erf-form GELU of a bf16 matrix
+ * `[rows, channels]` (channels % 32 == 0, 16-byte aligned) plus an optional fp32 per-channel bias (NULL: none), rounded
+ * to bf16 and quantised with static block-32 exponents.
+ * Replaces: ops.gelu_quantize with approximate = "none" (flashim/ops/quantize.py:62-74), the middle step of
+ * ops.mxfp8_gelu_mlp (flashim/ops/gemm.py:146-157). */
+int fim_gelu_quantize_mxfp8(const void* value, const float* input_bias, const int8_t* exponent, void* out, long long rows,
+                            int channels, void* stream);
+
 /* ---- RoMaV2 refiner heads -------------------------------------------------------------------------------------- */
 
 /* The 1x1 convolution of the refiner's last feature map to 2 displacement + 4 precision channels and what follows it:
@@ -149,7 +157,7 @@ int fim_dw5x5_relu_int8(const void* value, const void* weight, const float* bias
 /* ---- implicit-GEMM conv2d on tcgen05 tensor cores ----------------------------------------------------------- */
 
 typedef struct FimConvGeometry {
-  int batch, height, width, cin, cout; /* cin, cout: physical (padded) channel counts, multiples of 32 */
+  int batch, height, width, cin, cout; /* cin, cout: physical (padded) channel counts, multiples of 32 (BF16: cin % 16) */
   int kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
 } FimConvGeometry;
 
@@ -167,7 +175,8 @@ typedef struct FimConvEpilogue {
 
 /* Block-scaled MXFP8 conv: x E4M3 NHWC; activation scales either static (`act_exponent` int8 [cin/32], shared by every
  * pixel and tap) or per pixel (`act_scales_swizzled`: E8M0 bytes in the 128x4 swizzled layout over rows = B*H*W; 1x1
- * stride-1 unpadded convs only); weight E4M3 [cout, kh*kw*cin]; `weight_scales_swizzled`: E8M0 bytes of the
+ * stride-1 unpadded convs only). Strides 1 to 4 are supported (a strided conv reads every stride-th pixel through the
+ * tensor map's element strides); weight E4M3 [cout, kh*kw*cin]; `weight_scales_swizzled`: E8M0 bytes of the
  * [cout, kh*kw*cin/32] exponents in the 128x4 swizzled layout. fp32 accumulation in tensor memory, epilogue
  * bias -> bf16 rounding -> GELU -> residual add (one more bf16 rounding) -> ReLU -> requantisation, as `epilogue` selects:
  * GELU acts before the residual is added, ReLU after it (relu(out + residual), flashim/ops/conv.py:198-203).
@@ -182,6 +191,13 @@ int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const void* act_
  * Replaces ops.int8_conv2d (flashim/ops/conv.py:174-206; kernel flashim/backends/triton/conv.py:702-805). */
 int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, const float* w_scale,
                     const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status, void* stream);
+
+/* BF16 conv: x bf16 NHWC, weight bf16 [cout, kh*kw*cin] in (ky, kx, c) order, fp32 accumulation on the tensor cores
+ * (kind::f16), epilogue bias -> bf16 (FIM_OUT_BF16) or fp32 (FIM_OUT_F32), activation and residual as above. The
+ * pointwise product of ops.depthwise5x5_relu_pointwise (flashim/ops/conv.py:67-87; kernel
+ * flashim/backends/cuda/csrc/depthwise.cu:165-401) runs through this entry point as a 1x1 conv. */
+int fim_bf16_conv2d(const void* x, const void* weight, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out,
+                    int* status, void* stream);
 
 /* Tile configuration the conv entry points would use for a geometry (for reports and tests): writes
  * {tile_rows, tile_cols, block_n, block_k, stages, ctas}. Returns 0 or FIM_ERR_UNSUPPORTED. */

@@ -35,7 +35,8 @@ __all__ = [
     "mxfp8_conv2d", "int8_conv2d", "add_residual", "depthwise5x5_fp32", "depthwise5x5_relu_mxfp8",
     "depthwise5x5_relu_int8", "depthwise5x5_act_ext", "depthwise5x5_act_mxfp8_ext", "mxfp8_conv2d_ext",
     "int8_conv2d_accumulators_ext", "int8_conv2d_maxpool", "romav2_refiner_input", "romav2_refiner_heads", "mxfp8_scaled_mm", "int8_linear", "refiner_block_ext", "refiner_level_ext", "make_refiner_level_weights",
-    "dequantize_mx",
+    "dequantize_mx", "mxfp8_linear", "gelu_quantize", "mxfp8_gelu_mlp", "depthwise5x5_relu_pointwise",
+    "depthwise5x5_relu_pointwise_mxfp8", "depthwise5x5_relu_pointwise_int8",
 ]
 
 
@@ -352,6 +353,56 @@ def int8_linear(a, weight, a_scale, w_scale, bias, *, relu=False, gelu=False, re
     if residual is not None:
         out = residual + out
     return out
+
+
+def mxfp8_linear(values: Tensor, scale_exponent: Tensor, bias: Tensor | None, weight: Tensor, weight_exponent: Tensor) -> Tensor:
+    """Static MXFP8 linear: E4M3 ``values [rows, K]`` under the shared exponents ``[K/32]``, E4M3 ``weight [N, K]`` under
+    ``[N, K/32]`` exponents; fp32 product, ``+ bias`` in fp32, one bf16 rounding (flashim/ops/gemm.py:58-69)."""
+    out = mx_matmul_fp32(values, scale_exponent, weight, weight_exponent)
+    if bias is not None:
+        out = out + bias.float()
+    return out.to(torch.bfloat16)
+
+
+def gelu_quantize(value: Tensor, scale_exponent: Tensor, *, input_bias: Tensor | None = None) -> Tensor:
+    """``quantize_static(GELU(value [+ input_bias]))``, erf form: in fp32 when a bias is fused, else in ``value``'s dtype;
+    rounded to ``value``'s dtype before the static block-32 quantiser (flashim/ops/quantize.py:62-71)."""
+    if input_bias is not None:
+        activated = F.gelu(value.float() + input_bias.float()).to(value.dtype)
+    else:
+        activated = F.gelu(value)
+    return quantize_static_mx(activated, scale_exponent)
+
+
+def mxfp8_gelu_mlp(values, scale_exponent, w1, w1_exponent, b1, hidden_exponent, w2, w2_exponent) -> Tensor:
+    """``linear(quantize_static(GELU(linear(x, W1) [bf16] + b1) [bf16], hidden_exponent), W2)`` -> bf16; neither linear adds
+    a bias of its own (flashim/ops/gemm.py:146-154)."""
+    hidden = mxfp8_linear(values, scale_exponent, None, w1, w1_exponent)
+    return mxfp8_linear(gelu_quantize(hidden, hidden_exponent, input_bias=b1), hidden_exponent, None, w2, w2_exponent)
+
+
+def depthwise5x5_relu_pointwise(value, dw_weight, dw_bias, pw_weight, pw_bias) -> Tensor:
+    """bf16 refiner block: depthwise 5x5 + bias + ReLU in fp32, one bf16 rounding, pointwise ``[Cout, Cin]`` product in
+    fp32 plus bias, one bf16 rounding; NHWC ``[B, H, W, Cout]`` (the memory of the reference's channels-last result,
+    flashim/ops/conv.py:67-84)."""
+    hidden = F.relu(depthwise5x5_fp32(value, dw_weight, dw_bias)).to(torch.bfloat16).float()
+    out = F.conv2d(hidden, pw_weight.float()[:, :, None, None], pw_bias.float())
+    return out.to(torch.bfloat16).permute(0, 2, 3, 1).contiguous()
+
+
+def depthwise5x5_relu_pointwise_mxfp8(value, dw_weight, dw_bias, pw_weight, pw_scale_swizzled, pw_bias) -> Tensor:
+    """:func:`depthwise5x5_relu_mxfp8` then :func:`mxfp8_scaled_mm` with the pointwise weight ``[N, K]``; NHWC
+    ``[B, H, W, N]`` (flashim/ops/conv.py:93-110)."""
+    b, _, h, w = value.shape
+    q, scale = depthwise5x5_relu_mxfp8(value, dw_weight, dw_bias)
+    return mxfp8_scaled_mm(q, pw_weight.t(), scale, pw_scale_swizzled, pw_bias).reshape(b, h, w, -1)
+
+
+def depthwise5x5_relu_pointwise_int8(value, dw_weight, dw_bias, pw_weight, pw_wscale, pw_bias, scale) -> Tensor:
+    """:func:`depthwise5x5_relu_int8` then :func:`int8_linear`; NHWC ``[B, H, W, N]`` (flashim/ops/conv.py:119-135)."""
+    b, _, h, w = value.shape
+    q = depthwise5x5_relu_int8(value, dw_weight, dw_bias, scale)
+    return int8_linear(q, pw_weight, scale, pw_wscale, pw_bias).reshape(b, h, w, -1)
 
 
 def int8_conv2d_accumulators_ext(x, weight, kh, kw, sh, sw, ph, pw, dh, dw) -> Tensor:

@@ -48,12 +48,12 @@ def save(name: str, **arrays) -> None:
 
 
 def boundary_amax() -> torch.Tensor:
-    """amax values within +-6 ulp of ``448 * 2**k`` (where the fp32 log2 rule and the exact rule part ways), plus
-    zeros, tiny, huge and random values."""
+    """amax values within +-64 ulp of ``448 * 2**k`` (where the fp32 log2 rule and the exact rule part ways: the flip
+    point lies up to 39 ulp above the power of two, depending on the binade), plus zeros, tiny, huge and random values."""
     values = []
     for k in range(-60, 61):
         base = np.array([448.0 * 2.0**k], dtype=np.float32).view(np.int32)[0]
-        values += [base + n for n in range(-6, 7)]
+        values += [base + n for n in range(-64, 65)]
     edge = np.array(values, dtype=np.int32).view(np.float32)
     g = torch.Generator().manual_seed(10)
     rnd = torch.randn(4096, generator=g).abs() * torch.exp2(torch.randint(-30, 30, (4096,), generator=g).float())
@@ -253,11 +253,61 @@ def widening() -> None:
     save("widening", **arrays)
 
 
+def linears() -> None:
+    """Static MXFP8 linear, the GELU MLP and its middle step, INT8 linear with the GELU and ReLU-before-residual epilogues,
+    the bf16 depthwise + pointwise block and the two quantised composites (flashim/ops/gemm.py:58-157,
+    flashim/ops/quantize.py:62-74, flashim/ops/conv.py:67-138)."""
+    from flashim.quant.tensor import QuantizedTensor
+
+    g = torch.Generator().manual_seed(29)
+    arrays = {}
+    for i, (rows, k, hidden, n) in enumerate([(77, 64, 128, 32), (300, 128, 256, 96)]):
+        x = torch.randn(rows, k, generator=g).to(torch.bfloat16)
+        xe = ref_mx.calibrate_block32_exponent(x)
+        q = quantize_static(x, xe)
+        w1 = QuantizedWeight.from_float(torch.randn(hidden, k, generator=g) * 0.2)
+        w2 = QuantizedWeight.from_float(torch.randn(n, hidden, generator=g) * 0.2)
+        b1 = (torch.randn(hidden, generator=g) * 0.3).to(torch.bfloat16)
+        lin = ops.mxfp8_linear.get("reference")(q, b1, w1)
+        he = ref_mx.calibrate_block32_exponent(torch.nn.functional.gelu(lin.float()))
+        mlp = ops.mxfp8_gelu_mlp.get("reference")(q, w1, b1, he, w2)
+        gq = ops.gelu_quantize.get("reference")(lin, he, input_bias=b1.float())
+        gq_plain = ops.gelu_quantize.get("reference")(lin, he)
+        arrays.update({f"lin{i}_x": raw(q.values), f"lin{i}_xe": raw(xe), f"lin{i}_w1": raw(w1.values), f"lin{i}_w1e": raw(w1.scale_exponent),
+                       f"lin{i}_w2": raw(w2.values), f"lin{i}_w2e": raw(w2.scale_exponent), f"lin{i}_b1": raw(b1), f"lin{i}_he": raw(he),
+                       f"lin{i}_out": raw(lin), f"lin{i}_mlp": raw(mlp), f"lin{i}_gq": raw(gq.values), f"lin{i}_gq_plain": raw(gq_plain.values)})
+        a8 = torch.randint(-127, 128, (rows, k), dtype=torch.int8, generator=g)
+        w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=g)
+        ws = torch.rand(n, generator=g) * 0.002 + 0.0002
+        b8 = torch.randn(n, generator=g).to(torch.bfloat16)
+        res = torch.randn(rows, n, generator=g).to(torch.bfloat16)
+        scale = torch.tensor(0.02)
+        arrays.update({f"li{i}_a": raw(a8), f"li{i}_w": raw(w8), f"li{i}_ws": raw(ws), f"li{i}_b": raw(b8), f"li{i}_res": raw(res),
+                       f"li{i}_gelu": raw(ops.int8_linear.get("reference")(a8, w8, scale, ws, b8, gelu=True)),
+                       f"li{i}_gelu_res": raw(ops.int8_linear.get("reference")(a8, w8, scale, ws, b8, gelu=True, residual=res)),
+                       f"li{i}_relu_res": raw(ops.int8_linear.get("reference")(a8, w8, scale, ws, b8, relu=True, residual=res))})
+    for i, (b, c, h, w) in enumerate([(2, 32, 9, 11), (1, 64, 12, 7), (1, 128, 6, 10)]):
+        value = torch.randn(b, c, h, w, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dw_w = (torch.randn(25, c, generator=g) * 0.2).to(torch.bfloat16)
+        dw_b = torch.randn(c, generator=g)
+        pw_w = (torch.randn(c, c, generator=g) * 0.2).to(torch.bfloat16)
+        pw_b = torch.randn(c, generator=g).to(torch.bfloat16)
+        out = ops.depthwise5x5_relu_pointwise.get("reference")(value, dw_w, dw_b, pw_w, pw_b)
+        pq, pe = ref_mx.quantize_dynamic_2d(pw_w.float())
+        fused = ops.depthwise5x5_relu_pointwise_mxfp8.get("reference")(
+            value, dw_w, dw_b, pq, ref_mx.swizzle_scales(pe), ref_mx.exponent_to_e8m0(pe).view(torch.uint8), pw_b)
+        w8 = torch.randint(-127, 128, (c, c), dtype=torch.int8, generator=g)
+        ws = torch.rand(c, generator=g) * 0.002 + 0.0002
+        fused8 = ops.depthwise5x5_relu_pointwise_int8.get("reference")(value, dw_w, dw_b, w8, ws, pw_b, torch.tensor(0.03))
+        arrays.update({f"sep{i}_x": raw(value.permute(0, 2, 3, 1)), f"sep{i}_dw": raw(dw_w), f"sep{i}_db": raw(dw_b), f"sep{i}_pw": raw(pw_w),
+                       f"sep{i}_pb": raw(pw_b), f"sep{i}_out": raw(out.permute(0, 2, 3, 1)), f"sep{i}_pq": raw(pq), f"sep{i}_pe": raw(pe),
+                       f"sep{i}_mx": raw(fused.permute(0, 2, 3, 1)), f"sep{i}_w8": raw(w8), f"sep{i}_ws": raw(ws),
+                       f"sep{i}_i8": raw(fused8.permute(0, 2, 3, 1))})
+    save("linears", **arrays)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
-    formats()
-    convs()
-    depthwise()
-    modules()
-    gemms()
-    widening()
+    which = sys.argv[1:] or ["formats", "convs", "depthwise", "modules", "gemms", "widening", "linears"]
+    for name in which:
+        globals()[name]()

@@ -48,9 +48,11 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.fim_dw5x5_bf16(None, None, None, None, 1, 8, 8, 48, 0, None, None) == 99  # channels % 32
     assert lib.fim_dw5x5_bf16(None, None, None, None, 0, 8, 8, 64, 0, None, None) == 0
     assert lib.fim_dw5x5_bf16(None, None, None, None, 1, 8, 8, 64, 0, None, None) == -2
-    geometry = _native.ConvGeometry(1, 8, 8, 64, 64, 3, 3, 2, 2, 1, 1, 1, 1)
+    geometry = _native.ConvGeometry(1, 8, 8, 64, 64, 3, 3, 5, 5, 1, 1, 1, 1)
     plan = (ctypes.c_int * 6)()
-    assert lib.fim_conv_plan(ctypes.byref(geometry), 0, 0, ctypes.byref(plan)) == 99  # stride 2: no kernel
+    assert lib.fim_conv_plan(ctypes.byref(geometry), 0, 0, ctypes.byref(plan)) == 99  # stride 5: no kernel
+    geometry = _native.ConvGeometry(1, 8, 8, 64, 64, 3, 3, 2, 2, 1, 1, 1, 1)
+    assert lib.fim_conv_plan(ctypes.byref(geometry), 0, 0, ctypes.byref(plan)) == 0
     geometry = _native.ConvGeometry(4, 100, 100, 512, 512, 3, 3, 1, 1, 1, 1, 1, 1)
     assert lib.fim_conv_plan(ctypes.byref(geometry), 0, 0, ctypes.byref(plan)) == 0
     tile_h, tile_w, block_n, block_k, stages, ctas = list(plan)

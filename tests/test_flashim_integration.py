@@ -22,7 +22,9 @@ def test_registers_behind_flashims_own_registry():
 
     gained = register_into_flashim()
     assert set(gained) == {"mxfp8_conv2d", "int8_conv2d", "depthwise5x5_relu_mxfp8", "depthwise5x5_relu_int8",
-                           "quantize_mxfp8", "quantize_int8", "mxfp8_scaled_mm", "int8_linear", "int8_conv2d_maxpool", "romav2_refiner_heads", "romav2_refiner_input"}
+                           "quantize_mxfp8", "quantize_int8", "mxfp8_scaled_mm", "int8_linear", "int8_conv2d_maxpool", "romav2_refiner_heads", "romav2_refiner_input",
+                           "mxfp8_linear", "mxfp8_gelu_mlp", "gelu_quantize", "depthwise5x5_relu_pointwise",
+                           "depthwise5x5_relu_pointwise_mxfp8", "depthwise5x5_relu_pointwise_int8"}
     assert register_into_flashim() == gained  # idempotent
     b200 = Platform("cuda", 0, name="B200", capability=(10, 0),
                     features=frozenset({Feature.TCGEN05, Feature.TMA, Feature.NVCC, Feature.TRITON, Feature.FP8_E4M3,

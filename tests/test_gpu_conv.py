@@ -271,11 +271,12 @@ def test_baseline_config2(ops):
 
 
 def test_unsupported_geometry_raises(ops):
+    """A geometry outside what the kernels cover (stride 5 here) raises: there is no fallback to hide behind."""
     from flashim_b200.ops import NoImplementation
 
     x, ce, wq, we, bias = _mx_operands(1, 9, 9, 64, 64, 3, 3)
-    with pytest.raises(NoImplementation):  # stride 2 has no kernel and there is no fallback to hide behind
-        ops.mxfp8_conv2d(*to_dev(x, ce, wq, we, bias), 3, 3, 2, 2, 1, 1, 1, 1)
+    with pytest.raises(NoImplementation):
+        ops.mxfp8_conv2d(*to_dev(x, ce, wq, we, bias), 3, 3, 5, 5, 1, 1, 1, 1)
     report = ops.mxfp8_conv2d.explain(*to_dev(x, ce, wq, we, bias), 3, 3, 1, 1, 1, 1, 1, 1)
     assert report["sm100"] == "selected"
 
@@ -345,7 +346,7 @@ def test_mxfp8_scaled_mm_and_int8_linear_golden(ops, golden):
         assert same_bytes(fast(*args, residual=to_dev(g(f"li{i}_res", BF16))).cpu(), g(f"li{i}_out_res", BF16))
     # what the kernel does not cover is declined, not approximated
     a8, w8, s, ws, b = to_dev(g("li0_a"), g("li0_w"), torch.tensor(0.02), g("li0_ws"), g("li0_b", BF16))
-    assert ops.int8_linear.explain(a8, w8, s, ws, b, gelu=True)["sm100"] != "selected"
+    assert ops.int8_linear.explain(a8, w8, s, ws, b, relu=True, gelu=True)["sm100"] != "selected"
 
 
 # -- GELU in the epilogue ------------------------------------------------------------------------------------------------
@@ -391,7 +392,7 @@ def test_int8_epilogue_gelu_and_early_relu(ops):
     from flashim_b200 import _native
 
     xd, wd, sd, wsd, bd, rd = to_dev(x, w, a_scale.reshape(1), w_scale, bias, res)
-    got = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, _native.ACT["gelu"], _native.OUT_BF16)
+    got = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, 1, 1, _native.ACT["gelu"], _native.OUT_BF16)
     assert same_bytes(got.cpu(), res + F.gelu(plain.float()).to(BF16))
-    early = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, _native.ACT["relu_early"], _native.OUT_BF16)
+    early = int8_conv2d_launch(xd, wd, sd, wsd, bd, rd, None, 3, 3, 1, 1, 1, 1, 1, 1, _native.ACT["relu_early"], _native.OUT_BF16)
     assert same_bytes(early.cpu(), res + F.relu(plain))

@@ -286,3 +286,31 @@ def test_refiner_input_matches_reference_outputs(golden):
                                           torch.tensor([3.0, 2.0]), radius, pair)
         assert out.is_contiguous(memory_format=torch.channels_last)
         assert same_bytes(out.permute(0, 2, 3, 1), g(f"rin{i}_out", BF16)), f"case {i}"
+
+
+def test_linear_mlp_and_separable_blocks_match_reference_outputs(golden):
+    """Static MXFP8 linear, gelu_quantize, the GELU MLP, INT8 linear with GELU / ReLU-before-residual, the bf16 depthwise +
+    pointwise block and the two quantised composites, bit for bit against outputs of the reference itself."""
+    g = golden("linears")
+    for i in range(2):
+        x, xe = g(f"lin{i}_x", E4M3), g(f"lin{i}_xe")
+        w1, w1e, w2, w2e = g(f"lin{i}_w1", E4M3), g(f"lin{i}_w1e"), g(f"lin{i}_w2", E4M3), g(f"lin{i}_w2e")
+        b1, he = g(f"lin{i}_b1", BF16), g(f"lin{i}_he")
+        lin = oracle.mxfp8_linear(x, xe, b1, w1, w1e)
+        assert same_bytes(lin, g(f"lin{i}_out", BF16))
+        assert same_bytes(oracle.gelu_quantize(lin, he, input_bias=b1.float()), g(f"lin{i}_gq", E4M3))
+        assert same_bytes(oracle.gelu_quantize(lin, he), g(f"lin{i}_gq_plain", E4M3))
+        assert same_bytes(oracle.mxfp8_gelu_mlp(x, xe, w1, w1e, b1, he, w2, w2e), g(f"lin{i}_mlp", BF16))
+        args = (g(f"li{i}_a"), g(f"li{i}_w"), torch.tensor(0.02), g(f"li{i}_ws"), g(f"li{i}_b", BF16))
+        res = g(f"li{i}_res", BF16)
+        assert same_bytes(oracle.int8_linear(*args, gelu=True), g(f"li{i}_gelu", BF16))
+        assert same_bytes(oracle.int8_linear(*args, gelu=True, residual=res), g(f"li{i}_gelu_res", BF16))
+        assert same_bytes(oracle.int8_linear(*args, relu=True, residual=res), g(f"li{i}_relu_res", BF16))
+    for i in range(3):
+        value = g(f"sep{i}_x", BF16).permute(0, 3, 1, 2)
+        dw, db, pw, pb = g(f"sep{i}_dw", BF16), g(f"sep{i}_db"), g(f"sep{i}_pw", BF16), g(f"sep{i}_pb", BF16)
+        assert same_bytes(oracle.depthwise5x5_relu_pointwise(value, dw, db, pw, pb), g(f"sep{i}_out", BF16))
+        pq, pe = g(f"sep{i}_pq", E4M3), g(f"sep{i}_pe")
+        assert same_bytes(oracle.depthwise5x5_relu_pointwise_mxfp8(value, dw, db, pq, oracle.swizzle_32_4_4(pe), pb), g(f"sep{i}_mx", BF16))
+        assert same_bytes(oracle.depthwise5x5_relu_pointwise_int8(value, dw, db, g(f"sep{i}_w8"), g(f"sep{i}_ws"), pb, torch.tensor(0.03)),
+                          g(f"sep{i}_i8", BF16))
