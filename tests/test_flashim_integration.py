@@ -43,3 +43,31 @@ def test_registers_behind_flashims_own_registry():
     report = ops.mxfp8_conv2d.explain(*args)
     assert "does not match cpu" in report["sm100"] and report["reference"] == "selected"
     assert ops.mxfp8_conv2d(*args).shape == (1, 5, 6, 32)
+
+
+def test_conv_modules_are_routed_to_the_fused_op_on_capability_10():
+    """FlashIM's own gate keeps a wide MXFP8 conv on the im2col path unless the platform is one it was measured on; the
+    pass shipped here flips such modules to the fused op (and epilogue chaining) for compute capability 10.0 only."""
+    from flashim.quant.formats import mx
+    from flashim.quant.methods.conv2d import StaticInt8Conv2d, StaticMXFP8Conv2d
+
+    from flashim_b200 import integration
+
+    torch.manual_seed(0)
+    wide = torch.nn.Conv2d(256, 256, 3, padding=1)
+    strided = torch.nn.Conv2d(64, 64, 3, stride=2, padding=1)
+    x = torch.randn(1, 6, 6, 256)
+    model = torch.nn.Sequential(
+        StaticMXFP8Conv2d.from_conv(wide, mx.calibrate_block32_exponent(x)),
+        StaticMXFP8Conv2d.from_conv(strided, mx.calibrate_block32_exponent(x[..., :64])),
+        StaticInt8Conv2d.from_conv(strided, torch.tensor(0.05)),
+    )
+    assert not model[0].use_fused and not model[0].chain_output  # 72 (tap, block) products on an unlisted platform
+    assert integration.enable_sm100_conv_paths(model, capability=(9, 0)) == []
+    assert integration.enable_sm100_conv_paths(model) == []  # CPU tensors: no capability
+    changed = integration.enable_sm100_conv_paths(model, capability=(10, 0))
+    assert changed == ["0", "1", "2"]
+    assert all(m.use_fused and m.chain_output for m in model[:2]) and model[2].chain_output
+    assert model[0].feeds(model[0])
+    conv_pass = integration.SM100_CONV_PASS
+    assert conv_pass.stage == "post_quant" and conv_pass.apply(model, None) == []
