@@ -29,11 +29,32 @@ constexpr uint32_t kTmemColumns = 512;
 constexpr int kMaxStages = 12;  // a short K loop is bound by the latency of a stage's round trip: more stages in flight
 constexpr int kSmemLimit = 226 * 1024;
 
+// Division of a tile index by a run-time constant without the integer-division sequence (some forty instructions, which a
+// warp that owns 32 columns of a tile would pay several times per tile): q = floor(x * floor(2**32 / d) / 2**32) is the
+// quotient or one below it for every x < 2**32, so one compare-and-step finishes it. `magic` = floor(2**32 / d), or
+// 2**32 - 1 for d = 1 (which the same two steps turn into x).
+struct FastDiv {
+  uint32_t divisor, magic;
+};
+__host__ inline FastDiv make_fastdiv(int divisor) {
+  FastDiv f;
+  f.divisor = static_cast<uint32_t>(divisor < 1 ? 1 : divisor);
+  f.magic = f.divisor == 1 ? 0xFFFFFFFFu : static_cast<uint32_t>((1ull << 32) / f.divisor);
+  return f;
+}
+__device__ __forceinline__ void divmod(int x, const FastDiv& f, int& quotient, int& remainder) {
+  uint32_t q = __umulhi(static_cast<uint32_t>(x), f.magic);
+  uint32_t r = static_cast<uint32_t>(x) - q * f.divisor;
+  if (r >= f.divisor) ++q, r -= f.divisor;
+  quotient = static_cast<int>(q), remainder = static_cast<int>(r);
+}
+
 struct ConvParams {
   int cin, cout, out_h, out_w;
   int kh, kw, pad_h, pad_w, dil_h, dil_w, stride_h, stride_w;
   int tile_h, tile_w, tiles_x, tiles_y, tiles_n, total_tiles;
   int row_tiles;   // row tiles (of a CTA pair: pairs of them) per output-channel tile
+  FastDiv div_row_tiles, div_tiles_n, div_tiles_x, div_tiles_y;  // the same counts prepared for divmod()
   int n_major;     // tile order: 1 = all row tiles of an output-channel tile before the next (keeps weight scales resident)
   int batch;       // images (rows of a flattened 1x1 conv count as one)
   int full_tiles;  // tiles [0, full_tiles) are BN wide; the rest are the halves (BN / 2 columns) of the last few tiles
@@ -135,8 +156,29 @@ __device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_
   asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(bias_at + i * 16));
 }
 
-// bf16x2 words r[16] -> E4M3 codes of value * 2**-e, four per output word
+// bf16x2 words r[16] -> E4M3 codes of value * 2**-e, four per output word. The scaling is one mixed-precision FMA per
+// value (fp32 = bf16 * bf16 + -0, exact: a bf16 times a power of two; the addend -0 keeps the sign of a zero product),
+// which reads the halves of the packed word directly
+// and runs at the full fp32 rate; unpacking with shifts and masks first costs two half-rate integer instructions per pair.
 __device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[16]) {
+  // 2**-e as bf16 bits in both halves; 2**127 and 2**-127 (e = -127, 127) do not fit the bf16 exponent range exactly:
+  // those blocks (all-zero, or beyond 448 * 2**126) take the fp32 path
+  if (e > -127 && e < 127) {
+    const uint32_t inv16 = static_cast<uint32_t>(127 - e) << 7;
+    const uint32_t inv = inv16 | (inv16 << 16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float a, b, c, d;
+      asm("{\n\t.reg .b16 xl, xh, yl, yh, s, t;\n\t"
+          "mov.b32 {xl, xh}, %4;\n\tmov.b32 {yl, yh}, %5;\n\tmov.b32 {s, t}, %6;\n\t"
+          "fma.rn.f32.bf16 %0, xl, s, 0f80000000;\n\tfma.rn.f32.bf16 %1, xh, s, 0f80000000;\n\t"
+          "fma.rn.f32.bf16 %2, yl, s, 0f80000000;\n\tfma.rn.f32.bf16 %3, yh, s, 0f80000000;\n\t}"
+          : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+          : "r"(r[2 * i]), "r"(r[2 * i + 1]), "r"(inv));
+      w[i] = e4m3x4(a, b, c, d);
+    }
+    return;
+  }
   const float inv = exp2_int(-e);
   const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
@@ -319,11 +361,9 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
   }
   int nt;
   if (p.n_major) {
-    nt = whole / p.row_tiles;
-    m_tile = whole - nt * p.row_tiles;
+    divmod(whole, p.div_row_tiles, nt, m_tile);
   } else {
-    m_tile = whole / p.tiles_n;
-    nt = whole - m_tile * p.tiles_n;
+    divmod(whole, p.div_tiles_n, m_tile, nt);
   }
   n0 = nt * BN + half * (BN / 2);
 }
@@ -457,9 +497,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         decode_tile<BN>(p, tile, m_tile, n0, width);
         if (PAIR) m_tile = 2 * m_tile + static_cast<int>(rank);  // a pair owns two consecutive row tiles
         int m = m_tile;
-        const int tx = m % p.tiles_x; m /= p.tiles_x;
-        const int ty = m % p.tiles_y;
-        const int b = m / p.tiles_y;
+        int tx, ty, b;
+        divmod(m, p.div_tiles_x, m, tx);
+        divmod(m, p.div_tiles_y, b, ty);
         const int x0 = tx * p.tile_w * p.stride_w - p.pad_w, y0 = ty * p.tile_h * p.stride_h - p.pad_h;
         // the weight tile arrives in boxes of kWeightBoxRows rows (a 256-wide tile is two boxes, its half one)
         const int b_parts = PAIR ? 1 : width / kWeightBoxRows;
@@ -680,9 +720,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       decode_tile<BN>(p, tile, m, n0, width);
       if (PAIR) m = 2 * m + static_cast<int>(rank);
       const int n_end = min(p.cout, n0 + width);  // columns of this tile that exist
-      const int tx = m % p.tiles_x; m /= p.tiles_x;
-      const int ty = m % p.tiles_y;
-      const int b = m / p.tiles_y;
+      int tx, ty, b;
+      divmod(m, p.div_tiles_x, m, tx);
+      divmod(m, p.div_tiles_y, b, ty);
       const int x0 = tx * p.tile_w, y0 = ty * p.tile_h;
       const int x = x0 + rx, y = y0 + ry;
       const bool valid = row_in_tile && x < p.out_w && y < p.out_h && b < p.batch;
@@ -1059,6 +1099,8 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   p.batch = pl.flat ? 1 : g->batch;
   p.k_chunks = g->cin / pl.block_k, p.stages = pl.stages, p.panels_per_half = pl.panels_per_half;
   p.row_tiles = pl.total_tiles / pl.tiles_n;
+  p.div_row_tiles = make_fastdiv(p.row_tiles), p.div_tiles_n = make_fastdiv(pl.tiles_n);
+  p.div_tiles_x = make_fastdiv(pl.tiles_x), p.div_tiles_y = make_fastdiv(pl.tiles_y);
   p.resident_k = sc.resident_k, p.n_major = sc.n_major;
   p.act_exponent = act_exponent;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
