@@ -505,7 +505,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int b_parts = PAIR ? 1 : width / kWeightBoxRows;
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         // a pair's barrier (in the leader) counts the bytes of both CTAs, which load the same amounts
-        const uint32_t operand_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? static_cast<uint32_t>(PAIR ? width / 2 : width) * BK : 0u) +
+        // (a pair's weight box always has BN / 2 rows: for a half-width tile only the first width / 2 of them are used)
+        const uint32_t operand_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? (PAIR ? kBBytes : static_cast<uint32_t>(width) * BK) : 0u) +
                                        (dynamic_a ? 512u : 0u);
         const uint32_t sfb_bytes = SCALED ? scale_tiles * 512u : 0u;
         // weight scales of the first resident_k iterations are already in tensor memory when the tile before this one
@@ -540,7 +541,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               }
               if (PAIR) {
                 if (load_a) tma_load_4d_pair(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
-                if (load_b) tma_load_2d_pair(smem_b + s * kBBytes, &weight_map, bar, k0, n0 + static_cast<int>(rank) * (BN / 2));
+                if (load_b) tma_load_2d_pair(smem_b + s * kBBytes, &weight_map, bar, k0, n0 + static_cast<int>(rank) * (width / 2));
                 if (SCALED) {
                   // scale tiles through their tensor maps (128 words of 4 bytes per tile): only a tiled load can count
                   // on a barrier in the other CTA
@@ -961,11 +962,12 @@ struct Schedule {
 Schedule make_schedule(const FimConvGeometry& g, const Plan& pl, bool int8, bool per_pixel) {
   Schedule sc;
   sc.total_tiles = pl.total_tiles, sc.full_tiles = pl.total_tiles, sc.resident_k = 0, sc.n_major = 0;
-  if (pl.block_n == 256 && !pl.pair && pl.total_tiles > pl.ctas) {
+  const int walkers = pl.pair ? pl.ctas / 2 : pl.ctas;  // a CTA pair walks the tile list as one
+  if (pl.block_n == 256 && (!pl.pair || int8) && pl.total_tiles > walkers) {
     // the last round of the persistent CTAs: when at most half of them would have a tile, two half-width tiles each
-    // finish it in half the time
-    const int rest = pl.total_tiles % pl.ctas;
-    if (rest > 0 && 2 * rest <= pl.ctas && !(g_debug_flags & 16)) {
+    // finish it in half the time (block-scaled CTA pairs keep whole tiles: their scale tiles are laid out for 256 columns)
+    const int rest = pl.total_tiles % walkers;
+    if (rest > 0 && 2 * rest <= walkers && !(g_debug_flags & 16)) {
       sc.full_tiles = pl.total_tiles - rest;
       sc.total_tiles = sc.full_tiles + 2 * rest;
     }

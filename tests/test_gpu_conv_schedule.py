@@ -174,3 +174,27 @@ def test_mxfp8_pairs_many_tiles_per_pair_agree_with_single_ctas(ops, max_ctas):
         want = fast(*xd, *geometry)
     assert same_bytes(got, want)
     assert rel_l2(got, oracle.mxfp8_conv2d(x, ce, wq, we, bias, *geometry)) < 1e-3
+
+
+def test_int8_pairs_half_width_tail_round(ops):
+    """CTA pairs also finish a sparse last round as half-width tiles (BASELINE config 2 has 80 pair tiles for 74 pairs):
+    the schedule says so and the sums stay exact."""
+    b, h, w = 3, 24, 20
+    g = torch.Generator().manual_seed(8)
+    x = torch.randint(-127, 128, (b, h, w, 128), dtype=torch.int8, generator=g)
+    weight = torch.randint(-127, 128, (512, 9 * 128), dtype=torch.int8, generator=g)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    with conv_schedule(0, 10) as capped:
+        plan = capped.schedule((b, h, w, 128, 512, 3, 3, 1, 1), int8=True)
+        assert plan["pairs"] == 1 and plan["split_tiles"] > plan["tiles"] > plan["full_tiles"], plan
+        acc = ops.int8_conv2d_accumulators.get("sm100")(*to_dev(x, weight), *geometry)
+    assert torch.equal(acc.cpu(), oracle.int8_conv2d_accumulators_ext(x, weight, *geometry))
+    with conv_schedule(0, 10, 16) as whole:
+        plan = whole.schedule((b, h, w, 128, 512, 3, 3, 1, 1), int8=True)
+        assert plan["split_tiles"] == plan["tiles"]
+    config2 = conv_schedule().__enter__()
+    try:
+        plan = config2.schedule((2, 100, 100, 256, 256, 3, 3, 1, 1), int8=True)
+        assert plan["pairs"] == 1 and plan["tiles"] == 80 and plan["split_tiles"] == 86, plan  # 74 whole tiles + 6 split in two
+    finally:
+        config2.__exit__()
