@@ -80,6 +80,7 @@ struct ConvParams {
   const float* out_scale;
   int* status;
   uint32_t poll_backoff_ns;  // sleep between polls of the epilogue's wait for an accumulator
+  int warp_panels;           // flat 1x1 convs: every epilogue warp stages and stores its own 32 rows (no barrier between warps)
   int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
 
@@ -382,7 +383,7 @@ template <int FMT, int BN, int BK, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
-            const __grid_constant__ CUtensorMap sfa_map, const ConvParams p) {
+            const __grid_constant__ CUtensorMap sfa_map, const __grid_constant__ CUtensorMap out_warp_map, const ConvParams p) {
   static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
   constexpr bool INT8 = FMT == kFmtI8;
   constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
@@ -438,6 +439,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     tma_prefetch_desc(&act_map);
     tma_prefetch_desc(&weight_map);
     tma_prefetch_desc(&out_map);
+    if (p.warp_panels) tma_prefetch_desc(&out_warp_map);
   }
   if (warp == 1) {
     if (PAIR) {
@@ -713,6 +715,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
     const uint32_t panels = smem_out + group * p.panels_per_half * panel_bytes;
+    // A flat 1x1 conv (a tile = 128 consecutive rows of the pixel matrix) lets every warp stage and store its own 32 rows:
+    // the four warps of a group then never wait for each other. The panels take the same shared memory either way.
+    const bool own = p.warp_panels != 0;
+    const uint32_t own_bytes = 1024u * p.out_elem;
+    const uint32_t own_panels = smem_out + static_cast<uint32_t>(warp - 2) * p.panels_per_half * own_bytes;
     const bool store = !(probe_flags(p) & 4);
     constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
@@ -743,42 +750,61 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       // microseconds) and publishes whether it arrived; the four warps then take the same decision, so none of them can
       // be left alone at a named barrier below when a wait runs out. The word alternates with the tile parity: the
       // deciding warp cannot be two tiles ahead of a sibling, which it meets at this barrier every tile.
-      volatile int* go = &ctl.group_go[group][tile_it & 1u];
-      if (quarter == 0) {
-        const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.poll_backoff_ns);
-        if (lane == 0) *go = arrived ? 1 : 0;
-        __syncwarp();
+      if (own) {
+        // no barrier joins the warps below, so each waits for itself
+        if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+      } else {
+        volatile int* go = &ctl.group_go[group][tile_it & 1u];
+        if (quarter == 0) {
+          const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.poll_backoff_ns);
+          if (lane == 0) *go = arrived ? 1 : 0;
+          __syncwarp();
+        }
+        named_barrier(bar_id, 128);
+        if (*go == 0) break;
+        mbar_try_addr(tfull0 + 8 * acc, acc_phase);  // the phase is complete: this observes it for this warp too
       }
-      named_barrier(bar_id, 128);
-      if (*go == 0) break;
-      mbar_try_addr(tfull0 + 8 * acc, acc_phase);  // the phase is complete: this observes it for this warp too
       tc_fence_after();
       const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
       // Drain: every chunk of this warp is read, biased and rounded to bf16x2 words first (16 registers per chunk), and
       // the accumulator goes back to the MMA warp right after the last read; the long arithmetic follows. Four-byte
       // outputs cannot be held that compactly: their chunks are finished one by one.
       const bool wide = p.out_elem == 4;
-      auto take_panel = [&]() -> uint32_t {  // a free output panel of this group
-        const uint32_t panel = panels + (chunk_it & (p.panels_per_half - 1)) * panel_bytes;
+      auto take_panel = [&]() -> uint32_t {  // a free output panel of this group (of this warp: `own`)
+        const uint32_t slot = chunk_it & (p.panels_per_half - 1);
+        const uint32_t panel = own ? own_panels + slot * own_bytes : panels + slot * panel_bytes;
         ++chunk_it;
-        if (leader) {  // the store that last read this panel has finished with it
+        if (own ? lane == 0 : leader) {  // the store that last read this panel has finished with it
           if (p.panels_per_half == 2) {
             bulk_wait_read<1>();
           } else {
             bulk_wait_read<0>();
           }
         }
-        named_barrier(bar_id, 128);
+        if (own) {
+          __syncwarp();
+        } else {
+          named_barrier(bar_id, 128);
+        }
         return panel;
       };
       auto send_panel = [&](uint32_t panel, int n) {
         fence_async_proxy();
+        if (own) {
+          __syncwarp();
+          if (lane == 0 && store) {
+            tma_store_4d(&out_warp_map, panel, n * p.out_elem, x0 + quarter * 32, y0, b);
+            bulk_commit();
+          }
+          return;
+        }
         named_barrier(bar_id, 128);
         if (leader && store) {
           tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
           bulk_commit();
         }
       };
+      const int panel_row = own ? lane : row;
       auto release_accumulator = [&]() {
         tc_fence_before();
         __syncwarp();
@@ -801,7 +827,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           if (n >= n_end) continue;  // uniform over the four warps of this group
           wide_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, w);
           const uint32_t panel = take_panel();
-          stage_row<32>(panel, row, p.out_elem, w);
+          stage_row<32>(panel, panel_row, p.out_elem, w);
           send_panel(panel, n);
         }
       } else {
@@ -822,12 +848,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           uint32_t w[16];
           finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, smem_gelu, w);
           const uint32_t panel = take_panel();
-          stage_row<16>(panel, row, p.out_elem, w);
+          stage_row<16>(panel, panel_row, p.out_elem, w);
           send_panel(panel, n);
         }
       }
     }
-    if (leader) bulk_wait_read<0>();
+    if (own ? lane == 0 : leader) bulk_wait_read<0>();
     }
   }
 
@@ -992,7 +1018,7 @@ Schedule make_schedule(const FimConvGeometry& g, const Plan& pl, bool int8, bool
 }
 
 struct ConvMaps {
-  CUtensorMap act, weight, out, sfb, sfa;
+  CUtensorMap act, weight, out, sfb, sfa, out_warp;
 };
 
 template <int FMT, int BN, int BK, bool PAIR>
@@ -1018,9 +1044,9 @@ int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaS
     config.attrs = &attribute;
     config.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR>, maps.act, maps.weight, maps.out, maps.sfb,
-                                               maps.sfa, p));
+                                               maps.sfa, maps.out_warp, p));
   }
-  conv_kernel<FMT, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, p);
+  conv_kernel<FMT, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, maps.out_warp, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1164,6 +1190,15 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
     const uint32_t box[4] = {static_cast<uint32_t>(32 * out_elem), static_cast<uint32_t>(pl.tile_w), static_cast<uint32_t>(pl.tile_h), 1};
     const int rcm = make_tensor_map(&out_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, out, dims, strides, box, swizzle_for_bytes(32 * out_elem));
     if (rcm != kOk) return rcm;
+    maps.out_warp = out_map;
+    p.warp_panels = 0;
+    if (pl.flat && !(g_debug_flags & 512)) {  // one store per warp: 32 rows of the pixel matrix x 32 channels
+      const uint32_t warp_box[4] = {static_cast<uint32_t>(32 * out_elem), 32, 1, 1};
+      const int rcw = make_tensor_map(&maps.out_warp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, out, dims, strides, warp_box,
+                                      swizzle_for_bytes(32 * out_elem));
+      if (rcw != kOk) return rcw;
+      p.warp_panels = 1;
+    }
   }
 
   // scale tiles as tensors of 128 four-byte words per 512-byte tile: the loads of a CTA pair go through these
