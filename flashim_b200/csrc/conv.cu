@@ -119,21 +119,26 @@ __device__ __forceinline__ uint32_t idesc_i8(int block_n, int block_m = kTileM) 
 }
 
 #include "gelu_table.inc"
+constexpr uint32_t kGeluSmemBytes = (kGeluEntries * 4u + 1023u) / 1024u * 1024u;  // keeps the tiles behind it 1024-byte aligned
 
 // GELU of two bf16 values in one word, as bf16: the erf form torch evaluates (x * 0.5 * (1 + erf(x / sqrt 2)) in fp32,
-// rounded to bf16), looked up instead of computed. `table` is the shared-memory copy of kGeluTable: per magnitude a
+// rounded to bf16), looked up instead of computed. `table2` holds the shared-memory address of the copy of kGeluTable in
+// both halves: per magnitude a
 // 16-bit delta for either sign; result magnitude = max(a + delta, 0), result sign = input sign. Magnitudes below
 // kGeluBase share entry 0 (half the value: the exponent drops by one; zero stays zero), those above the table share the
 // last entry (x itself for positive values, -0 for negative ones). Exact for every bf16 input except subnormals, which
-// become zero. Thirteen integer instructions per pair and no MUFU; the arithmetic form costs about forty.
-__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, uint32_t table) {
+// become zero. Eleven instructions per pair and no MUFU; the arithmetic form costs about forty.
+__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, uint32_t table2) {
   constexpr uint32_t kNegBase = ((0x10000u - static_cast<uint32_t>(kGeluBase - 1)) & 0xFFFFu) * 0x00010001u;
   constexpr uint32_t kLast = static_cast<uint32_t>(kGeluEntries - 1) * 0x00010001u;
   const uint32_t a = r & 0x7FFF7FFFu;
   const uint32_t t = __viaddmin_s16x2_relu(a, kNegBase, kLast);  // clamp(a - (base - 1), 0, entries - 1) in each half
+  // both entry addresses with one multiply-add: the table sits in the first 64 KB of the shared window, so an address
+  // fits a half and neither half carries into the other
+  const uint32_t at = t * 4u + table2;
   uint32_t w0, w1, negative;
-  asm("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(table + ((t & 0xFFFFu) << 2)));
-  asm("ld.shared.b32 %0, [%1];" : "=r"(w1) : "r"(table + ((t >> 16) << 2)));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(at & 0xFFFFu));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w1) : "r"(at >> 16));
   // byte 0 of `negative` = 0xFF when the low value is negative, byte 1 the same for the high value (sign replication of
   // bytes 1 and 3); each byte steers two selector nibbles: bytes 2-3 of w0 / w1 (the delta for negative values) or 0-1
   asm("prmt.b32 %0, %1, %2, 0x00B9;" : "=r"(negative) : "r"(r), "r"(0u));
@@ -157,36 +162,23 @@ __device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_
   asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(bias_at + i * 16));
 }
 
-// bf16x2 words r[16] -> E4M3 codes of value * 2**-e, four per output word. The scaling is one mixed-precision FMA per
-// value (fp32 = bf16 * bf16 + -0, exact: a bf16 times a power of two; the addend -0 keeps the sign of a zero product),
-// which reads the halves of the packed word directly
-// and runs at the full fp32 rate; unpacking with shifts and masks first costs two half-rate integer instructions per pair.
+// bf16x2 words r[16] -> E4M3 codes of value * 2**-e (e in [-127, 127]), four per output word. The scaling is one
+// mixed-precision FMA per value (fp32 = bf16 * bf16 + -0, exact: a bf16 times a power of two; the addend -0 keeps the
+// sign of a zero product), which reads the halves of the packed word directly and runs at the full fp32 rate; unpacking
+// with shifts and masks first costs two half-rate integer instructions per pair.
 __device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[16]) {
-  // 2**-e as bf16 bits in both halves; 2**127 and 2**-127 (e = -127, 127) do not fit the bf16 exponent range exactly:
-  // those blocks (all-zero, or beyond 448 * 2**126) take the fp32 path
-  if (e > -127 && e < 127) {
-    const uint32_t inv16 = static_cast<uint32_t>(127 - e) << 7;
-    const uint32_t inv = inv16 | (inv16 << 16);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float a, b, c, d;
-      asm("{\n\t.reg .b16 xl, xh, yl, yh, s, t;\n\t"
-          "mov.b32 {xl, xh}, %4;\n\tmov.b32 {yl, yh}, %5;\n\tmov.b32 {s, t}, %6;\n\t"
-          "fma.rn.f32.bf16 %0, xl, s, 0f80000000;\n\tfma.rn.f32.bf16 %1, xh, s, 0f80000000;\n\t"
-          "fma.rn.f32.bf16 %2, yl, s, 0f80000000;\n\tfma.rn.f32.bf16 %3, yh, s, 0f80000000;\n\t}"
-          : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
-          : "r"(r[2 * i]), "r"(r[2 * i + 1]), "r"(inv));
-      w[i] = e4m3x4(a, b, c, d);
-    }
-    return;
-  }
-  const float inv = exp2_int(-e);
-  const uint64_t inv2 = pack2(inv, inv);
+  // 2**-e as bf16 bits in both halves; 2**-127 (e = 127) is a bf16 subnormal, which the instruction takes as it is
+  const uint32_t inv16 = e == 127 ? 0x0040u : static_cast<uint32_t>(127 - e) << 7;
+  const uint32_t inv = inv16 * 0x00010001u;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float a, b, c, d;
-    unpack2(mul2(bf16x2_to_f32x2(r[2 * i]), inv2), a, b);
-    unpack2(mul2(bf16x2_to_f32x2(r[2 * i + 1]), inv2), c, d);
+    asm("{\n\t.reg .b16 xl, xh, yl, yh, s, t;\n\t"
+        "mov.b32 {xl, xh}, %4;\n\tmov.b32 {yl, yh}, %5;\n\tmov.b32 {s, t}, %6;\n\t"
+        "fma.rn.f32.bf16 %0, xl, s, 0f80000000;\n\tfma.rn.f32.bf16 %1, xh, s, 0f80000000;\n\t"
+        "fma.rn.f32.bf16 %2, yl, s, 0f80000000;\n\tfma.rn.f32.bf16 %3, yh, s, 0f80000000;\n\t}"
+        : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+        : "r"(r[2 * i]), "r"(r[2 * i + 1]), "r"(inv));
     w[i] = e4m3x4(a, b, c, d);
   }
 }
@@ -406,17 +398,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   __shared__ __align__(8) SharedControl ctl;
 
   // dynamic shared memory, 1024-byte aligned:
-  // [stages x A][stages x B][output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles][bias]
+  // [GELU table][stages x A][stages x B][output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles][bias]
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t panel_bytes = 4096u * p.out_elem;
-  const uint32_t smem_a = base;
+  const uint32_t smem_gelu = base;  // kGeluTable first, when the epilogue applies GELU: its addresses must fit 16 bits
+  const uint32_t smem_a = base + (p.act == kActGelu ? kGeluSmemBytes : 0u);
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + p.stages * kBBytes;
   const uint32_t smem_sfb = smem_out + kEpiGroups * p.panels_per_half * panel_bytes;
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
-  const uint32_t smem_gelu = smem_bias + p.tiles_n * BN * 4;                 // kGeluTable, when the epilogue applies GELU
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dynamic_a = SCALED && p.act_scales != nullptr;
@@ -846,7 +838,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const int n = n0 + group * kGroupColumns + g * 32;
           if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
-          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, smem_gelu, w);
+          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, smem_gelu * 0x00010001u, w);
           const uint32_t panel = take_panel();
           stage_row<16>(panel, panel_row, p.out_elem, w);
           send_panel(panel, n);
@@ -918,7 +910,11 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   pl.block_k = g.cin % 128 == 0 ? 128 : (g.cin % 64 == 0 ? 64 : 32);
   // Output-channel tile: 256 halves the activation re-reads of a wide layer; narrower layers keep two accumulators in
   // tensor memory so the epilogue overlaps the next tile.
-  int bn = g.cout <= 64 ? 64 : (g.cout % 256 == 0 && g.kh * g.kw * g.cin >= 1024 ? 256 : 128);
+  // A block-scaled 1x1 layer that writes at least as much as it reads is bound by its epilogue: the wide tile halves the
+  // per-tile work of the epilogue warps (measured 5 to 16 % faster at 256 and 512 input channels); one that reads more
+  // than it writes keeps the narrow tile, whose smaller stages hold more activation bytes in flight.
+  const bool wide_pointwise = fmt == kFmtMx && pointwise && allow_flat && g.cout >= g.cin;
+  int bn = g.cout <= 64 ? 64 : (g.cout % 256 == 0 && (g.kh * g.kw * g.cin >= 1024 || wide_pointwise) ? 256 : 128);
   if (g_forced_block_n == 256 && g.cout > 128) bn = 256;
   if (g_forced_block_n == 128 && g.cout > 64) bn = 128;
   if (g_forced_block_n == 64) bn = 64;
@@ -965,7 +961,7 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
   const int epilogue_groups = bn >= 128 ? 4 : 2;
-  const int gelu_bytes = gelu ? (kGeluEntries * 4 + 15) / 16 * 16 : 0;
+  const int gelu_bytes = gelu ? static_cast<int>(kGeluSmemBytes) : 0;
   const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
