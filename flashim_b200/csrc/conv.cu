@@ -166,7 +166,8 @@ __device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_
 // mixed-precision FMA per value (fp32 = bf16 * bf16 + -0, exact: a bf16 times a power of two; the addend -0 keeps the
 // sign of a zero product), which reads the halves of the packed word directly and runs at the full fp32 rate; unpacking
 // with shifts and masks first costs two half-rate integer instructions per pair.
-__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[16]) {
+template <int WORDS>  // only the first eight words of `w` are written
+__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[WORDS]) {
   // 2**-e as bf16 bits in both halves; 2**-127 (e = 127) is a bf16 subnormal, which the instruction takes as it is
   const uint32_t inv16 = e == 127 ? 0x0040u : static_cast<uint32_t>(127 - e) << 7;
   const uint32_t inv = inv16 * 0x00010001u;
@@ -371,12 +372,19 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
 // of K, so a BF16 layer is a conv over 2 * Cin "channels" of one byte without scales).
 constexpr int kFmtMx = 0, kFmtI8 = 1, kFmtBf16 = 2;
 
-template <int FMT, int BN, int BK, bool PAIR>
+// EPI: 0 = the general epilogue, every switch read from ConvParams at run time. Otherwise kEpiLean plus the switches of a
+// flat block-scaled 1x1 layer fixed at compile time (bias present; bf16 output, or E4M3 with per-pixel scales when
+// kEpiDynamic; GELU when kEpiGelu; a dense bf16 residual covering every output channel when kEpiResidual): the layers a
+// refiner block is made of, whose time is the instruction count of this epilogue.
+constexpr int kEpiGelu = 1, kEpiDynamic = 2, kEpiResidual = 4, kEpiLean = 8;
+
+template <int FMT, int BN, int BK, bool PAIR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
             const __grid_constant__ CUtensorMap sfa_map, const __grid_constant__ CUtensorMap out_warp_map, const ConvParams p) {
   static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
+  static_assert(EPI == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the fixed epilogues serve flat block-scaled layers");
   constexpr bool INT8 = FMT == kFmtI8;
   constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
   constexpr int kAccStages = acc_stages(BN);
@@ -699,6 +707,128 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one column group of the tile =====
     const int quarter = warp & 3;
     const int group = (warp - 2) >> 2;
+    if constexpr (EPI != 0) {
+      // ----- fixed epilogue of a flat 1x1 layer: a tile is 128 consecutive rows of the pixel matrix, this warp owns 32 of
+      // them and kChunksPerWarp chunks of 32 channels, stages each chunk in two panels of its own and stores it itself
+      constexpr bool kGelu = (EPI & kEpiGelu) != 0, kDynamic = (EPI & kEpiDynamic) != 0, kResidual = (EPI & kEpiResidual) != 0;
+      constexpr uint32_t kElem = kDynamic ? 1u : 2u;            // bytes per output element
+      constexpr uint32_t kPitch = 32u * kElem, kSlots = kPitch >> 4;
+      constexpr uint32_t kPanelBytes = 32u * kPitch;
+      constexpr int kGroupColumns = BN / kEpiGroups;
+      const uint32_t my_panels = smem_out + static_cast<uint32_t>(warp - 2) * 2u * kPanelBytes;
+      // 16-byte slot i of this lane's row sits at row_at ^ (i << 4) (the swizzle a TMA store of kPitch-byte rows reads)
+      const uint32_t row_at = static_cast<uint32_t>(lane) * kPitch + ((((static_cast<uint32_t>(lane) * kPitch) >> 7) & (kSlots - 1)) << 4);
+      const uint32_t bias_at = smem_bias + static_cast<uint32_t>(group * kGroupColumns) * 4u;
+      const uint32_t lane_tmem = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + group * kGroupColumns;
+      const uint32_t gelu2 = smem_gelu * 0x00010001u;
+      const int row = quarter * 32 + lane;
+      const int scale_tiles = ((p.cout >> 5) + 3) >> 2;         // 4-group tiles per row tile of the output scales
+      const uint32_t scale_at = static_cast<uint32_t>(lane * 16 + quarter * 4);
+      const long long res_pitch = p.res_stride[2];
+      uint32_t tile_it = 0, chunk_it = 0;
+      for (int tile = worker; tile < p.total_tiles; tile += workers, ++tile_it) {
+        int m, n0, width;
+        decode_tile<BN>(p, tile, m, n0, width);
+        const int pixel = m * kTileM + row;  // the host keeps rows below 2**31
+        const bool valid = pixel < p.out_w;
+        const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
+        const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
+        const int column0 = group * kGroupColumns;  // first column of this warp inside the tile
+        const __nv_bfloat16* res_row = nullptr;
+        if (kResidual) {
+          res_row = p.residual + static_cast<long long>(pixel) * res_pitch + n0 + column0;
+          // ask for the line in L2 before the wait for the accumulator (a prefetch holds no registers)
+          if (valid && column0 < width) asm volatile("prefetch.global.L2 [%0];" ::"l"(res_row));
+        }
+        if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+        tc_fence_after();
+        uint32_t q[kChunksPerWarp][16];
+#pragma unroll
+        for (int g = 0; g < kChunksPerWarp; ++g) {
+          uint32_t raw[32];
+          tmem_load_32(lane_tmem + acc * BN + g * 32, raw);
+          tmem_load_wait();
+          if (g + 1 == kChunksPerWarp) {  // the accumulator goes back to the MMA warp before the long arithmetic
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_addr(tempty0 + 8 * acc);
+          }
+          if (column0 + g * 32 >= width) continue;  // a half-width tile of a split last round: nothing behind this chunk
+          const uint32_t bias_chunk = bias_at + static_cast<uint32_t>(n0 + g * 32) * 4u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint64_t b0, b1;
+            load_bias_pairs(bias_chunk, i, b0, b1);
+            float v0, v1, v2, v3;
+            unpack2(add2(pack2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1])), b0), v0, v1);
+            unpack2(add2(pack2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3])), b1), v2, v3);
+            q[g][2 * i] = pack_bf16(v0, v1);
+            q[g][2 * i + 1] = pack_bf16(v2, v3);
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < kChunksPerWarp; ++g) {
+          if (column0 + g * 32 >= width) continue;
+          uint32_t(&r)[16] = q[g];
+          if (kGelu) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = gelu_bf16x2(r[i], gelu2);
+          }
+          if (kResidual) {
+            if (valid) {
+              const uint4* r4 = reinterpret_cast<const uint4*>(res_row + g * 32);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint4 v = __ldg(r4 + i);
+                r[4 * i] = bf16x2_add(r[4 * i], v.x);
+                r[4 * i + 1] = bf16x2_add(r[4 * i + 1], v.y);
+                r[4 * i + 2] = bf16x2_add(r[4 * i + 2], v.z);
+                r[4 * i + 3] = bf16x2_add(r[4 * i + 3], v.w);
+              }
+            }
+          }
+          const uint32_t panel = my_panels + (chunk_it & 1u) * kPanelBytes;
+          ++chunk_it;
+          const uint32_t at = panel + row_at;
+          if (kDynamic) {
+            uint32_t mx[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx[i] = bf16x2_absmax(r[2 * i], r[2 * i + 1]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mx[i] = bf16x2_absmax(mx[2 * i], mx[2 * i + 1]);
+            mx[0] = bf16x2_absmax(bf16x2_absmax(mx[0], mx[1]), bf16x2_absmax(mx[2], mx[3]));
+            const uint32_t top = max(mx[0] & 0x7FFFu, (mx[0] >> 16) & 0x7FFFu);
+            const int e = e8m0_exponent_bits(top << 16);
+            if (valid) {
+              const int kg = (n0 + column0 + g * 32) >> 5;
+              p.out_scales[(static_cast<size_t>(m) * scale_tiles + (kg >> 2)) * 512 + scale_at + (kg & 3)] = static_cast<uint8_t>(e + 127);
+            }
+            uint32_t w[8];
+            scale_to_e4m3(r, e, w);
+            if (lane == 0) bulk_wait_read<1>();  // the store that last read this panel has finished with it
+            __syncwarp();
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at ^ 16u), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+          } else {
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at ^ (i << 4)), "r"(r[4 * i]), "r"(r[4 * i + 1]),
+                           "r"(r[4 * i + 2]), "r"(r[4 * i + 3])
+                           : "memory");
+            }
+          }
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&out_warp_map, panel, (n0 + column0 + g * 32) * static_cast<int>(kElem), m * kTileM + quarter * 32, 0, 0);
+            bulk_commit();
+          }
+        }
+      }
+      if (lane == 0) bulk_wait_read<0>();
+    } else
     if (group < kEpiGroups) {
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its group
     const uint32_t bar_id = 1 + group;
@@ -878,6 +1008,7 @@ struct Plan {
   int tiles_x, tiles_y, tiles_n, total_tiles;
   bool flat;
   bool pair;  // clusters of two CTAs driving one cta_group::2 instruction stream
+  int fixed_epilogue = 0;  // kEpiLean | switches when one of the compile-time epilogues serves this call, else 0
   int out_h, out_w;
   size_t smem;
 };
@@ -1017,14 +1148,14 @@ struct ConvMaps {
   CUtensorMap act, weight, out, sfb, sfa, out_warp;
 };
 
-template <int FMT, int BN, int BK, bool PAIR>
+template <int FMT, int BN, int BK, bool PAIR, int EPI = 0>
 int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
   // the shared-memory opt-in is a per-device attribute of the function: set once per device and instantiation
   static bool configured[kMaxDevices] = {};
   const int device = current_device();
   if (device < 0 || device >= kMaxDevices || !configured[device]) {
     const cudaError_t e =
-        cudaFuncSetAttribute(conv_kernel<FMT, BN, BK, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        cudaFuncSetAttribute(conv_kernel<FMT, BN, BK, PAIR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
@@ -1039,10 +1170,10 @@ int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaS
     attribute.val.clusterDim.x = 2, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR>, maps.act, maps.weight, maps.out, maps.sfb,
+    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR, EPI>, maps.act, maps.weight, maps.out, maps.sfb,
                                                maps.sfa, maps.out_warp, p));
   }
-  conv_kernel<FMT, BN, BK, PAIR><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, maps.out_warp, p);
+  conv_kernel<FMT, BN, BK, PAIR, EPI><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, maps.out_warp, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1053,6 +1184,17 @@ int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cud
       if (pl.block_k == 128) return launch_conv<FMT, BN, 128, true>(maps, p, pl, stream);
       if (pl.block_k == 64) return launch_conv<FMT, BN, 64, true>(maps, p, pl, stream);
       return launch_conv<FMT, BN, 32, true>(maps, p, pl, stream);
+    }
+  }
+  if constexpr (FMT == kFmtMx && BN >= 128) {
+    if (pl.block_k == 128) {  // the epilogues fixed at compile time: the three 1x1 layers of a refiner block
+      switch (pl.fixed_epilogue) {
+        case kEpiLean: return launch_conv<FMT, BN, 128, false, kEpiLean>(maps, p, pl, stream);
+        case kEpiLean | kEpiResidual: return launch_conv<FMT, BN, 128, false, kEpiLean | kEpiResidual>(maps, p, pl, stream);
+        case kEpiLean | kEpiGelu | kEpiDynamic:
+          return launch_conv<FMT, BN, 128, false, kEpiLean | kEpiGelu | kEpiDynamic>(maps, p, pl, stream);
+        default: break;
+      }
     }
   }
   if (pl.block_k == 128) return launch_conv<FMT, BN, 128, false>(maps, p, pl, stream);
@@ -1194,6 +1336,17 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
                                       swizzle_for_bytes(32 * out_elem));
       if (rcw != kOk) return rcw;
       p.warp_panels = 1;
+    }
+  }
+  if (fmt == kFmtMx && p.warp_panels && !pl.pair && pl.block_n >= 128 && pl.block_k == 128 && p.bias != nullptr &&
+      !(g_debug_flags & 1024)) {
+    const bool plain = p.act == kActNone && p.out_mode == FIM_OUT_BF16;
+    const bool res_ok = p.residual != nullptr && p.res_stride[3] == 1 && p.res_channels >= p.cout && p.res_stride[2] % 8 == 0 &&
+                        reinterpret_cast<uintptr_t>(p.residual) % 16 == 0;
+    if (plain && p.residual == nullptr) pl.fixed_epilogue = kEpiLean;
+    if (plain && res_ok) pl.fixed_epilogue = kEpiLean | kEpiResidual;
+    if (p.act == kActGelu && p.out_mode == FIM_OUT_E4M3_DYNAMIC && p.residual == nullptr) {
+      pl.fixed_epilogue = kEpiLean | kEpiGelu | kEpiDynamic;
     }
   }
 

@@ -16,7 +16,8 @@ extern "C" {
  * width, 64 disables CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; default for INT8 with
  * 256-wide tiles), 128 enables them for MXFP8 too, 256 reloads the weight scales for every tile instead of keeping the
  * first K iterations resident in tensor memory, 512 makes the four warps of an epilogue group of a 1x1 conv share one
- * output panel and one store (as the spatial convs do) instead of one per warp. A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
+ * output panel and one store (as the spatial convs do) instead of one per warp, 1024 sends the 1x1 layers of a refiner
+ * block through the general epilogue instead of the ones fixed at compile time. A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
  * bits 1, 2, 4, 8 (skip activation loads / weight loads / stores / scale copies), which make results invalid. */
 void fim_conv_tune(int block_n, int max_ctas, int flags);
 

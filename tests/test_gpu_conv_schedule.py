@@ -198,3 +198,38 @@ def test_int8_pairs_half_width_tail_round(ops):
         assert plan["pairs"] == 1 and plan["tiles"] == 80 and plan["split_tiles"] == 86, plan  # 74 whole tiles + 6 split in two
     finally:
         config2.__exit__()
+
+
+@pytest.mark.parametrize("max_ctas", [3, 11])
+@pytest.mark.parametrize("cin,cout", [(128, 256), (256, 256), (512, 256), (256, 128)])
+def test_fixed_epilogues_agree_with_the_general_one(ops, cin, cout, max_ctas):
+    """The three 1x1 layers of a refiner block (projection, up conv with GELU + dynamic requantisation, down conv with a
+    residual) run through epilogues fixed at compile time; tuning flag 1024 sends the same call through the general
+    epilogue, which must give the same bytes. With 11 CTAs the 24 tiles of the 256-wide cases end in a split round."""
+    b, h, w = 2, 37, 41
+    g = torch.Generator().manual_seed(16)
+    dense = torch.randn(b * h * w, cin, generator=g) * torch.exp2(torch.randint(-4, 4, (b * h * w, 1), generator=g).float())
+    q, e = oracle.quantize_rows_dynamic(dense)
+    wq = (torch.randn(cout, cin, generator=g) * 2).to(E4M3)
+    we = torch.randint(-9, -3, (cout, cin // 32), dtype=torch.int8, generator=g)
+    bias = torch.randn(cout, generator=g).to(BF16)
+    res = to_dev(torch.randn(b, h, w, cout, generator=g).to(BF16))
+    point = (1, 1, 1, 1, 0, 0, 1, 1)
+    fast = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(q.reshape(b, h, w, cin), oracle.swizzle_32_4_4(e), wq, oracle.swizzle_32_4_4(we), bias)
+
+    def three():
+        up_q, up_s = fast(*xd, *point, act="gelu", dynamic_out=True)
+        return fast(*xd, *point), fast(*xd, *point, residual=res), up_q, up_s
+
+    with conv_schedule(0, max_ctas) as capped:
+        plan = capped.schedule((b, h, w, cin, cout, 1, 1, 0, 1), per_pixel=True)
+        if max_ctas == 11 and cout == 256 and cout >= cin:  # 256-wide tiles: 24 of them, the last two split
+            assert plan["split_tiles"] > plan["tiles"]
+        fixed = three()
+    with conv_schedule(0, max_ctas, flags=1024):
+        general = three()
+    for a, b_ in zip(fixed, general):
+        assert same_bytes(a, b_)
+    want = oracle.mxfp8_conv2d_ext(q.reshape(b, h, w, cin), e, wq, we, bias, *point)
+    assert rel_l2(fixed[0], want) < 1e-3
