@@ -152,6 +152,37 @@ __device__ __forceinline__ uint32_t idesc_bf16(int block_n, int block_m = kTileM
          (static_cast<uint32_t>(block_m >> 4) << 24);
 }
 
+// What the epilogue does, as template argument EPI of the kernel. 0 = the general epilogue with every switch read from
+// ConvParams at run time. kEpiFixed = the same code with the switches below as compile-time constants (bias present, two
+// panels per group), which removes the tests, the parameter loads and the register moves at their joins: about a third
+// of the epilogue's instructions. kEpiLean = the shorter epilogue of a flat block-scaled 1x1 layer (bias present; bf16
+// output, or E4M3 with per-pixel scales when kEpiDynamic; GELU when kEpiGelu; a dense bf16 residual over every output
+// channel when kEpiResidual): the layers a refiner block is made of.
+constexpr int kEpiGelu = 1, kEpiDynamic = 2, kEpiResidual = 4, kEpiLean = 8, kEpiFixed = 16, kEpiStatic = 32;
+
+struct EpilogueSwitches {
+  int act, out_mode;
+  uint32_t out_elem, panels;  // bytes per output element; output panels per group
+  bool has_bias, has_residual;
+};
+template <int EPI>
+__device__ __forceinline__ EpilogueSwitches epilogue_switches(const ConvParams& p) {
+  EpilogueSwitches sw;
+  if constexpr ((EPI & kEpiFixed) != 0) {
+    sw.act = (EPI & kEpiGelu) ? kActGelu : kActNone;
+    sw.out_mode = (EPI & kEpiStatic) ? FIM_OUT_E4M3_STATIC : ((EPI & kEpiDynamic) ? FIM_OUT_E4M3_DYNAMIC : FIM_OUT_BF16);
+    sw.out_elem = sw.out_mode == FIM_OUT_BF16 ? 2u : 1u;
+    sw.panels = 2u;
+    sw.has_bias = true;
+    sw.has_residual = (EPI & kEpiResidual) != 0;
+  } else {
+    sw.act = p.act, sw.out_mode = p.out_mode;
+    sw.out_elem = static_cast<uint32_t>(p.out_elem), sw.panels = static_cast<uint32_t>(p.panels_per_half);
+    sw.has_bias = p.bias != nullptr, sw.has_residual = p.residual != nullptr;
+  }
+  return sw;
+}
+
 // ---- epilogue arithmetic on 32 consecutive output channels of one pixel ----------------------------------------------
 // Fills `w` with the output bytes of the chunk (32 * out_elem bytes, little end first). The block-scaled path works on
 // packed pairs throughout: fp32 pairs (one issue slot for two channels) up to the bf16 rounding, bf16x2 words after it
@@ -186,8 +217,8 @@ __device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, ui
 
 // fp32 value (+ INT8 dequantisation) + bias of one chunk, as 16 packed pairs
 template <bool INT8>
-__device__ __forceinline__ void biased_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
-                                             uint64_t (&v2)[16]) {
+__device__ __forceinline__ void biased_chunk(const ConvParams& p, const EpilogueSwitches& sw, const uint32_t (&raw)[32], int n,
+                                             uint32_t bias_at, float a_scale, uint64_t (&v2)[16]) {
   if (INT8) {
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
@@ -201,7 +232,7 @@ __device__ __forceinline__ void biased_chunk(const ConvParams& p, const uint32_t
 #pragma unroll
     for (int i = 0; i < 16; ++i) v2[i] = pack2(__uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
   }
-  if (p.bias != nullptr) {
+  if (sw.has_bias) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       uint64_t b0, b1;
@@ -214,15 +245,15 @@ __device__ __forceinline__ void biased_chunk(const ConvParams& p, const uint32_t
 
 // Four-byte outputs: the int32 accumulators as they are, or the biased fp32 values
 template <bool INT8>
-__device__ __forceinline__ void wide_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
-                                           uint32_t (&w)[32]) {
-  if (INT8 && p.out_mode == FIM_OUT_INT32) {
+__device__ __forceinline__ void wide_chunk(const ConvParams& p, const EpilogueSwitches& sw, const uint32_t (&raw)[32], int n,
+                                           uint32_t bias_at, float a_scale, uint32_t (&w)[32]) {
+  if (INT8 && sw.out_mode == FIM_OUT_INT32) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) w[i] = raw[i];
     return;
   }
   uint64_t v2[16];
-  biased_chunk<INT8>(p, raw, n, bias_at, a_scale, v2);
+  biased_chunk<INT8>(p, sw, raw, n, bias_at, a_scale, v2);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     float lo, hi;
@@ -234,10 +265,10 @@ __device__ __forceinline__ void wide_chunk(const ConvParams& p, const uint32_t (
 // First step of the other outputs: one bf16 rounding of the biased values, 16 bf16x2 words. This step is short, so the
 // accumulator can go back to the MMA warp before the long arithmetic starts.
 template <bool INT8>
-__device__ __forceinline__ void round_chunk(const ConvParams& p, const uint32_t (&raw)[32], int n, uint32_t bias_at, float a_scale,
-                                            uint32_t (&r)[16]) {
+__device__ __forceinline__ void round_chunk(const ConvParams& p, const EpilogueSwitches& sw, const uint32_t (&raw)[32], int n,
+                                            uint32_t bias_at, float a_scale, uint32_t (&r)[16]) {
   uint64_t v2[16];
-  biased_chunk<INT8>(p, raw, n, bias_at, a_scale, v2);
+  biased_chunk<INT8>(p, sw, raw, n, bias_at, a_scale, v2);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     float lo, hi;
@@ -249,13 +280,13 @@ __device__ __forceinline__ void round_chunk(const ConvParams& p, const uint32_t 
 // Second step, on the rounded values: activation (ReLU waits for the residual when there is one), residual, and the
 // output format.
 template <bool INT8>
-__device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[16], int n, size_t pixel, int b, int y, int x,
-                                             bool valid, uint32_t gelu_table, uint32_t (&w)[16]) {
-  const bool has_res = p.residual != nullptr;
-  if (p.act == kActGelu) {
+__device__ __forceinline__ void finish_chunk(const ConvParams& p, const EpilogueSwitches& sw, uint32_t (&r)[16], int n, size_t pixel,
+                                             int b, int y, int x, bool valid, uint32_t gelu_table, uint32_t (&w)[16]) {
+  const bool has_res = sw.has_residual;
+  if (sw.act == kActGelu) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) r[i] = gelu_bf16x2(r[i], gelu_table);
-  } else if (p.act == kActReluEarly || (p.act == kActRelu && !has_res)) {
+  } else if (sw.act == kActReluEarly || (sw.act == kActRelu && !has_res)) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) r[i] = bf16x2_max(r[i], 0u);
   }
@@ -283,12 +314,12 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[
         }
       }
     }
-    if (p.act == kActRelu) {
+    if (sw.act == kActRelu) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) r[i] = bf16x2_max(r[i], 0u);
     }
   }
-  if (p.out_mode == FIM_OUT_BF16) {
+  if (sw.out_mode == FIM_OUT_BF16) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) w[i] = r[i];
     return;
@@ -302,7 +333,7 @@ __device__ __forceinline__ void finish_chunk(const ConvParams& p, uint32_t (&r)[
     return;
   }
   int e;
-  if (p.out_mode == FIM_OUT_E4M3_STATIC) {
+  if (sw.out_mode == FIM_OUT_E4M3_STATIC) {
     e = static_cast<int>(__ldg(p.out_exponent + (n >> 5)));
   } else {
     // block maximum of |value| on bf16x2 words: max.xorsign.abs keeps the larger magnitude in both halves (signs are
@@ -372,19 +403,13 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
 // of K, so a BF16 layer is a conv over 2 * Cin "channels" of one byte without scales).
 constexpr int kFmtMx = 0, kFmtI8 = 1, kFmtBf16 = 2;
 
-// EPI: 0 = the general epilogue, every switch read from ConvParams at run time. Otherwise kEpiLean plus the switches of a
-// flat block-scaled 1x1 layer fixed at compile time (bias present; bf16 output, or E4M3 with per-pixel scales when
-// kEpiDynamic; GELU when kEpiGelu; a dense bf16 residual covering every output channel when kEpiResidual): the layers a
-// refiner block is made of, whose time is the instruction count of this epilogue.
-constexpr int kEpiGelu = 1, kEpiDynamic = 2, kEpiResidual = 4, kEpiLean = 8;
-
 template <int FMT, int BN, int BK, bool PAIR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
             const __grid_constant__ CUtensorMap sfa_map, const __grid_constant__ CUtensorMap out_warp_map, const ConvParams p) {
   static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
-  static_assert(EPI == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the fixed epilogues serve flat block-scaled layers");
+  static_assert((EPI & kEpiLean) == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the short epilogues serve flat block-scaled layers");
   constexpr bool INT8 = FMT == kFmtI8;
   constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
   constexpr int kAccStages = acc_stages(BN);
@@ -401,6 +426,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       sfa_column + 4u * static_cast<uint32_t>(SCALED && p.act_scales != nullptr ? p.stages : (p.cin + 127) / 128);
   constexpr int kEpiGroups = BN >= 128 ? 4 : 2;          // column groups of the epilogue, four warps (one per lane quarter) each
   constexpr int kChunksPerWarp = BN / (32 * kEpiGroups); // 32-column chunks each epilogue warp owns
+  // A 64-wide tile has two column groups; the other eight epilogue warps form a second set, and the sets drain alternate
+  // tiles (set s always meets accumulator stage s), so a narrow layer has all sixteen warps at work too.
+  constexpr int kTileSets = BN >= 128 ? 1 : 2;
+  static_assert(kTileSets == 1 || kAccStages == 2, "each set of epilogue warps needs an accumulator stage of its own");
+  constexpr int kPanelGroups = 4;                        // four-warp groups that own output panels
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) SharedControl ctl;
@@ -413,7 +443,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_a = base + (p.act == kActGelu ? kGeluSmemBytes : 0u);
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + p.stages * kBBytes;
-  const uint32_t smem_sfb = smem_out + kEpiGroups * p.panels_per_half * panel_bytes;
+  const uint32_t smem_sfb = smem_out + kPanelGroups * p.panels_per_half * panel_bytes;
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
@@ -707,8 +737,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one column group of the tile =====
     const int quarter = warp & 3;
     const int group = (warp - 2) >> 2;
-    if constexpr (EPI != 0) {
-      // ----- fixed epilogue of a flat 1x1 layer: a tile is 128 consecutive rows of the pixel matrix, this warp owns 32 of
+    if constexpr ((EPI & kEpiLean) != 0) {
+      // ----- short epilogue of a flat 1x1 layer: a tile is 128 consecutive rows of the pixel matrix, this warp owns 32 of
       // them and kChunksPerWarp chunks of 32 channels, stages each chunk in two panels of its own and stores it itself
       constexpr bool kGelu = (EPI & kEpiGelu) != 0, kDynamic = (EPI & kEpiDynamic) != 0, kResidual = (EPI & kEpiResidual) != 0;
       constexpr uint32_t kElem = kDynamic ? 1u : 2u;            // bytes per output element
@@ -829,23 +859,28 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       }
       if (lane == 0) bulk_wait_read<0>();
     } else
-    if (group < kEpiGroups) {
+    if (group < kEpiGroups * kTileSets) {
+    const int cgroup = group & (kEpiGroups - 1);  // column group inside the tile
+    const uint32_t tile_set = static_cast<uint32_t>(group / kEpiGroups);
+    const EpilogueSwitches sw = epilogue_switches<EPI>(p);
+    const uint32_t panel_bytes_ = 4096u * sw.out_elem;
     const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its group
     const uint32_t bar_id = 1 + group;
     const int row = quarter * 32 + lane;
     const int ry = row / p.tile_w, rx = row - ry * p.tile_w;
     const bool row_in_tile = row < p.tile_h * p.tile_w;
     const float a_scale = INT8 && p.a_scale != nullptr ? __ldg(p.a_scale) : 1.0f;
-    const uint32_t panels = smem_out + group * p.panels_per_half * panel_bytes;
+    const uint32_t panels = smem_out + group * sw.panels * panel_bytes_;
     // A flat 1x1 conv (a tile = 128 consecutive rows of the pixel matrix) lets every warp stage and store its own 32 rows:
     // the four warps of a group then never wait for each other. The panels take the same shared memory either way.
     const bool own = p.warp_panels != 0;
-    const uint32_t own_bytes = 1024u * p.out_elem;
-    const uint32_t own_panels = smem_out + static_cast<uint32_t>(warp - 2) * p.panels_per_half * own_bytes;
+    const uint32_t own_bytes = 1024u * sw.out_elem;
+    const uint32_t own_panels = smem_out + static_cast<uint32_t>(warp - 2) * sw.panels * own_bytes;
     const bool store = !(probe_flags(p) & 4);
     constexpr int kGroupColumns = BN / kEpiGroups;
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = worker; tile < p.total_tiles; tile += workers, ++tile_it) {
+      if (kTileSets == 2 && (tile_it & 1u) != tile_set) continue;  // the other set's tile
       int m, n0, width;
       decode_tile<BN>(p, tile, m, n0, width);
       if (PAIR) m = 2 * m + static_cast<int>(rank);
@@ -859,10 +894,10 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const size_t pixel = (static_cast<size_t>(b) * p.out_h + y) * p.out_w + x;
       const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
       const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
-      if (p.residual != nullptr && valid && p.res_stride[3] == 1) {
+      if (sw.has_residual && valid && p.res_stride[3] == 1) {
         // ask for this row's residual line in L2 before the wait for the accumulator, so that the loads in the epilogue
         // do not pay the DRAM latency (a prefetch holds no registers)
-        const int n_first = n0 + group * kGroupColumns;
+        const int n_first = n0 + cgroup * kGroupColumns;
         if (n_first < p.res_channels) {
           asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + b * p.res_stride[0] + y * p.res_stride[1] + x * p.res_stride[2] +
                                                           n_first));
@@ -870,13 +905,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       }
       // One warp of the group waits for the accumulator (sleeping between polls: the main loop of a tile takes
       // microseconds) and publishes whether it arrived; the four warps then take the same decision, so none of them can
-      // be left alone at a named barrier below when a wait runs out. The word alternates with the tile parity: the
+      // be left alone at a named barrier below when a wait runs out. The word alternates from one tile of the group to its next: the
       // deciding warp cannot be two tiles ahead of a sibling, which it meets at this barrier every tile.
       if (own) {
         // no barrier joins the warps below, so each waits for itself
         if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
       } else {
-        volatile int* go = &ctl.group_go[group][tile_it & 1u];
+        volatile int* go = &ctl.group_go[group][(tile_it >> (kTileSets - 1)) & 1u];
         if (quarter == 0) {
           const bool arrived = mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, false, p.poll_backoff_ns);
           if (lane == 0) *go = arrived ? 1 : 0;
@@ -887,17 +922,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         mbar_try_addr(tfull0 + 8 * acc, acc_phase);  // the phase is complete: this observes it for this warp too
       }
       tc_fence_after();
-      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + group * kGroupColumns;
+      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cgroup * kGroupColumns;
       // Drain: every chunk of this warp is read, biased and rounded to bf16x2 words first (16 registers per chunk), and
       // the accumulator goes back to the MMA warp right after the last read; the long arithmetic follows. Four-byte
       // outputs cannot be held that compactly: their chunks are finished one by one.
-      const bool wide = p.out_elem == 4;
+      const bool wide = sw.out_elem == 4;
       auto take_panel = [&]() -> uint32_t {  // a free output panel of this group (of this warp: `own`)
-        const uint32_t slot = chunk_it & (p.panels_per_half - 1);
-        const uint32_t panel = own ? own_panels + slot * own_bytes : panels + slot * panel_bytes;
+        const uint32_t slot = chunk_it & (sw.panels - 1);
+        const uint32_t panel = own ? own_panels + slot * own_bytes : panels + slot * panel_bytes_;
         ++chunk_it;
         if (own ? lane == 0 : leader) {  // the store that last read this panel has finished with it
-          if (p.panels_per_half == 2) {
+          if (sw.panels == 2) {
             bulk_wait_read<1>();
           } else {
             bulk_wait_read<0>();
@@ -915,14 +950,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         if (own) {
           __syncwarp();
           if (lane == 0 && store) {
-            tma_store_4d(&out_warp_map, panel, n * p.out_elem, x0 + quarter * 32, y0, b);
+            tma_store_4d(&out_warp_map, panel, n * static_cast<int>(sw.out_elem), x0 + quarter * 32, y0, b);
             bulk_commit();
           }
           return;
         }
         named_barrier(bar_id, 128);
         if (leader && store) {
-          tma_store_4d(&out_map, panel, n * p.out_elem, x0, y0, b);
+          tma_store_4d(&out_map, panel, n * static_cast<int>(sw.out_elem), x0, y0, b);
           bulk_commit();
         }
       };
@@ -941,36 +976,36 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       if (wide) {
 #pragma unroll
         for (int g = 0; g < kChunksPerWarp; ++g) {
-          const int n = n0 + group * kGroupColumns + g * 32;
+          const int n = n0 + cgroup * kGroupColumns + g * 32;
           uint32_t raw[32], w[32];
           tmem_load_32(lane_addr + g * 32, raw);
           tmem_load_wait();
           if (g + 1 == kChunksPerWarp) release_accumulator();
           if (n >= n_end) continue;  // uniform over the four warps of this group
-          wide_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, w);
+          wide_chunk<INT8>(p, sw, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, w);
           const uint32_t panel = take_panel();
-          stage_row<32>(panel, panel_row, p.out_elem, w);
+          stage_row<32>(panel, panel_row, sw.out_elem, w);
           send_panel(panel, n);
         }
       } else {
         uint32_t q[kChunksPerWarp][16];
 #pragma unroll
         for (int g = 0; g < kChunksPerWarp; ++g) {
-          const int n = n0 + group * kGroupColumns + g * 32;
+          const int n = n0 + cgroup * kGroupColumns + g * 32;
           uint32_t raw[32];
           tmem_load_32(lane_addr + g * 32, raw);
           tmem_load_wait();
           if (g + 1 == kChunksPerWarp) release_accumulator();
-          if (n < n_end) round_chunk<INT8>(p, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, q[g]);
+          if (n < n_end) round_chunk<INT8>(p, sw, raw, n, smem_bias + static_cast<uint32_t>(n) * 4u, a_scale, q[g]);
         }
 #pragma unroll
         for (int g = 0; g < kChunksPerWarp; ++g) {
-          const int n = n0 + group * kGroupColumns + g * 32;
+          const int n = n0 + cgroup * kGroupColumns + g * 32;
           if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
-          finish_chunk<INT8>(p, q[g], n, pixel, b, y, x, valid, smem_gelu * 0x00010001u, w);
+          finish_chunk<INT8>(p, sw, q[g], n, pixel, b, y, x, valid, smem_gelu * 0x00010001u, w);
           const uint32_t panel = take_panel();
-          stage_row<16>(panel, panel_row, p.out_elem, w);
+          stage_row<16>(panel, panel_row, sw.out_elem, w);
           send_panel(panel, n);
         }
       }
@@ -1091,7 +1126,7 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   const int stage_bytes = kTileM * pl.block_k + (pl.pair ? bn / 2 : bn) * pl.block_k + scale_tiles_b(bn) * 512 + 512;
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
-  const int epilogue_groups = bn >= 128 ? 4 : 2;
+  const int epilogue_groups = 4;  // four-warp groups with output panels of their own
   const int gelu_bytes = gelu ? static_cast<int>(kGeluSmemBytes) : 0;
   const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
@@ -1179,6 +1214,23 @@ int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaS
 
 template <int FMT, int BN>
 int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
+  // the general epilogue with its switches fixed at compile time, for the layers measured most: a block-scaled conv with
+  // bias, GELU and static requantisation at each tile width's usual K step, and the INT8 conv with bias and bf16 output
+  constexpr int kGeluStatic = kEpiFixed | kEpiGelu | kEpiStatic;
+  if constexpr (FMT == kFmtMx) {
+    if (pl.fixed_epilogue == kGeluStatic && !pl.pair) {
+      if constexpr (BN == 64) {
+        if (pl.block_k == 64) return launch_conv<FMT, BN, 64, false, kGeluStatic>(maps, p, pl, stream);
+      } else {
+        if (pl.block_k == 128) return launch_conv<FMT, BN, 128, false, kGeluStatic>(maps, p, pl, stream);
+      }
+    }
+  }
+  if constexpr (FMT == kFmtI8 && BN == 256) {
+    if (pl.fixed_epilogue == kEpiFixed && pl.pair && pl.block_k == 128) {
+      return launch_conv<FMT, BN, 128, true, kEpiFixed>(maps, p, pl, stream);
+    }
+  }
   if constexpr (BN == 256 && FMT != kFmtBf16) {
     if (pl.pair) {
       if (pl.block_k == 128) return launch_conv<FMT, BN, 128, true>(maps, p, pl, stream);
@@ -1348,6 +1400,10 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
     if (p.act == kActGelu && p.out_mode == FIM_OUT_E4M3_DYNAMIC && p.residual == nullptr) {
       pl.fixed_epilogue = kEpiLean | kEpiGelu | kEpiDynamic;
     }
+  }
+  if (pl.fixed_epilogue == 0 && p.bias != nullptr && p.residual == nullptr && pl.panels_per_half == 2 && !(g_debug_flags & 1024)) {
+    if (fmt == kFmtMx && p.act == kActGelu && p.out_mode == FIM_OUT_E4M3_STATIC) pl.fixed_epilogue = kEpiFixed | kEpiGelu | kEpiStatic;
+    if (fmt == kFmtI8 && p.act == kActNone && p.out_mode == FIM_OUT_BF16) pl.fixed_epilogue = kEpiFixed;
   }
 
   // scale tiles as tensors of 128 four-byte words per 512-byte tile: the loads of a CTA pair go through these

@@ -233,3 +233,43 @@ def test_fixed_epilogues_agree_with_the_general_one(ops, cin, cout, max_ctas):
         assert same_bytes(a, b_)
     want = oracle.mxfp8_conv2d_ext(q.reshape(b, h, w, cin), e, wq, we, bias, *point)
     assert rel_l2(fixed[0], want) < 1e-3
+
+
+@pytest.mark.parametrize("case", [(2, 24, 30, 64, 64, 3), (2, 24, 30, 128, 128, 3), (2, 24, 30, 256, 256, 3), (2, 24, 30, 64, 64, 1)],
+                         ids=lambda c: "c%d-%d_k%d" % c[3:])
+def test_gelu_static_epilogue_with_fixed_switches_agrees_with_the_general_one(ops, case):
+    """Bias + GELU + static requantisation, the epilogue of the conv shape sweep, runs with its switches fixed at compile
+    time for each tile width's usual K step (64-wide tiles with both sets of epilogue warps draining alternate tiles);
+    flag 1024 reads the switches at run time instead. Same bytes, and the oracle quantiser on the kernel's own bf16."""
+    b, h, w, cin, cout, k = case
+    x, ce, wq, we, bias = _mx_operands(b, h, w, cin, cout, k, seed=21)
+    geometry = (k, k, 1, 1, k // 2, k // 2, 1, 1)
+    fused = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(x, ce, wq, oracle.swizzle_32_4_4(we), bias)
+    with conv_schedule(0, 5):
+        dense = fused(*xd, *geometry, act="gelu")
+        oe = to_dev(oracle.static_block_exponent(dense.cpu().float()))
+        fixed = fused(*xd, *geometry, act="gelu", out_exponent=oe)
+    with conv_schedule(0, 5, flags=1024):
+        general = fused(*xd, *geometry, act="gelu", out_exponent=oe)
+    assert same_bytes(fixed, general)
+    assert same_bytes(fixed.cpu(), oracle.quantize_static_mx(dense.cpu(), oe.cpu()))
+    assert rel_l2(dense, oracle.mxfp8_conv2d_ext(x, ce, wq, we, bias, *geometry, act="gelu")) < 1e-3
+
+
+def test_int8_bias_epilogue_with_fixed_switches_agrees_with_the_general_one(ops):
+    b, h, w = 3, 24, 20
+    g = torch.Generator().manual_seed(8)
+    x = torch.randint(-127, 128, (b, h, w, 128), dtype=torch.int8, generator=g)
+    weight = torch.randint(-127, 128, (256, 9 * 128), dtype=torch.int8, generator=g)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    a_scale, w_scale = torch.tensor(0.02), torch.rand(256, generator=g) * 0.01 + 0.001
+    bias = torch.randn(256, generator=g).to(BF16)
+    args = to_dev(x, weight, a_scale, w_scale, bias)
+    with conv_schedule(0, 6) as capped:
+        assert capped.schedule((b, h, w, 128, 256, 3, 3, 1, 1), int8=True)["pairs"] == 1
+        fixed = ops.int8_conv2d.get("sm100")(*args, *geometry)
+    with conv_schedule(0, 6, flags=1024):
+        general = ops.int8_conv2d.get("sm100")(*args, *geometry)
+    assert same_bytes(fixed, general)
+    assert same_bytes(fixed.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry))
