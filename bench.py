@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload stack|conv|dw|int8] [--impl reference]
 
-Workloads (BASELINE.json configs; seeded synthetic inputs of the stated shapes and distributions):
+Workloads (seeded synthetic inputs of the stated shapes and distributions):
   stack  config 5: synthetic refiner stack, 64 image pairs (128 direction-images) over the 3-level bf16 pyramid,
          batch-sharded over the N GPUs with no communication; metric pairs/s ("strong" scaling: 64 pairs in total).
   conv   config 3, H=W=100 C=512->512 3x3, N=4: bf16 -> static MXFP8 quantise -> conv + bias + GELU + MXFP8 requant;
@@ -150,7 +150,7 @@ def _time_launches(fn, count: int) -> float:
 
 
 class ConvWorkload(Workload):
-    """BASELINE config 3 at its largest compute-bound shape: N=4, H=W=100, 512 -> 512, 3x3 pad 1."""
+    """The conv shape sweep at its largest compute-bound shape: N=4, H=W=100, 512 -> 512, 3x3 pad 1."""
 
     name, metric, unit, dtype = "mxfp8-conv-100x100x512-k3", "mxfp8_conv_tflops", "TFLOP/s", "fp8_e4m3"
     traffic_key = "conv_mxfp8_3x3_100x100x512"
@@ -233,7 +233,7 @@ class ConvWorkload(Workload):
 
 
 class Int8Workload(ConvWorkload):
-    """BASELINE config 2: INT8 [2,100,100,256] -> 256, 3x3 pad 1, bias, bf16 out."""
+    """The INT8 case: INT8 [2,100,100,256] -> 256, 3x3 pad 1, bias, bf16 out."""
 
     name, metric, unit, dtype = "int8-conv-100x100x256-k3", "int8_conv_tops", "TOP/s", "int8"
     traffic_key = "conv_int8_3x3_100x100x256"
@@ -303,7 +303,7 @@ class Int8Workload(ConvWorkload):
 
 
 class DepthwiseWorkload(Workload):
-    """BASELINE config 4: depthwise 5x5 + bias + GELU on bf16 [4,200,200,256] -> bf16."""
+    """The depthwise case: depthwise 5x5 + bias + GELU on bf16 [4,200,200,256] -> bf16."""
 
     name, metric, unit, dtype = "depthwise5x5-gelu-4x200x200x256", "depthwise_gbs", "GB/s", "f32"
     traffic_key = "depthwise_gelu_bf16_4x200x200x256"
@@ -378,7 +378,7 @@ class DepthwiseWorkload(Workload):
 
 
 class StackWorkload(Workload):
-    """BASELINE config 5: 64 pairs (128 direction-images) through the refiner stack, sharded by pairs over the ranks."""
+    """The refiner stack: 64 pairs (128 direction-images) through the refiner stack, sharded by pairs over the ranks."""
 
     name, metric, unit, dtype = "refiner-stack-64-pairs", "refiner_stack_pairs_per_s", "pairs/s", "fp8_e4m3"
     traffic_key = "depthwise_mxfp8_refiner_level_400x400x128"
@@ -539,7 +539,7 @@ def kernel_table(device, steps: int) -> list[dict]:
         rows.append(row)
 
     fused = ops.mxfp8_conv2d_fused.get("sm100")
-    # BASELINE config 3 (k = 3): E4M3 in -> conv + bias + GELU + static MXFP8 requantisation, N = 4
+    # the conv shape sweep (k = 3): E4M3 in -> conv + bias + GELU + static MXFP8 requantisation, N = 4
     for size, c in ((100, 512), (200, 256), (400, 128), (800, 64)):
         n, k = 4, 3
         nxt = rotate(lambda: randn(n, size, size, c, dtype=e4m3), n * size * size * c)
@@ -551,7 +551,7 @@ def kernel_table(device, steps: int) -> list[dict]:
             lambda: fused(nxt(), ce, w, ws, bias, k, k, 1, 1, 1, 1, 1, 1, act="gelu", out_exponent=oe),
             2.0 * n * size * size * c * c * k * k, n * size * size * c * 2 + k * k * c * c, "tensor" if c >= 128 else "hbm",
             "conv_mxfp8_3x3_100x100x512" if size == 100 else None)
-    # BASELINE config 2: INT8 3x3, scales + bias -> bf16
+    # the INT8 case: INT8 3x3, scales + bias -> bf16
     n, size, c, k = 2, 100, 256, 3
     nxt8 = rotate(lambda: torch.randint(-127, 128, (n, size, size, c), generator=g, device=device, dtype=torch.int8), n * size * size * c)
     w8 = torch.randint(-127, 128, (c, k * k * c), generator=g, device=device, dtype=torch.int8)
@@ -560,7 +560,7 @@ def kernel_table(device, steps: int) -> list[dict]:
     add("conv_kernel<int8> 3x3 + scales + bias", f"2x{size}x{size}x{c} -> {c}",
         lambda: ops.int8_conv2d.get("sm100")(nxt8(), w8, a_scale, w_scale, bias8, k, k, 1, 1, 1, 1, 1, 1),
         2.0 * n * size * size * c * c * k * k, n * size * size * c * 3 + k * k * c * c, "tensor", "conv_int8_3x3_100x100x256")
-    # BASELINE config 4: depthwise 5x5 + bias + GELU -> bf16
+    # the depthwise case: depthwise 5x5 + bias + GELU -> bf16
     n, size, c = 4, 200, 256
     nxtd = rotate(lambda: randn(n, size, size, c).permute(0, 3, 1, 2), n * size * size * c * 2)
     dw, db = randn(25, c, scale=0.05), randn(c, dtype=torch.float32)
@@ -725,7 +725,7 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-kernel-table", action="store_true", help="skip the per-kernel timings of the `kernels` entry")
     parser.add_argument("--pairs", type=int, default=StackWorkload.PAIRS,
-                        help="image pairs of the stack workload (BASELINE config 5 has 64; smaller values are for ncu captures)")
+                        help="image pairs of the stack workload (the benchmark has 64; smaller values are for ncu captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     StackWorkload.PAIRS = args.pairs

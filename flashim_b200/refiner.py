@@ -25,7 +25,7 @@ from flashim_b200.build import EAGER, BuildContext, EngineSpec, ModelSpec
 from flashim_b200.config import RunConfig
 from flashim_b200.quant.tensor import QuantizedWeight, padded_channels, swizzle_scales
 
-LEVELS = ((100, 512), (200, 256), (400, 128))  # (height = width, channels) of the feature pyramid in BASELINE config 5
+LEVELS = ((100, 512), (200, 256), (400, 128))  # (height = width, channels) of the benchmark's feature pyramid
 
 
 class PointwiseMX(nn.Module):

@@ -512,7 +512,7 @@ def depthwise5x5_act_mxfp8_ext(value, weight, bias, act="gelu") -> tuple[Tensor,
 
 
 # ---------------------------------------------------------------------------------------------------------------
-# synthetic refiner stack (BASELINE config 5); block structure after flashim/models/romav2/refiner.py:45-148 and
+# synthetic refiner stack (the benchmark's stack workload); block structure after flashim/models/romav2/refiner.py:45-148 and
 # flashim/quant/passes/separable_conv_block.py:69-110, widened to the C -> 2C -> C residual MLP the benchmark names.
 # ---------------------------------------------------------------------------------------------------------------
 

@@ -155,7 +155,7 @@ def depthwise() -> None:
 
 
 def modules() -> None:
-    """Weight packing of the quantised conv modules, and BASELINE config 1 end to end through the module."""
+    """Weight packing of the quantised conv modules, and the benchmark's CPU-runnable case ([1, 64, 64, 128], 128 -> 128 3x3) end to end through the module."""
     torch.manual_seed(0)
     x = torch.randn(1, 64, 64, 128)  # NHWC, config 1
     conv = torch.nn.Conv2d(128, 128, 3, 1, 1)

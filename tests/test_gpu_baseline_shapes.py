@@ -1,4 +1,4 @@
-"""The kernels at the full shapes the benchmark runs (BASELINE configs 3, 4 and 5) against the CPU oracle, and one
+"""The kernels at the full shapes the benchmark runs (the conv shape sweep, the depthwise case and the refiner stack) against the CPU oracle, and one
 launch per kernel family whose tensors hold more than 2**31 elements (64-bit offsets).
 
 Config 3: batch 4, (H = W, C) in (100, 512), (200, 256), (400, 128), (800, 64), 3x3 pad 1 and 1x1, bf16 input -> static

@@ -157,7 +157,7 @@ def test_per_pixel_scales_pointwise(ops, rows_shape, cin, cout):
 
 
 def test_baseline_config1(ops, golden):
-    """BASELINE config 1: fp32 NHWC [1, 64, 64, 128] from seed 0, 128 -> 128 3x3 pad 1, static MXFP8, fp32 / bf16 out."""
+    """The benchmark's CPU-runnable case: fp32 NHWC [1, 64, 64, 128] from seed 0, 128 -> 128 3x3 pad 1, static MXFP8, fp32 / bf16 out."""
     g = golden("modules")
     torch.manual_seed(0)
     x = torch.randn(1, 64, 64, 128)
@@ -253,7 +253,7 @@ def test_int8_conv2d_maxpool_golden(ops, golden):
 
 
 def test_baseline_config2(ops):
-    """BASELINE config 2: bf16 NHWC [2, 100, 100, 256] from seed 1, 256 -> 256 3x3 pad 1, int32 sums bit-exact, bf16 out."""
+    """The benchmark's INT8 case: bf16 NHWC [2, 100, 100, 256] from seed 1, 256 -> 256 3x3 pad 1, int32 sums bit-exact, bf16 out."""
     torch.manual_seed(1)
     x = torch.randn(2, 100, 100, 256).to(BF16)
     weight = torch.empty(256, 256, 3, 3)

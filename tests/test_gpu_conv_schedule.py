@@ -177,7 +177,7 @@ def test_mxfp8_pairs_many_tiles_per_pair_agree_with_single_ctas(ops, max_ctas):
 
 
 def test_int8_pairs_half_width_tail_round(ops):
-    """CTA pairs also finish a sparse last round as half-width tiles (BASELINE config 2 has 80 pair tiles for 74 pairs):
+    """CTA pairs also finish a sparse last round as half-width tiles (the benchmark's INT8 case has 79 pair tiles for 74 pairs):
     the schedule says so and the sums stay exact."""
     b, h, w = 3, 24, 20
     g = torch.Generator().manual_seed(8)

@@ -185,7 +185,7 @@ def test_module_packing_and_config1_against_reference(golden):
     assert torch.equal(w8, g("c1_int8_packed")) and torch.equal(s8, g("c1_int8_scale"))
     sq, se = oracle.pack_mx_conv_weight(g("small_weight"))
     assert same_bytes(sq, g("small_packed", E4M3)) and torch.equal(se, g("small_packed_exponent"))
-    # BASELINE config 1 regenerated from its seed: [1, 64, 64, 128] fp32 -> 128 -> 128 3x3, static MXFP8
+    # the benchmark's CPU-runnable case regenerated from its seed: [1, 64, 64, 128] fp32 -> 128 -> 128 3x3, static MXFP8
     torch.manual_seed(0)
     x = torch.randn(1, 64, 64, 128)
     assert torch.equal(x[0, :4, :4], g("c1_x_sample"))
