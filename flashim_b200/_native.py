@@ -74,6 +74,7 @@ SIGNATURES: dict[str, tuple] = {
     "fim_dw5x5_mxfp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
     "fim_dw5x5_relu_int8": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "fim_mxfp8_conv2d": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
+    "fim_mxfp8_conv2d_bf16": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_int8_conv2d": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_bf16_conv2d": (_I, [_P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_gelu_quantize_mxfp8": (_I, [_P, _P, _P, _P, _L, _I, _P]),

@@ -356,9 +356,14 @@ def mxfp8_conv2d_launch(
         out_scales = torch.empty(0, device=x.device, dtype=torch.uint8)
     geometry = _geometry(x, cout, kh, kw, sh, sw, ph, pw, dh, dw)
     epilogue = _epilogue(bias, residual, act, out_mode, out_exponent, out_scales if out_scales.numel() else None)
-    code = _native.library().fim_mxfp8_conv2d(
-        x.data_ptr(), _ptr(act_exponent), _ptr(act_scales), weight.data_ptr(), weight_scales.data_ptr(),
-        ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
+    if x.dtype == torch.bfloat16:  # the activation quantiser runs inside the kernel (1x1 layers, Cin % 128 == 0)
+        code = _native.library().fim_mxfp8_conv2d_bf16(
+            x.data_ptr(), _ptr(act_exponent), weight.data_ptr(), weight_scales.data_ptr(),
+            ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
+    else:
+        code = _native.library().fim_mxfp8_conv2d(
+            x.data_ptr(), _ptr(act_exponent), _ptr(act_scales), weight.data_ptr(), weight_scales.data_ptr(),
+            ctypes.byref(geometry), ctypes.byref(epilogue), out.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
     _finish(code, f"mxfp8_conv2d {tuple(x.shape)} -> {cout} k{kh}x{kw} s{sh}x{sw}", x.device)
     return out, out_scales
 
@@ -557,6 +562,33 @@ def register(ops=None, device_spec=None, feature=None) -> None:
             out, scales = mxfp8_conv2d_launch(
                 x, None if per_pixel else act_scale, act_scale if per_pixel else None, weight, weight_scales, bias, residual,
                 out_exponent, kh, kw, sh, sw, ph, pw, dh, dw, act_code[act], mode)
+            return (out, scales) if dynamic_out else out
+
+    def bf16_in_when(x, act_exponent, weight, weight_scales, bias, *, act="none", residual=None, out_exponent=None,
+                     dynamic_out=False, out_fp32=False):
+        return (
+            have() and _cuda(x, act_exponent, weight, weight_scales, bias, residual, out_exponent)
+            and x.dtype == torch.bfloat16 and x.ndim == 4 and x.is_contiguous() and x.shape[-1] % 128 == 0
+            and weight.dtype == E4M3 and weight.is_contiguous() and weight.shape[1] == x.shape[-1] and weight.shape[0] % BLOCK == 0
+            and weight_scales.dtype == torch.uint8
+            and weight_scales.numel() == swizzled_scale_bytes(weight.shape[0], weight.shape[1] // BLOCK)
+            and (act_exponent is None or (act_exponent.dtype == torch.int8 and tuple(act_exponent.shape) == (x.shape[-1] // 32,)))
+            and act in act_code and _residual_ok(residual, weight.shape[0])
+            and (out_exponent is None) + (not dynamic_out) + (not out_fp32) >= 2
+        )
+
+    if hasattr(ops, "mxfp8_conv2d_bf16"):
+        @ops.mxfp8_conv2d_bf16.register("sm100", device=spec, requires=requires, priority=3, when=bf16_in_when)
+        def mxfp8_conv2d_bf16(x, act_exponent, weight, weight_scales, bias, *, act="none", residual=None, out_exponent=None,
+                              dynamic_out=False, out_fp32=False):
+            if out_fp32:
+                mode = _native.OUT_F32
+            elif dynamic_out:
+                mode = _native.OUT_E4M3_DYNAMIC
+            else:
+                mode = _native.OUT_BF16 if out_exponent is None else _native.OUT_E4M3_STATIC
+            out, scales = mxfp8_conv2d_launch(x, act_exponent, None, weight, weight_scales, bias, residual, out_exponent,
+                                              1, 1, 1, 1, 0, 0, 1, 1, act_code[act], mode)
             return (out, scales) if dynamic_out else out
 
     def int8_when(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, residual=None,

@@ -24,6 +24,11 @@ namespace fim {
 namespace {
 
 constexpr int kThreads = 576;  // producer warp, MMA warp, 16 epilogue warps
+// A layer that takes bf16 activations adds four converter warps, which quantise each 128 x 128 tile on its way from the
+// TMA landing ring into the K-major stage the MMAs read.
+constexpr int kConverterWarps = 4, kConvertThreads = kThreads + 32 * kConverterWarps;
+constexpr int kRawStages = 2;                       // landing ring of bf16 tiles
+constexpr uint32_t kRawBytes = 128u * 128u * 2u;    // 128 pixels x 128 channels of bf16
 constexpr int kTileM = 128;
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kMaxStages = 12;  // a short K loop is bound by the latency of a stage's round trip: more stages in flight
@@ -80,6 +85,7 @@ struct ConvParams {
   const float* out_scale;
   int* status;
   uint32_t poll_backoff_ns;  // sleep between polls of the epilogue's wait for an accumulator
+  int convert_static;        // bf16 activations: 1 = quantise with act_exponent, 0 = per pixel and 32 channels on the fly
   int warp_panels;           // flat 1x1 convs: every epilogue warp stages and stores its own 32 rows (no barrier between warps)
   int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
@@ -96,6 +102,8 @@ struct SharedControl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t raw_full[kRawStages];   // bf16 landing ring of a converting layer
+  uint64_t raw_empty[kRawStages];
   uint32_t tmem_base;
   int abort_flag;
   int group_go[4][2];  // epilogue: did the accumulator of tile (parity) arrive? One decision per column group
@@ -403,12 +411,18 @@ __device__ __forceinline__ void decode_tile(const ConvParams& p, int tile, int& 
 // of K, so a BF16 layer is a conv over 2 * Cin "channels" of one byte without scales).
 constexpr int kFmtMx = 0, kFmtI8 = 1, kFmtBf16 = 2;
 
-template <int FMT, int BN, int BK, bool PAIR, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+// CONVERT: the activations arrive as bf16 rows of a flat 1x1 layer (through `act_map`, 128 x 128 boxes without swizzle) and
+// are quantised to E4M3 on chip — with the static exponents of `act_exponent`, or per pixel and 32 channels, in which case
+// the converter warps also write the stage's activation-scale tile — by exactly the arithmetic of the standalone
+// quantisers, so the result equals quantising first and convolving then, bit for bit.
+template <int FMT, int BN, int BK, bool PAIR, int EPI, bool CONVERT>
+__global__ void __launch_bounds__(CONVERT ? kConvertThreads : kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
             const __grid_constant__ CUtensorMap sfa_map, const __grid_constant__ CUtensorMap out_warp_map, const ConvParams p) {
   static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
+  static_assert(!CONVERT || (FMT == kFmtMx && !PAIR && BK == 128), "the converter feeds flat block-scaled layers");
+  constexpr int kBlockThreads = CONVERT ? kConvertThreads : kThreads;
   static_assert((EPI & kEpiLean) == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the short epilogues serve flat block-scaled layers");
   constexpr bool INT8 = FMT == kFmtI8;
   constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
@@ -423,7 +437,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   // then the resident weight scales (kSfbColumns per K iteration, kept while consecutive tiles share their channels)
   const uint32_t sfa_column = kSfbColumn + static_cast<uint32_t>(p.stages) * kSfbColumns;
   const uint32_t resident_column =
-      sfa_column + 4u * static_cast<uint32_t>(SCALED && p.act_scales != nullptr ? p.stages : (p.cin + 127) / 128);
+      sfa_column + 4u * static_cast<uint32_t>(SCALED && (CONVERT ? p.convert_static == 0 : p.act_scales != nullptr) ? p.stages : (p.cin + 127) / 128);
   constexpr int kEpiGroups = BN >= 128 ? 4 : 2;          // column groups of the epilogue, four warps (one per lane quarter) each
   constexpr int kChunksPerWarp = BN / (32 * kEpiGroups); // 32-column chunks each epilogue warp owns
   // A 64-wide tile has two column groups; the other eight epilogue warps form a second set, and the sets drain alternate
@@ -447,9 +461,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
+  const uint32_t smem_raw = (smem_bias + static_cast<uint32_t>(p.tiles_n * BN) * 4u + 1023u) & ~1023u;  // CONVERT: bf16 landing ring
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool dynamic_a = SCALED && p.act_scales != nullptr;
+  // per-pixel activation scales: read from HBM tiles, or written into the stage by the converter warps
+  const bool dynamic_a = SCALED && (CONVERT ? p.convert_static == 0 : p.act_scales != nullptr);
   const int taps = p.kh * p.kw;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                   // 0: the CTA that issues the MMAs
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);  // tile walker index
@@ -458,8 +474,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.full[s], CONVERT ? 1 + kConverterWarps : 1);  // the producer's bytes (+ the converter warps' tile)
       mbar_init(&ctl.empty[s], 1);
+    }
+    if (CONVERT) {
+      for (int s = 0; s < kRawStages; ++s) {
+        mbar_init(&ctl.raw_full[s], 1);
+        mbar_init(&ctl.raw_empty[s], kConverterWarps);
+      }
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl.tmem_full[s], 1);
@@ -497,13 +519,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   }
   if (p.bias != nullptr) {
     // the bias widened to fp32 once per CTA (zero for the columns a ragged last tile pads)
-    for (int i = threadIdx.x; i < p.tiles_n * BN; i += kThreads) {
+    for (int i = threadIdx.x; i < p.tiles_n * BN; i += kBlockThreads) {
       const float value = i < p.cout ? __bfloat162float(p.bias[i]) : 0.0f;
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias + i * 4), "f"(value) : "memory");
     }
   }
   if (p.act == kActGelu) {
-    for (int i = threadIdx.x; i < kGeluEntries; i += kThreads) {
+    for (int i = threadIdx.x; i < kGeluEntries; i += kBlockThreads) {
       asm volatile("st.shared.b32 [%0], %1;" ::"r"(smem_gelu + i * 4), "r"(kGeluTable[i]) : "memory");
     }
   }
@@ -514,6 +536,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t tmem = ctl.tmem_base;
   const uint32_t full0 = smem_u32(&ctl.full[0]), empty0 = smem_u32(&ctl.empty[0]);
   const uint32_t tfull0 = smem_u32(&ctl.tmem_full[0]), tempty0 = smem_u32(&ctl.tmem_empty[0]);
+  const uint32_t raw_full0 = smem_u32(&ctl.raw_full[0]), raw_empty0 = smem_u32(&ctl.raw_empty[0]);
   volatile int* abort_flag = &ctl.abort_flag;
 
   if (warp == 0) {
@@ -521,7 +544,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     if (lane == 0) {
       const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
       const bool load_a = !(probe_flags(p) & 1), load_b = !(probe_flags(p) & 2);
-      uint32_t s = 0, phase = 0;
+      uint32_t s = 0, phase = 0, raw_s = 0, raw_phase = 0;
       bool alive = true;
       int last_n0 = -1;
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers) {
@@ -538,8 +561,10 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const int scale_tiles = BN <= 128 ? 1 : width / 128;
         // a pair's barrier (in the leader) counts the bytes of both CTAs, which load the same amounts
         // (a pair's weight box always has BN / 2 rows: for a half-width tile only the first width / 2 of them are used)
-        const uint32_t operand_bytes = (load_a ? a_box_bytes : 0u) + (load_b ? (PAIR ? kBBytes : static_cast<uint32_t>(width) * BK) : 0u) +
-                                       (dynamic_a ? 512u : 0u);
+        // (a converting layer's activation tile and scale tile are written by the converter warps, not counted here)
+        const uint32_t operand_bytes = (load_a && !CONVERT ? a_box_bytes : 0u) +
+                                       (load_b ? (PAIR ? kBBytes : static_cast<uint32_t>(width) * BK) : 0u) +
+                                       (dynamic_a && !CONVERT ? 512u : 0u);
         const uint32_t sfb_bytes = SCALED ? scale_tiles * 512u : 0u;
         // weight scales of the first resident_k iterations are already in tensor memory when the tile before this one
         // had the same output channels
@@ -551,12 +576,22 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const int row_tile = min(n0 / 128 + i, p.weight_row_tiles - 1);
           sfb_src[i] = p.weight_scales + static_cast<size_t>(row_tile) * p.weight_scale_tiles * 512;
         }
-        const uint8_t* sfa_src = dynamic_a ? p.act_scales + static_cast<size_t>(m_tile) * p.act_scale_tiles * 512 : nullptr;
+        const uint8_t* sfa_src = dynamic_a && !CONVERT ? p.act_scales + static_cast<size_t>(m_tile) * p.act_scale_tiles * 512 : nullptr;
         int k0 = 0;  // offset along the weight's K axis
         for (int ky = 0; ky < p.kh && alive; ++ky) {
           for (int kx = 0; kx < p.kw && alive; ++kx) {
             const int cx = x0 + kx * p.dil_w, cy = y0 + ky * p.dil_h;
             for (int j = 0; j < p.k_chunks; ++j, k0 += BK) {
+              if (CONVERT) {
+                // the bf16 tile of this K step into the landing ring: 128 rows of the pixel matrix x 128 channels
+                if (!mbar_wait_addr(raw_empty0 + 8 * raw_s, raw_phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+                  alive = false;
+                  break;
+                }
+                mbar_expect_tx_addr(raw_full0 + 8 * raw_s, kRawBytes);
+                tma_load_4d_addr(smem_raw + raw_s * kRawBytes, &act_map, raw_full0 + 8 * raw_s, j * 128, m_tile * kTileM, 0, 0);
+                if (++raw_s == kRawStages) raw_s = 0, raw_phase ^= 1;
+              }
               if (!mbar_wait_addr(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
                 alive = false;
                 break;
@@ -592,7 +627,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
                 continue;
               }
-              if (load_a) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
+              if (load_a && !CONVERT) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
               if (load_b) {
 #pragma unroll
                 for (int part = 0; part < BN / kWeightBoxRows; ++part) {
@@ -609,7 +644,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                     bulk_load_addr(smem_sfb + (s * kScaleTilesB + i) * 512, sfb_src[i] + static_cast<size_t>(w_tile) * 512, 512, bar);
                   }
                 }
-                if (dynamic_a) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
+                if (dynamic_a && !CONVERT) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
               }
               if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
             }
@@ -733,6 +768,62 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
       }
     }
+  } else if (CONVERT && warp >= 2 + 16) {
+    // ===== converter: bf16 landing tile -> E4M3 K-major stage (+ the stage's activation-scale tile) =====
+    // 1024 pieces of 16 channels per tile, eight per thread: piece t = (row t / 8, channels 16 * (t % 8) ...); the two
+    // lanes of a 32-channel block are neighbours. A warp reads 1 KB of consecutive shared memory per step and writes four
+    // rows of the 128-byte-swizzled stage, both without bank conflicts.
+    const int ctid = static_cast<int>(threadIdx.x) - 32 * (2 + 16);
+    const int piece = ctid & 7, group = piece >> 1;
+    uint32_t s = 0, phase = 0, raw_s = 0, raw_phase = 0;
+    bool alive = true;
+    for (int tile = worker; tile < p.total_tiles && alive; tile += workers) {
+      for (int j = 0; j < p.k_chunks; ++j) {
+        if (!mbar_wait_addr(raw_full0 + 8 * raw_s, raw_phase, abort_flag, p.status, kStatusWaitFull) ||
+            !mbar_wait_addr(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+          alive = false;
+          break;
+        }
+        const uint32_t from = smem_raw + raw_s * kRawBytes, to = smem_a + s * kABytes, scale_tile = smem_sfa + s * 512;
+        const int static_e = p.convert_static ? static_cast<int>(__ldg(p.act_exponent + j * 4 + group)) : 0;
+#pragma unroll 2
+        for (int i = 0; i < 8; ++i) {
+          const int row = i * 16 + (ctid >> 3);
+          uint32_t w[8];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(from + row * 256 + piece * 32));
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(from + row * 256 + piece * 32 + 16));
+          float v[16];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[2 * k] = bf16_lo(w[k]), v[2 * k + 1] = bf16_hi(w[k]);
+          int e = static_e;
+          if (!p.convert_static) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) amax = fmaxf(amax, fabsf(v[k]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            e = e8m0_exponent(amax);
+            if ((piece & 1) == 0) {
+              asm volatile("st.shared.u8 [%0], %1;" ::"r"(scale_tile + (row & 31) * 16 + (row >> 5) * 4 + group), "r"(e + 127) : "memory");
+            }
+          }
+          const float inv = exp2_int(-e);
+          uint32_t q[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) q[k] = e4m3x4(v[4 * k] * inv, v[4 * k + 1] * inv, v[4 * k + 2] * inv, v[4 * k + 3] * inv);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(to + row * 128 + ((piece ^ (row & 7)) << 4)), "r"(q[0]), "r"(q[1]),
+                       "r"(q[2]), "r"(q[3])
+                       : "memory");
+        }
+        fence_async_proxy();  // the MMAs (and the scale copy) read these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_addr(full0 + 8 * s);
+          mbar_arrive_addr(raw_empty0 + 8 * raw_s);
+        }
+        if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
+        if (++raw_s == kRawStages) raw_s = 0, raw_phase ^= 1;
+      }
+    }
   } else {
     // ===== epilogue: warp w owns tensor-memory lanes 32 * (w % 4) ... + 31 and one column group of the tile =====
     const int quarter = warp & 3;
@@ -745,7 +836,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       constexpr uint32_t kPitch = 32u * kElem, kSlots = kPitch >> 4;
       constexpr uint32_t kPanelBytes = 32u * kPitch;
       constexpr int kGroupColumns = BN / kEpiGroups;
-      const uint32_t my_panels = smem_out + static_cast<uint32_t>(warp - 2) * 2u * kPanelBytes;
+      constexpr uint32_t kPanels = CONVERT ? 1u : 2u;  // a converting layer gives the second panel's room to its landing ring
+      const uint32_t my_panels = smem_out + static_cast<uint32_t>(warp - 2) * kPanels * kPanelBytes;
       // 16-byte slot i of this lane's row sits at row_at ^ (i << 4) (the swizzle a TMA store of kPitch-byte rows reads)
       const uint32_t row_at = static_cast<uint32_t>(lane) * kPitch + ((((static_cast<uint32_t>(lane) * kPitch) >> 7) & (kSlots - 1)) << 4);
       const uint32_t bias_at = smem_bias + static_cast<uint32_t>(group * kGroupColumns) * 4u;
@@ -817,7 +909,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               }
             }
           }
-          const uint32_t panel = my_panels + (chunk_it & 1u) * kPanelBytes;
+          const uint32_t panel = my_panels + (chunk_it & (kPanels - 1u)) * kPanelBytes;
           ++chunk_it;
           const uint32_t at = panel + row_at;
           if (kDynamic) {
@@ -835,12 +927,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
             }
             uint32_t w[8];
             scale_to_e4m3(r, e, w);
-            if (lane == 0) bulk_wait_read<1>();  // the store that last read this panel has finished with it
+            if (lane == 0) bulk_wait_read<kPanels - 1>();  // the store that last read this panel has finished with it
             __syncwarp();
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at ^ 16u), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
           } else {
-            if (lane == 0) bulk_wait_read<1>();
+            if (lane == 0) bulk_wait_read<kPanels - 1>();
             __syncwarp();
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
@@ -1043,6 +1135,7 @@ struct Plan {
   int tiles_x, tiles_y, tiles_n, total_tiles;
   bool flat;
   bool pair;  // clusters of two CTAs driving one cta_group::2 instruction stream
+  bool convert = false;    // bf16 activations, quantised on chip
   int fixed_epilogue = 0;  // kEpiLean | switches when one of the compile-time epilogues serves this call, else 0
   int out_h, out_w;
   size_t smem;
@@ -1057,7 +1150,8 @@ int out_elem_bytes(int out_mode) {
   }
 }
 
-int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan) {
+int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan,
+              bool convert = false) {
   // `g.cin` counts bytes of K per tap here (a BF16 layer arrives with its channel count doubled)
   const bool int8 = fmt == kFmtI8, scaled = fmt == kFmtMx;
   if (g.batch <= 0 || g.height <= 0 || g.width <= 0 || g.cin <= 0 || g.cout <= 0) return kBadArgument;
@@ -1088,6 +1182,8 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   if (bn == 64 && g.cout > 64 && scaled) bn = 128;  // a 64-wide tile may only start at column 0 of its scale tile
   pl.block_n = bn;
   pl.flat = pointwise && allow_flat;
+  pl.convert = convert;
+  if (convert && !(fmt == kFmtMx && pl.flat && pl.block_k == 128)) return kUnsupported;
   if (pl.flat) {
     pl.tile_h = 1, pl.tile_w = kTileM;
     const long long rows = static_cast<long long>(g.batch) * out_h * out_w;
@@ -1114,21 +1210,23 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   // CTA pairs for the wide, compute-bound INT8 tiles: a pair owns two consecutive row tiles (the last one may not exist:
   // its loads are zero-filled and its stores clipped). The block-scaled form is correct too but measured slower than
   // single CTAs (its scale copies serialise the pair's tensor pipes): it only runs when asked for (tuning flag 128).
-  pl.pair = bn == 256 && row_tiles >= 2 && !(g_debug_flags & 64) && (int8 || (g_debug_flags & 128));
+  pl.pair = bn == 256 && row_tiles >= 2 && !(g_debug_flags & 64) && (int8 || (g_debug_flags & 128)) && !convert;
   const long long total = (pl.pair ? (row_tiles + 1) / 2 : row_tiles) * pl.tiles_n;
   if (total > 0x3fffffffLL) return kUnsupported;
   pl.total_tiles = static_cast<int>(total);
   // shared memory: alignment slack + output panels + static activation-scale tiles + the stage ring. A layer with few
   // K iterations per tile is bound by its stores: it gets more panels in flight; a long main loop gets the stages.
   const int k_iters = g.kh * g.kw * (g.cin / pl.block_k);
-  pl.panels_per_half = out_elem == 4 ? 1 : 2;  // 16 KB panels of a 4-byte output: one per column group
+  pl.panels_per_half = out_elem == 4 || convert ? 1 : 2;  // 16 KB panels of a 4-byte output: one per column group
   (void)k_iters;
   const int stage_bytes = kTileM * pl.block_k + (pl.pair ? bn / 2 : bn) * pl.block_k + scale_tiles_b(bn) * 512 + 512;
   const int bias_bytes = pl.tiles_n * bn * 4;
   if (bias_bytes > 32 * 1024) return kUnsupported;
   const int epilogue_groups = 4;  // four-warp groups with output panels of their own
   const int gelu_bytes = gelu ? static_cast<int>(kGeluSmemBytes) : 0;
-  const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes;
+  const int raw_bytes = convert ? 1024 + kRawStages * static_cast<int>(kRawBytes) : 0;  // landing ring (+ its alignment)
+  const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes +
+                    raw_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
@@ -1183,14 +1281,14 @@ struct ConvMaps {
   CUtensorMap act, weight, out, sfb, sfa, out_warp;
 };
 
-template <int FMT, int BN, int BK, bool PAIR, int EPI = 0>
+template <int FMT, int BN, int BK, bool PAIR, int EPI = 0, bool CONVERT = false>
 int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaStream_t stream) {
   // the shared-memory opt-in is a per-device attribute of the function: set once per device and instantiation
   static bool configured[kMaxDevices] = {};
   const int device = current_device();
   if (device < 0 || device >= kMaxDevices || !configured[device]) {
     const cudaError_t e =
-        cudaFuncSetAttribute(conv_kernel<FMT, BN, BK, PAIR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        cudaFuncSetAttribute(conv_kernel<FMT, BN, BK, PAIR, EPI, CONVERT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (device >= 0 && device < kMaxDevices) configured[device] = true;
   }
@@ -1205,10 +1303,10 @@ int launch_conv(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cudaS
     attribute.val.clusterDim.x = 2, attribute.val.clusterDim.y = 1, attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR, EPI>, maps.act, maps.weight, maps.out, maps.sfb,
+    return static_cast<int>(cudaLaunchKernelEx(&config, conv_kernel<FMT, BN, BK, PAIR, EPI, CONVERT>, maps.act, maps.weight, maps.out, maps.sfb,
                                                maps.sfa, maps.out_warp, p));
   }
-  conv_kernel<FMT, BN, BK, PAIR, EPI><<<pl.ctas, kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, maps.out_warp, p);
+  conv_kernel<FMT, BN, BK, PAIR, EPI, CONVERT><<<pl.ctas, CONVERT ? kConvertThreads : kThreads, pl.smem, stream>>>(maps.act, maps.weight, maps.out, maps.sfb, maps.sfa, maps.out_warp, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1217,6 +1315,14 @@ int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cud
   // the general epilogue with its switches fixed at compile time, for the layers measured most: a block-scaled conv with
   // bias, GELU and static requantisation at each tile width's usual K step, and the INT8 conv with bias and bf16 output
   constexpr int kGeluStatic = kEpiFixed | kEpiGelu | kEpiStatic;
+  if constexpr (FMT == kFmtMx) {
+    if (pl.convert) {  // bf16 activations quantised on chip (flat layers, 128 channels per K step)
+      if constexpr (BN >= 128) {
+        if (pl.fixed_epilogue == kEpiLean) return launch_conv<FMT, BN, 128, false, kEpiLean, true>(maps, p, pl, stream);
+      }
+      return launch_conv<FMT, BN, 128, false, 0, true>(maps, p, pl, stream);
+    }
+  }
   if constexpr (FMT == kFmtMx) {
     if (pl.fixed_epilogue == kGeluStatic && !pl.pair) {
       if constexpr (BN == 64) {
@@ -1258,7 +1364,7 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 
 int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act_scales, const void* weight,
              const void* weight_scales, const float* a_scale, const float* w_scale, const FimConvGeometry* geometry,
-             const FimConvEpilogue* ep, void* out, int* status, void* stream) {
+             const FimConvEpilogue* ep, void* out, int* status, void* stream, bool convert = false) {
   const bool int8 = fmt == kFmtI8;
   if (geometry == nullptr || ep == nullptr) return kBadArgument;
   if (geometry->batch == 0 || geometry->height == 0 || geometry->width == 0) return kOk;
@@ -1278,7 +1384,8 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   } else if (fmt == kFmtBf16) {
     if (ep->out_mode != FIM_OUT_BF16 && ep->out_mode != FIM_OUT_F32) return kBadArgument;
   } else {
-    if (weight_scales == nullptr || (act_exponent == nullptr) == (act_scales == nullptr)) return kBadArgument;
+    if (weight_scales == nullptr) return kBadArgument;
+    if (convert ? act_scales != nullptr : (act_exponent == nullptr) == (act_scales == nullptr)) return kBadArgument;
     if (ep->out_mode == FIM_OUT_INT8 || ep->out_mode == FIM_OUT_INT32) return kBadArgument;
     if (ep->out_mode == FIM_OUT_E4M3_STATIC && ep->out_exponent == nullptr) return kBadArgument;
     if (ep->out_mode == FIM_OUT_E4M3_DYNAMIC && ep->out_scales == nullptr) return kBadArgument;
@@ -1288,13 +1395,15 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
     return kBadLayout;
   }
   const int out_elem = out_elem_bytes(ep->out_mode);
+  // one activation scale per pixel and 32 channels: given by the caller, or formed on chip from bf16 activations
+  const bool per_pixel = act_scales != nullptr || (convert && act_exponent == nullptr);
 
   // a 1x1 conv is a plain GEMM over flattened pixels when the residual (if any) is dense NHWC
   bool allow_flat = true;
   Plan pl;
   {
     Plan probe;
-    const int rc0 = make_plan(*g, fmt, act_scales != nullptr, true, out_elem, ep->act == FIM_ACT_GELU, &probe);
+    const int rc0 = make_plan(*g, fmt, per_pixel, true, out_elem, ep->act == FIM_ACT_GELU, &probe, convert);
     if (rc0 != kOk) return rc0;
     if (probe.flat && ep->residual != nullptr) {
       const long long c = ep->res_stride[3], xs = ep->res_stride[2], ys = ep->res_stride[1], bs = ep->res_stride[0];
@@ -1302,10 +1411,10 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
       if (!dense) allow_flat = false;
     }
   }
-  const int rc = make_plan(*g, fmt, act_scales != nullptr, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl);
+  const int rc = make_plan(*g, fmt, per_pixel, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl, convert);
   if (rc != kOk) return rc;
 
-  const Schedule sc = make_schedule(*g, pl, fmt != kFmtMx, act_scales != nullptr);
+  const Schedule sc = make_schedule(*g, pl, fmt != kFmtMx, per_pixel);
   ConvParams p;
   p.cin = g->cin, p.cout = g->cout;
   p.out_h = pl.out_h, p.out_w = pl.out_w;
@@ -1321,6 +1430,7 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   p.div_tiles_x = make_fastdiv(pl.tiles_x), p.div_tiles_y = make_fastdiv(pl.tiles_y);
   p.resident_k = sc.resident_k, p.n_major = sc.n_major;
   p.act_exponent = act_exponent;
+  p.convert_static = convert && act_exponent != nullptr ? 1 : 0;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;
   p.weight_scales = static_cast<const uint8_t*>(weight_scales);
@@ -1352,7 +1462,16 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   CUtensorMap& act_map = maps.act;
   CUtensorMap& weight_map = maps.weight;
   CUtensorMap& out_map = maps.out;
-  {
+  if (convert) {
+    // bf16 rows of the pixel matrix, landing as they lie in memory (256 bytes per row of a 128-channel box)
+    const uint64_t dims[4] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w), 1, 1};
+    const uint64_t strides[3] = {static_cast<uint64_t>(g->cin) * 2, static_cast<uint64_t>(in_w) * g->cin * 2,
+                                 static_cast<uint64_t>(in_w) * g->cin * 2};
+    const uint32_t box[4] = {128, static_cast<uint32_t>(kTileM), 1, 1};
+    const int rcm = make_tensor_map(&act_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rcm != kOk) return rcm;
+  } else {
     const uint64_t dims[4] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w), static_cast<uint64_t>(in_h),
                               static_cast<uint64_t>(in_b)};
     const uint64_t strides[3] = {static_cast<uint64_t>(g->cin), static_cast<uint64_t>(in_w) * g->cin,
@@ -1448,6 +1567,14 @@ extern "C" int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const
                                 const FimConvEpilogue* epilogue, void* out, int* status, void* stream) {
   return run_conv(kFmtMx, x, act_exponent, act_scales_swizzled, weight, weight_scales_swizzled, nullptr, nullptr, geometry, epilogue,
                   out, status, stream);
+}
+
+extern "C" int fim_mxfp8_conv2d_bf16(const void* x_bf16, const int8_t* act_exponent, const void* weight,
+                                     const void* weight_scales_swizzled, const FimConvGeometry* geometry,
+                                     const FimConvEpilogue* epilogue, void* out, int* status, void* stream) {
+  if (geometry != nullptr && geometry->cin % 128) return kUnsupported;
+  return run_conv(kFmtMx, x_bf16, act_exponent, nullptr, weight, weight_scales_swizzled, nullptr, nullptr, geometry, epilogue, out,
+                  status, stream, true);
 }
 
 extern "C" int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, const float* w_scale,

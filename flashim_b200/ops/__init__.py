@@ -70,6 +70,10 @@ mxfp8_conv2d_fused = Op("mxfp8_conv2d_fused", doc="(x, act_scale, weight, weight
                         "dw, *, act, residual, out_exponent, dynamic_out, out_fp32): mxfp8_conv2d with per-pixel activation "
                         "scales (act_scale uint8 swizzled) or static ones (int8 [Cin/32]), pre-swizzled weight scales, and "
                         "the GELU / dynamic-requant / fp32 epilogues")
+mxfp8_conv2d_bf16 = Op("mxfp8_conv2d_bf16", doc="(x bf16 [B, H, W, Cin], act_exponent int8 [Cin/32] | None, weight, weight_scales, "
+                       "bias, *, act, residual, out_exponent, dynamic_out, out_fp32): a 1x1 mxfp8_conv2d_fused whose "
+                       "activation quantiser (static exponents, or per pixel and 32 channels when act_exponent is None) "
+                       "runs inside the conv kernel; the same bits as quantising first")
 int8_conv2d_accumulators = Op("int8_conv2d_accumulators", doc="(x, weight, kh, kw, sh, sw, ph, pw, dh, dw) -> int32 "
                               "[B, Ho, Wo, Cout]: the raw sums of int8_conv2d")
 

@@ -47,6 +47,15 @@ class PointwiseMX(nn.Module):
                                       1, 1, 1, 1, 0, 0, 1, 1, **epilogue)
 
 
+    def forward_bf16(self, x: Tensor, **epilogue):
+        """The same layer on bf16 activations: quantised per pixel and 32 channels inside the conv kernel where it takes
+        them (Cin a multiple of 128), by the standalone quantiser otherwise. Same bits either way."""
+        if self.cin % 128 == 0:
+            return ops.mxfp8_conv2d_bf16(x, None, self.weight.view(torch.float8_e4m3fn), self.weight_scales, self.bias, **epilogue)
+        q, s = ops.quantize_mxfp8_dynamic(x)
+        return self.forward(q, s, **epilogue)
+
+
 class RefinerBlock(nn.Module):
     def __init__(self, channels: int, generator: torch.Generator) -> None:
         super().__init__()
@@ -75,12 +84,10 @@ class RefinerLevel(nn.Module):
 
     def forward(self, x: Tensor) -> Tensor:
         """bf16 ``[B, H, W, C]`` -> bf16 ``[B, H, W, 32]`` (channels 0-1 warp, 2-3 confidence, the rest padding)."""
-        q, s = ops.quantize_mxfp8_dynamic(x)
-        y = self.proj(q, s)
+        y = self.proj.forward_bf16(x)
         for block in self.blocks:
             y = block(y)
-        q, s = ops.quantize_mxfp8_dynamic(y)
-        return self.head(q, s)
+        return self.head.forward_bf16(y)
 
 
 class RefinerStack(nn.Module):

@@ -186,6 +186,15 @@ int fim_mxfp8_conv2d(const void* x, const int8_t* act_exponent, const void* act_
                      const void* weight_scales_swizzled, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue,
                      void* out, int* status, void* stream);
 
+/* The same conv on bf16 activations, with the activation quantiser inside the kernel (1x1, stride 1, unpadded,
+ * cin % 128 == 0 only; anything else returns FIM_ERR_UNSUPPORTED and the caller quantises first): converter warps turn
+ * each bf16 tile into E4M3 on its way to the MMAs, with the static exponents `act_exponent` (int8 [cin/32]) or, when that
+ * is NULL, with one exponent per pixel and 32 channels formed on the fly. The result equals fim_quantize_mxfp8_static /
+ * fim_quantize_mxfp8_dynamic followed by fim_mxfp8_conv2d bit for bit. Replaces the quantize_mxfp8 + mxfp8_conv2d pair of
+ * StaticMXFP8Conv2d.forward (flashim/quant/methods/conv2d.py:217-251) for such layers. */
+int fim_mxfp8_conv2d_bf16(const void* x_bf16, const int8_t* act_exponent, const void* weight, const void* weight_scales_swizzled,
+                          const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status, void* stream);
+
 /* INT8 conv: x int8 NHWC, weight int8 [cout, kh*kw*cin]; exact int32 accumulation in tensor memory; epilogue
  * float(acc) * (*a_scale * w_scale[n]) + bias (separately rounded), ReLU, bf16, residual, optional INT8 requantisation.
  * Replaces ops.int8_conv2d (flashim/ops/conv.py:174-206; kernel flashim/backends/triton/conv.py:702-805). */
