@@ -133,6 +133,13 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, vo
   if (mbar_try_addr(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, code, heed_abort, backoff_ns);
 }
+// The wait as a whole warp takes it: every lane polls, and the warp agrees on the outcome, so the code after it stays
+// warp-uniform (addresses and descriptors computed there can live in uniform registers).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                               bool heed_abort = true, uint32_t backoff_ns = 0) {
+  const bool ok = mbar_wait_addr(bar, parity, abort_flag, status, code, heed_abort, backoff_ns);
+  return __all_sync(0xffffffffu, ok) != 0;
+}
 // The same wait with its polling loop inlined: for kernels whose warps change their register allowance (setmaxnreg),
 // where a function shared by regions with different allowances cannot be allocated.
 __device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,

@@ -541,7 +541,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
 
   if (warp == 0) {
     // ===== TMA producer =====
-    if (lane == 0) {
+    // The whole warp walks the loops (warp-uniform control flow lets the coordinates, addresses and byte counts live in
+    // uniform registers, which is where the copy instructions take them from); one lane, picked by elect.sync, issues.
+    {
       const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
       const bool load_a = !(probe_flags(p) & 1), load_b = !(probe_flags(p) & 2);
       uint32_t s = 0, phase = 0, raw_s = 0, raw_phase = 0;
@@ -584,22 +586,25 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
             for (int j = 0; j < p.k_chunks; ++j, k0 += BK) {
               if (CONVERT) {
                 // the bf16 tile of this K step into the landing ring: 128 rows of the pixel matrix x 128 channels
-                if (!mbar_wait_addr(raw_empty0 + 8 * raw_s, raw_phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+                if (!mbar_wait_warp(raw_empty0 + 8 * raw_s, raw_phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
                   alive = false;
                   break;
                 }
-                mbar_expect_tx_addr(raw_full0 + 8 * raw_s, kRawBytes);
-                tma_load_4d_addr(smem_raw + raw_s * kRawBytes, &act_map, raw_full0 + 8 * raw_s, j * 128, m_tile * kTileM, 0, 0);
+                if (elect_one()) {
+                  mbar_expect_tx_addr(raw_full0 + 8 * raw_s, kRawBytes);
+                  tma_load_4d_addr(smem_raw + raw_s * kRawBytes, &act_map, raw_full0 + 8 * raw_s, j * 128, m_tile * kTileM, 0, 0);
+                }
                 if (++raw_s == kRawStages) raw_s = 0, raw_phase ^= 1;
               }
-              if (!mbar_wait_addr(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+              if (!mbar_wait_warp(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
                 alive = false;
                 break;
               }
               const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
               const bool load_sfb = SCALED && (fresh || k0 >= p.resident_k * BK);
               const uint32_t tx_bytes = (PAIR ? 2u : 1u) * (operand_bytes + (load_sfb ? sfb_bytes : 0u));
-              if (!PAIR || rank == 0) {
+              const bool issuer = elect_one();  // one lane, and the compiler knows it is one: operands stay in uniform registers
+              if (issuer && (!PAIR || rank == 0)) {
                 if (tx_bytes != 0) {
                   mbar_expect_tx_addr(full0 + 8 * s, tx_bytes);
                 } else {
@@ -607,6 +612,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 }
               }
               if (PAIR) {
+                if (issuer) {
                 if (load_a) tma_load_4d_pair(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
                 if (load_b) tma_load_2d_pair(smem_b + s * kBBytes, &weight_map, bar, k0, n0 + static_cast<int>(rank) * (width / 2));
                 if (SCALED) {
@@ -624,9 +630,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                     tma_load_2d_pair(smem_sfa + s * 512, &sfa_map, bar, 0, m_tile * p.act_scale_tiles + ((j * BK) >> 7));
                   }
                 }
+                }
                 if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
                 continue;
               }
+              if (issuer) {
               if (load_a && !CONVERT) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
               if (load_b) {
 #pragma unroll
@@ -646,6 +654,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 }
                 if (dynamic_a && !CONVERT) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
               }
+              }
               if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
             }
           }
@@ -654,12 +663,13 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
   } else if (warp == 1) {
     // ===== MMA issuer (of a pair: the leader CTA's) =====
-    if (lane == 0 && rank == 0) {
+    // (the whole warp walks the loops, as in the producer; one lane issues the tcgen05 instructions and their commits)
+    if (rank == 0) {
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
       const int k_iters = taps * p.k_chunks;
       const bool copy_scales = SCALED && !(probe_flags(p) & 8);
-      if (SCALED && !dynamic_a) {
+      if (SCALED && !dynamic_a && elect_one()) {
         // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
         const int tiles = (p.cin + 127) / 128;
         for (int t = 0; t < tiles; ++t) {
@@ -676,7 +686,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers, ++tile_it) {
         const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
         const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
-        if (!mbar_wait_addr(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
+        if (!mbar_wait_warp(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
         int m_tile, n0, width;
@@ -689,7 +699,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         int j = 0;            // channel chunk within the tap
         uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
         for (int ki = 0; ki < k_iters; ++ki) {
-          if (!mbar_wait_addr(full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
+          if (!mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
             alive = false;
             break;
           }
@@ -705,60 +715,65 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const bool resident = ki < p.resident_k;
           const uint32_t sfb_tmem = tmem + (resident ? resident_column + kSfbColumns * ki : kSfbColumn + kSfbColumns * s);
           const uint32_t sfa_tmem = tmem + sfa_column + 4 * (dynamic_a ? s : (kb_a >> 2));
-          if (copy_scales) {
+          // everything the instructions take is formed here, by the whole warp; the issuing lane only issues
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
+          const uint64_t sfb_from = sfb_desc0 + static_cast<uint64_t>((s * kScaleTilesB * 512) >> 4);
+          const uint64_t sfa_from = sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4);
+          const bool copy_b = copy_scales && (fresh || !resident), copy_a = copy_scales && dynamic_a;
+          const uint32_t scaled0 = idesc | (a_id << 29) | (b_id << 4);  // the scale ids advance by one per K step
+          const uint32_t first = ki > 0 ? 1u : 0u;
+          if (elect_one()) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
-              if (i < scale_tiles && (fresh || !resident)) {
-                const uint64_t from = sfb_desc0 + static_cast<uint64_t>(((s * kScaleTilesB + i) * 512) >> 4);
+              if (i < scale_tiles && copy_b) {
                 if (PAIR) {
-                  tc_copy_scales_pair(sfb_tmem + 4 * i, from);
+                  tc_copy_scales_pair(sfb_tmem + 4 * i, sfb_from + 32 * i);
                 } else {
-                  tc_copy_scales(sfb_tmem + 4 * i, from);
+                  tc_copy_scales(sfb_tmem + 4 * i, sfb_from + 32 * i);
                 }
               }
             }
-            if (dynamic_a) {
+            if (copy_a) {
               if (PAIR) {
-                tc_copy_scales_pair(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
+                tc_copy_scales_pair(sfa_tmem, sfa_from);
               } else {
-                tc_copy_scales(sfa_tmem, sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4));
+                tc_copy_scales(sfa_tmem, sfa_from);
               }
             }
-          }
-          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
 #pragma unroll
-          for (int k = 0; k < kKSteps; ++k) {
-            const uint32_t accumulate = (ki > 0 || k > 0) ? 1u : 0u;
-            if (INT8) {
-              if (PAIR) {
-                tc_mma_i8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+            for (int k = 0; k < kKSteps; ++k) {
+              const uint32_t accumulate = k > 0 ? 1u : first;
+              if (INT8) {
+                if (PAIR) {
+                  tc_mma_i8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+                } else {
+                  tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+                }
+              } else if (!SCALED) {
+                tc_mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
               } else {
-                tc_mma_i8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
-              }
-            } else if (!SCALED) {
-              tc_mma_bf16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
-            } else {
-              const uint32_t scaled = idesc | ((a_id + k) << 29) | ((b_id + k) << 4);
-              if (PAIR) {
-                tc_mma_mxf8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
-              } else {
-                tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
+                const uint32_t scaled = scaled0 + static_cast<uint32_t>(k) * ((1u << 29) | (1u << 4));
+                if (PAIR) {
+                  tc_mma_mxf8_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
+                } else {
+                  tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa_tmem, sfb_tmem, accumulate);
+                }
               }
             }
-          }
-          // the stage is free once these MMAs have read it (of a pair: in both CTAs)
-          if (PAIR) {
-            tc_commit_pair(empty0 + 8 * s);
-            tc_commit_pair((empty0 + 8 * s) | kPeerBit);
-          } else {
-            tc_commit(&ctl.empty[s]);
+            // the stage is free once these MMAs have read it (of a pair: in both CTAs)
+            if (PAIR) {
+              tc_commit_pair(empty0 + 8 * s);
+              tc_commit_pair((empty0 + 8 * s) | kPeerBit);
+            } else {
+              tc_commit(&ctl.empty[s]);
+            }
           }
           if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
           if (++j == p.k_chunks) j = 0;
           if (BK != 128) b_id = (b_id + kKSteps) & 3;
         }
-        if (alive) {
+        if (alive && elect_one()) {
           if (PAIR) {
             tc_commit_pair(tfull0 + 8 * acc);
             tc_commit_pair((tfull0 + 8 * acc) | kPeerBit);
