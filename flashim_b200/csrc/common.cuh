@@ -37,6 +37,13 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// A value the compiler must keep in a register: kernel parameters read inside the single-thread issue loops are otherwise
+// re-read from the constant bank every iteration, and each such load is tens of cycles in a chain one thread walks alone.
+__device__ __forceinline__ uint32_t in_register(uint32_t v) {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

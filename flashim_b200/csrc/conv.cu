@@ -16,6 +16,8 @@
 // tensor pipe.
 //
 // Rounding points follow FlashIM's torch reference: flashim/ops/conv.py:174-206,309-342 and flashim/ops/gemm.py:58-98.
+#include <cstdio>
+
 #include "common.cuh"
 #include "flashim_sm100.h"
 #include "flashim_sm100_tune.h"
@@ -539,12 +541,27 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t raw_full0 = smem_u32(&ctl.raw_full[0]), raw_empty0 = smem_u32(&ctl.raw_empty[0]);
   volatile int* abort_flag = &ctl.abort_flag;
 
+  // how the producer and MMA warps walk their loops (see the producer): one elected lane alone, or the whole warp
+  constexpr bool kLaneLoop = BN <= 128;
+  auto loop_wait = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+    return kLaneLoop ? mbar_wait_addr(bar, parity, abort_flag, p.status, code) : mbar_wait_warp(bar, parity, abort_flag, p.status, code);
+  };
   if (warp == 0) {
     // ===== TMA producer =====
-    // The whole warp walks the loops (warp-uniform control flow lets the coordinates, addresses and byte counts live in
-    // uniform registers, which is where the copy instructions take them from); one lane, picked by elect.sync, issues.
-    {
-      const uint32_t a_box_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w) * BK;
+    // The issuing lane is picked by elect.sync rather than by its lane number: the compiler then knows that a single lane
+    // runs the code and keeps coordinates, addresses and byte counts in uniform registers, which is where the copy
+    // instructions take them from (behind `lane == 0` every operand of every copy went through a vector-to-uniform move,
+    // several hundred cycles per K step in a chain this lane walks alone). Narrow tiles, whose K steps are short, let that
+    // one lane walk the whole loop (kLaneLoop); for 256-wide tiles the whole warp walks it, polls the barriers together
+    // and elects the issuer per K step, which measured 3 % faster there and 10 % slower on the narrow ones.
+    if (kLaneLoop ? elect_one() : true) {
+      const uint32_t a_box_bytes = in_register(static_cast<uint32_t>(p.tile_h * p.tile_w) * BK);
+      // loop parameters, once into registers (a kernel parameter read in the loop is a constant-bank load per iteration)
+      const uint32_t stages = in_register(static_cast<uint32_t>(p.stages));
+      const int k_chunks = static_cast<int>(in_register(static_cast<uint32_t>(p.k_chunks)));
+      const int kh = static_cast<int>(in_register(static_cast<uint32_t>(p.kh))), kw = static_cast<int>(in_register(static_cast<uint32_t>(p.kw)));
+      const int dil_h = static_cast<int>(in_register(static_cast<uint32_t>(p.dil_h))), dil_w = static_cast<int>(in_register(static_cast<uint32_t>(p.dil_w)));
+      const int resident_bytes = static_cast<int>(in_register(static_cast<uint32_t>(p.resident_k * BK)));
       const bool load_a = !(probe_flags(p) & 1), load_b = !(probe_flags(p) & 2);
       uint32_t s = 0, phase = 0, raw_s = 0, raw_phase = 0;
       bool alive = true;
@@ -580,30 +597,30 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
         const uint8_t* sfa_src = dynamic_a && !CONVERT ? p.act_scales + static_cast<size_t>(m_tile) * p.act_scale_tiles * 512 : nullptr;
         int k0 = 0;  // offset along the weight's K axis
-        for (int ky = 0; ky < p.kh && alive; ++ky) {
-          for (int kx = 0; kx < p.kw && alive; ++kx) {
-            const int cx = x0 + kx * p.dil_w, cy = y0 + ky * p.dil_h;
-            for (int j = 0; j < p.k_chunks; ++j, k0 += BK) {
+        for (int ky = 0; ky < kh && alive; ++ky) {
+          for (int kx = 0; kx < kw && alive; ++kx) {
+            const int cx = x0 + kx * dil_w, cy = y0 + ky * dil_h;
+            for (int j = 0; j < k_chunks; ++j, k0 += BK) {
               if (CONVERT) {
                 // the bf16 tile of this K step into the landing ring: 128 rows of the pixel matrix x 128 channels
-                if (!mbar_wait_warp(raw_empty0 + 8 * raw_s, raw_phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+                if (!loop_wait(raw_empty0 + 8 * raw_s, raw_phase ^ 1, kStatusWaitEmpty)) {
                   alive = false;
                   break;
                 }
-                if (elect_one()) {
+                if (kLaneLoop || elect_one()) {
                   mbar_expect_tx_addr(raw_full0 + 8 * raw_s, kRawBytes);
                   tma_load_4d_addr(smem_raw + raw_s * kRawBytes, &act_map, raw_full0 + 8 * raw_s, j * 128, m_tile * kTileM, 0, 0);
                 }
                 if (++raw_s == kRawStages) raw_s = 0, raw_phase ^= 1;
               }
-              if (!mbar_wait_warp(empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+              if (!loop_wait(empty0 + 8 * s, phase ^ 1, kStatusWaitEmpty)) {
                 alive = false;
                 break;
               }
               const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
-              const bool load_sfb = SCALED && (fresh || k0 >= p.resident_k * BK);
+              const bool load_sfb = SCALED && (fresh || k0 >= resident_bytes);
               const uint32_t tx_bytes = (PAIR ? 2u : 1u) * (operand_bytes + (load_sfb ? sfb_bytes : 0u));
-              const bool issuer = elect_one();  // one lane, and the compiler knows it is one: operands stay in uniform registers
+              const bool issuer = kLaneLoop || elect_one();
               if (issuer && (!PAIR || rank == 0)) {
                 if (tx_bytes != 0) {
                   mbar_expect_tx_addr(full0 + 8 * s, tx_bytes);
@@ -631,7 +648,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                   }
                 }
                 }
-                if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
+                if (++s == stages) s = 0, phase ^= 1;
                 continue;
               }
               if (issuer) {
@@ -655,7 +672,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 if (dynamic_a && !CONVERT) bulk_load_addr(smem_sfa + s * 512, sfa_src + static_cast<size_t>((j * BK) >> 7) * 512, 512, bar);
               }
               }
-              if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
+              if (++s == stages) s = 0, phase ^= 1;
             }
           }
         }
@@ -663,13 +680,20 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
   } else if (warp == 1) {
     // ===== MMA issuer (of a pair: the leader CTA's) =====
-    // (the whole warp walks the loops, as in the producer; one lane issues the tcgen05 instructions and their commits)
-    if (rank == 0) {
+    // (one lane picked by elect.sync, as in the producer: it issues the tcgen05 instructions and their commits)
+    if (rank == 0 && (kLaneLoop ? elect_one() : true)) {
       const uint64_t a_desc0 = kmajor_desc(smem_a, BK), b_desc0 = kmajor_desc(smem_b, BK);
       const uint64_t sfb_desc0 = scale_desc(smem_sfb), sfa_desc0 = scale_desc(dynamic_a ? smem_sfa : smem_sfa_static);
-      const int k_iters = taps * p.k_chunks;
+      const int k_iters = static_cast<int>(in_register(static_cast<uint32_t>(taps * p.k_chunks)));
       const bool copy_scales = SCALED && !(probe_flags(p) & 8);
-      if (SCALED && !dynamic_a && elect_one()) {
+      // loop parameters, once into registers
+      const uint32_t stages = in_register(static_cast<uint32_t>(p.stages));
+      const int k_chunks = static_cast<int>(in_register(static_cast<uint32_t>(p.k_chunks)));
+      const int resident_k = static_cast<int>(in_register(static_cast<uint32_t>(p.resident_k)));
+      const uint32_t sfa_base = in_register(tmem + sfa_column), sfb_stage_base = in_register(tmem + kSfbColumn);
+      const uint32_t sfb_resident_base = in_register(tmem + resident_column);
+      const bool per_stage_a = in_register(dynamic_a ? 1u : 0u) != 0;
+      if (SCALED && !dynamic_a && (kLaneLoop || elect_one())) {
         // static activation scales never change: all tiles go to tensor memory once, ahead of the first MMA
         const int tiles = (p.cin + 127) / 128;
         for (int t = 0; t < tiles; ++t) {
@@ -683,10 +707,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       uint32_t s = 0, phase = 0, tile_it = 0;
       bool alive = true;
       int last_n0 = -1;
+#if FIM_PROBE_BUILD
+      long long c_wait = 0, c_issue = 0, c_tile = 0, c_rounds = 0;
+      const long long c_start = clock64();
+#endif
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers, ++tile_it) {
+#if FIM_PROBE_BUILD
+        const long long c_t0 = clock64();
+#endif
         const uint32_t acc = kAccStages == 2 ? (tile_it & 1u) : 0u;
         const uint32_t acc_phase = kAccStages == 2 ? ((tile_it >> 1) & 1u) : (tile_it & 1u);
-        if (!mbar_wait_warp(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty)) break;
+        if (!loop_wait(tempty0 + 8 * acc, acc_phase ^ 1, kStatusWaitTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
         int m_tile, n0, width;
@@ -698,12 +729,22 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         last_n0 = n0;
         int j = 0;            // channel chunk within the tap
         uint32_t b_id = 0;    // (32-channel block index along the weight's K) mod 4 at the start of the stage
+#if FIM_PROBE_BUILD
+        c_tile += clock64() - c_t0;
+#endif
         for (int ki = 0; ki < k_iters; ++ki) {
-          if (!mbar_wait_warp(full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
+#if FIM_PROBE_BUILD
+          const long long c_a = clock64();
+#endif
+          if (!loop_wait(full0 + 8 * s, phase, kStatusWaitFull)) {
             alive = false;
             break;
           }
           tc_fence_after();
+#if FIM_PROBE_BUILD
+          const long long c_b = clock64();
+          c_wait += c_b - c_a;
+#endif
           uint32_t a_id = 0;
           const uint32_t kb_a = j * kKSteps;  // 32-channel block index of the activation chunk
           if (BK != 128) a_id = kb_a & 3;
@@ -712,18 +753,17 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           // ring of stages earlier). Issuing a stage's copies one stage early was measured: no gain, the pipe serialises
           // copies and MMAs either way.
           // the first resident_k iterations keep their weight scales in columns of their own from tile to tile
-          const bool resident = ki < p.resident_k;
-          const uint32_t sfb_tmem = tmem + (resident ? resident_column + kSfbColumns * ki : kSfbColumn + kSfbColumns * s);
-          const uint32_t sfa_tmem = tmem + sfa_column + 4 * (dynamic_a ? s : (kb_a >> 2));
-          // everything the instructions take is formed here, by the whole warp; the issuing lane only issues
+          const bool resident = ki < resident_k;
+          const uint32_t sfb_tmem = resident ? sfb_resident_base + kSfbColumns * ki : sfb_stage_base + kSfbColumns * s;
+          const uint32_t sfa_tmem = sfa_base + 4 * (per_stage_a ? s : (kb_a >> 2));
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
           const uint64_t sfb_from = sfb_desc0 + static_cast<uint64_t>((s * kScaleTilesB * 512) >> 4);
           const uint64_t sfa_from = sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4);
-          const bool copy_b = copy_scales && (fresh || !resident), copy_a = copy_scales && dynamic_a;
+          const bool copy_b = copy_scales && (fresh || !resident), copy_a = copy_scales && per_stage_a;
           const uint32_t scaled0 = idesc | (a_id << 29) | (b_id << 4);  // the scale ids advance by one per K step
           const uint32_t first = ki > 0 ? 1u : 0u;
-          if (elect_one()) {
+          if (kLaneLoop || elect_one()) {
 #pragma unroll
             for (int i = 0; i < kScaleTilesB; ++i) {
               if (i < scale_tiles && copy_b) {
@@ -769,11 +809,15 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               tc_commit(&ctl.empty[s]);
             }
           }
-          if (++s == static_cast<uint32_t>(p.stages)) s = 0, phase ^= 1;
-          if (++j == p.k_chunks) j = 0;
+#if FIM_PROBE_BUILD
+          c_issue += clock64() - c_b;
+          ++c_rounds;
+#endif
+          if (++s == stages) s = 0, phase ^= 1;
+          if (++j == k_chunks) j = 0;
           if (BK != 128) b_id = (b_id + kKSteps) & 3;
         }
-        if (alive && elect_one()) {
+        if (alive && (kLaneLoop || elect_one())) {
           if (PAIR) {
             tc_commit_pair(tfull0 + 8 * acc);
             tc_commit_pair((tfull0 + 8 * acc) | kPeerBit);
@@ -782,6 +826,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           }
         }
       }
+#if FIM_PROBE_BUILD
+      if ((p.debug & 2048) && blockIdx.x == 0 && (kLaneLoop || lane == 0)) {
+        printf("mma warp: %lld K rounds, per round wait %.1f issue %.1f clk; per tile head %.1f clk over %u tiles; total %lld clk\n", c_rounds,
+               double(c_wait) / double(c_rounds), double(c_issue) / double(c_rounds), double(c_tile) / double(tile_it), tile_it, clock64() - c_start);
+      }
+#endif
     }
   } else if (CONVERT && warp >= 2 + 16) {
     // ===== converter: bf16 landing tile -> E4M3 K-major stage (+ the stage's activation-scale tile) =====

@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __gri
   __syncthreads();
   if (u_end <= u_begin) return;
 
-  // ---- copies: issued by lane 0 of warp 0 (the cursor lives in every lane of that warp, uniformly) ----
+  // ---- copies: issued by one lane of warp 0 (the cursor lives in every lane of that warp, uniformly) ----
   CopyCursor cur;
   cur.u = u_begin, cur.u_end = u_end, cur.g = 1, cur.len = 0, cur.k0 = 0, cur.tx = 0, cur.ct = 0, cur.b = 0;
   uint32_t copy_stage = 0;
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __gri
       cur.b = t / p.channel_tiles;
       cur.g = 0;
     }
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, known to the compiler as one: the copy's operands stay in uniform registers
       mbar_expect_tx_addr(full0 + 8 * copy_stage, kChunkBytes);
       tma_load_4d_addr(smem0 + copy_stage * kChunkBytes, &in_map, full0 + 8 * copy_stage, cur.ct * kChannels,
                        cur.tx * kTileCols - 2, (cur.k0 + cur.g) * kChunkRows - 2, cur.b);
@@ -340,7 +340,8 @@ __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __gri
             bool free_stage = true;
             if (taken >= 1) {
               const uint32_t round = (taken - 1) / kStages;
-              free_stage = mbar_wait_addr(empty0 + 8 * copy_stage, round & 1u, &abort_flag, p.status, kStatusWaitRows);
+              // (the warp agrees on the outcome: the copy below is issued through elect.sync, which every lane must reach)
+              free_stage = __all_sync(0xffffffffu, mbar_wait_addr(empty0 + 8 * copy_stage, round & 1u, &abort_flag, p.status, kStatusWaitRows));
             }
             copies_left = free_stage && issue_copy();
           }
