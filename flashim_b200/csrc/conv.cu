@@ -465,7 +465,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
   const uint32_t smem_raw = (smem_bias + static_cast<uint32_t>(p.tiles_n * BN) * 4u + 1023u) & ~1023u;  // CONVERT: bf16 landing ring
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (the warp index through a shuffle: the compiler then treats it, and every address or coordinate derived from it, as
+  // uniform over the warp)
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   // per-pixel activation scales: read from HBM tiles, or written into the stage by the converter warps
   const bool dynamic_a = SCALED && (CONVERT ? p.convert_static == 0 : p.act_scales != nullptr);
   const int taps = p.kh * p.kw;
@@ -927,7 +929,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           // ask for the line in L2 before the wait for the accumulator (a prefetch holds no registers)
           if (valid && column0 < width) asm volatile("prefetch.global.L2 [%0];" ::"l"(res_row));
         }
-        if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+        // (the warp leaves together: its stores are issued through elect.sync, which every lane must reach)
+        if (!mbar_wait_warp(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
         tc_fence_after();
         uint32_t q[kChunksPerWarp][16];
 #pragma unroll
@@ -992,12 +995,12 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
             }
             uint32_t w[8];
             scale_to_e4m3(r, e, w);
-            if (lane == 0) bulk_wait_read<kPanels - 1>();  // the store that last read this panel has finished with it
+            if (elect_one()) bulk_wait_read<kPanels - 1>();  // the store that last read this panel has finished with it
             __syncwarp();
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at ^ 16u), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
           } else {
-            if (lane == 0) bulk_wait_read<kPanels - 1>();
+            if (elect_one()) bulk_wait_read<kPanels - 1>();
             __syncwarp();
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
@@ -1008,20 +1011,21 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           }
           fence_async_proxy();
           __syncwarp();
-          if (lane == 0) {
+          if (elect_one()) {  // always the same lane (the lowest): the bulk groups it commits are the ones it waits for
             tma_store_4d(&out_warp_map, panel, (n0 + column0 + g * 32) * static_cast<int>(kElem), m * kTileM + quarter * 32, 0, 0);
             bulk_commit();
           }
         }
       }
-      if (lane == 0) bulk_wait_read<0>();
+      if (elect_one()) bulk_wait_read<0>();
     } else
     if (group < kEpiGroups * kTileSets) {
     const int cgroup = group & (kEpiGroups - 1);  // column group inside the tile
     const uint32_t tile_set = static_cast<uint32_t>(group / kEpiGroups);
     const EpilogueSwitches sw = epilogue_switches<EPI>(p);
     const uint32_t panel_bytes_ = 4096u * sw.out_elem;
-    const bool leader = ((warp - 2) & 3) == 0 && lane == 0;  // issues the TMA stores of its group
+    // the warp whose elected lane issues the TMA stores of its group (always the same lane: it waits for the groups it commits)
+    const bool leader_warp = ((warp - 2) & 3) == 0;
     const uint32_t bar_id = 1 + group;
     const int row = quarter * 32 + lane;
     const int ry = row / p.tile_w, rx = row - ry * p.tile_w;
@@ -1066,7 +1070,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       // deciding warp cannot be two tiles ahead of a sibling, which it meets at this barrier every tile.
       if (own) {
         // no barrier joins the warps below, so each waits for itself
-        if (!mbar_wait_addr(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+        if (!mbar_wait_warp(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
       } else {
         volatile int* go = &ctl.group_go[group][(tile_it >> (kTileSets - 1)) & 1u];
         if (quarter == 0) {
@@ -1088,7 +1092,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         const uint32_t slot = chunk_it & (sw.panels - 1);
         const uint32_t panel = own ? own_panels + slot * own_bytes : panels + slot * panel_bytes_;
         ++chunk_it;
-        if (own ? lane == 0 : leader) {  // the store that last read this panel has finished with it
+        if ((own || leader_warp) && elect_one()) {  // the store that last read this panel has finished with it
           if (sw.panels == 2) {
             bulk_wait_read<1>();
           } else {
@@ -1106,14 +1110,14 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         fence_async_proxy();
         if (own) {
           __syncwarp();
-          if (lane == 0 && store) {
+          if (store && elect_one()) {
             tma_store_4d(&out_warp_map, panel, n * static_cast<int>(sw.out_elem), x0 + quarter * 32, y0, b);
             bulk_commit();
           }
           return;
         }
         named_barrier(bar_id, 128);
-        if (leader && store) {
+        if (leader_warp && store && elect_one()) {
           tma_store_4d(&out_map, panel, n * static_cast<int>(sw.out_elem), x0, y0, b);
           bulk_commit();
         }
@@ -1167,7 +1171,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
       }
     }
-    if (own ? lane == 0 : leader) bulk_wait_read<0>();
+    if ((own || leader_warp) && elect_one()) bulk_wait_read<0>();
     }
   }
 
