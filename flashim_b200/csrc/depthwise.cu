@@ -197,7 +197,8 @@ __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __gri
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ int abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (the warp index through a shuffle: uniform to the compiler, and so is everything derived from it)
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
   // Persistent CTAs over work units of five output rows. A strip is one (image, channel tile, column tile) over all rows;
   // the units of all strips form one sequence, of which this CTA owns the contiguous range [u_begin, u_end): an equal
