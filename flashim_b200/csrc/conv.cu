@@ -87,6 +87,8 @@ struct ConvParams {
   const float* out_scale;
   int* status;
   uint32_t poll_backoff_ns;  // sleep between polls of the epilogue's wait for an accumulator
+  int b_slots;               // weight (and weight-scale) tiles held in shared memory: `stages`, or every K step of a tile (resident)
+  int weights_resident;      // 1: the layer's whole weight matrix is loaded once per CTA and stays in shared memory
   int convert_static;        // bf16 activations: 1 = quantise with act_exponent, 0 = per pixel and 32 channels on the fly
   int warp_panels;           // flat 1x1 convs: every epilogue warp stages and stores its own 32 rows (no barrier between warps)
   int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
@@ -104,6 +106,7 @@ struct SharedControl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t weights_ready;          // resident weights: their one-time copies have landed
   uint64_t raw_full[kRawStages];   // bf16 landing ring of a converting layer
   uint64_t raw_empty[kRawStages];
   uint32_t tmem_base;
@@ -458,9 +461,9 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_gelu = base;  // kGeluTable first, when the epilogue applies GELU: its addresses must fit 16 bits
   const uint32_t smem_a = base + (p.act == kActGelu ? kGeluSmemBytes : 0u);
   const uint32_t smem_b = smem_a + p.stages * kABytes;
-  const uint32_t smem_out = smem_b + p.stages * kBBytes;
+  const uint32_t smem_out = smem_b + static_cast<uint32_t>(p.b_slots) * kBBytes;
   const uint32_t smem_sfb = smem_out + kPanelGroups * p.panels_per_half * panel_bytes;
-  const uint32_t smem_sfa = smem_sfb + p.stages * kScaleTilesB * 512;
+  const uint32_t smem_sfa = smem_sfb + static_cast<uint32_t>(p.b_slots) * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
   const uint32_t smem_raw = (smem_bias + static_cast<uint32_t>(p.tiles_n * BN) * 4u + 1023u) & ~1023u;  // CONVERT: bf16 landing ring
@@ -481,6 +484,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       mbar_init(&ctl.full[s], CONVERT ? 1 + kConverterWarps : 1);  // the producer's bytes (+ the converter warps' tile)
       mbar_init(&ctl.empty[s], 1);
     }
+    mbar_init(&ctl.weights_ready, 1);
     if (CONVERT) {
       for (int s = 0; s < kRawStages; ++s) {
         mbar_init(&ctl.raw_full[s], 1);
@@ -568,6 +572,29 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       uint32_t s = 0, phase = 0, raw_s = 0, raw_phase = 0;
       bool alive = true;
       int last_n0 = -1;
+      const bool resident_b = in_register(static_cast<uint32_t>(p.weights_resident)) != 0;
+      if (resident_b && worker < p.total_tiles && (kLaneLoop || elect_one())) {
+        // A layer with one output-channel tile whose weights fit beside the activation ring: every K step's weight tile
+        // and scale tiles are copied once and stay; the loop below then moves activations only.
+        const int k_total = kh * kw * k_chunks;
+        mbar_expect_tx_addr(smem_u32(&ctl.weights_ready), static_cast<uint32_t>(k_total) * (kBBytes + (SCALED ? kScaleTilesB * 512u : 0u)));
+        for (int ki = 0; ki < k_total; ++ki) {
+#pragma unroll
+          for (int part = 0; part < BN / kWeightBoxRows; ++part) {
+            tma_load_2d_addr(smem_b + ki * kBBytes + part * kWeightBoxRows * BK, &weight_map, smem_u32(&ctl.weights_ready), ki * BK,
+                             part * kWeightBoxRows);
+          }
+          if (SCALED) {
+#pragma unroll
+            for (int i = 0; i < kScaleTilesB; ++i) {
+              const int row_tile = min(i, p.weight_row_tiles - 1);
+              bulk_load_addr(smem_sfb + (ki * kScaleTilesB + i) * 512,
+                             p.weight_scales + (static_cast<size_t>(row_tile) * p.weight_scale_tiles + ((ki * BK) >> 7)) * 512, 512,
+                             smem_u32(&ctl.weights_ready));
+            }
+          }
+        }
+      }
       for (int tile = worker; tile < p.total_tiles && alive; tile += workers) {
         int m_tile, n0, width;
         decode_tile<BN>(p, tile, m_tile, n0, width);
@@ -584,7 +611,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         // (a pair's weight box always has BN / 2 rows: for a half-width tile only the first width / 2 of them are used)
         // (a converting layer's activation tile and scale tile are written by the converter warps, not counted here)
         const uint32_t operand_bytes = (load_a && !CONVERT ? a_box_bytes : 0u) +
-                                       (load_b ? (PAIR ? kBBytes : static_cast<uint32_t>(width) * BK) : 0u) +
+                                       (load_b && !resident_b ? (PAIR ? kBBytes : static_cast<uint32_t>(width) * BK) : 0u) +
                                        (dynamic_a && !CONVERT ? 512u : 0u);
         const uint32_t sfb_bytes = SCALED ? scale_tiles * 512u : 0u;
         // weight scales of the first resident_k iterations are already in tensor memory when the tile before this one
@@ -620,7 +647,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
                 break;
               }
               const uint32_t bar = PAIR ? ((full0 + 8 * s) & ~kPeerBit) : full0 + 8 * s;
-              const bool load_sfb = SCALED && (fresh || k0 >= resident_bytes);
+              const bool load_sfb = SCALED && !resident_b && (fresh || k0 >= resident_bytes);
               const uint32_t tx_bytes = (PAIR ? 2u : 1u) * (operand_bytes + (load_sfb ? sfb_bytes : 0u));
               const bool issuer = kLaneLoop || elect_one();
               if (issuer && (!PAIR || rank == 0)) {
@@ -655,7 +682,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
               }
               if (issuer) {
               if (load_a && !CONVERT) tma_load_4d_addr(smem_a + s * kABytes, &act_map, bar, j * BK, cx, cy, b);
-              if (load_b) {
+              if (load_b && !resident_b) {
 #pragma unroll
                 for (int part = 0; part < BN / kWeightBoxRows; ++part) {
                   if (part < b_parts) {
@@ -709,6 +736,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       uint32_t s = 0, phase = 0, tile_it = 0;
       bool alive = true;
       int last_n0 = -1;
+      const bool resident_b = in_register(static_cast<uint32_t>(p.weights_resident)) != 0;
+      if (resident_b && worker < p.total_tiles) alive = loop_wait(smem_u32(&ctl.weights_ready), 0, kStatusWaitFull);
 #if FIM_PROBE_BUILD
       long long c_wait = 0, c_issue = 0, c_tile = 0, c_rounds = 0;
       const long long c_start = clock64();
@@ -759,8 +788,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const uint32_t sfb_tmem = resident ? sfb_resident_base + kSfbColumns * ki : sfb_stage_base + kSfbColumns * s;
           const uint32_t sfa_tmem = sfa_base + 4 * (per_stage_a ? s : (kb_a >> 2));
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * kABytes) >> 4);
-          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * kBBytes) >> 4);
-          const uint64_t sfb_from = sfb_desc0 + static_cast<uint64_t>((s * kScaleTilesB * 512) >> 4);
+          // weights: the stage's tile, or K step ki of the resident matrix (a half-width tile starts n0 rows into it)
+          const uint32_t b_slot = resident_b ? static_cast<uint32_t>(ki) : s;
+          const uint32_t b_row0 = resident_b ? static_cast<uint32_t>(n0) : 0u;
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((b_slot * kBBytes + b_row0 * BK) >> 4);
+          const uint64_t sfb_from = sfb_desc0 + static_cast<uint64_t>(((b_slot * kScaleTilesB + (b_row0 >> 7)) * 512) >> 4);
           const uint64_t sfa_from = sfa_desc0 + static_cast<uint64_t>((s * 512) >> 4);
           const bool copy_b = copy_scales && (fresh || !resident), copy_a = copy_scales && per_stage_a;
           const uint32_t scaled0 = idesc | (a_id << 29) | (b_id << 4);  // the scale ids advance by one per K step
@@ -829,7 +861,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
       }
 #if FIM_PROBE_BUILD
-      if ((p.debug & 2048) && blockIdx.x == 0 && (kLaneLoop || lane == 0)) {
+      if ((p.debug & 8192) && blockIdx.x == 0 && (kLaneLoop || lane == 0)) {
         printf("mma warp: %lld K rounds, per round wait %.1f issue %.1f clk; per tile head %.1f clk over %u tiles; total %lld clk\n", c_rounds,
                double(c_wait) / double(c_rounds), double(c_issue) / double(c_rounds), double(c_tile) / double(tile_it), tile_it, clock64() - c_start);
       }
@@ -1205,6 +1237,7 @@ struct Plan {
   bool flat;
   bool pair;  // clusters of two CTAs driving one cta_group::2 instruction stream
   bool convert = false;    // bf16 activations, quantised on chip
+  bool resident_b = false; // the whole weight matrix stays in shared memory (one output-channel tile, small K)
   int fixed_epilogue = 0;  // kEpiLean | switches when one of the compile-time epilogues serves this call, else 0
   int out_h, out_w;
   size_t smem;
@@ -1300,6 +1333,20 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
   pl.smem = static_cast<size_t>(fixed) + static_cast<size_t>(pl.stages) * stage_bytes;
+  // One output-channel tile and a weight matrix that fits beside at least three activation stages: the weights (and their
+  // scale tiles) are copied once per CTA instead of once per tile and K step, which leaves the producer one copy per K
+  // step. Used for 64-wide tiles, where the producer's copies are what a K step waits for (3x3 64 -> 64: 377 -> 345 us);
+  // measured without gain at 128 and slower at 256 columns (1x1 128 -> 256: 163 -> 175 us), flag 4096 asks for it there.
+  if (pl.tiles_n == 1 && !pl.pair && !convert && g.cout <= bn && !(g_debug_flags & 2048) && (bn == 64 || (g_debug_flags & 4096))) {
+    const int all_b = k_iters * (bn * pl.block_k + scale_tiles_b(bn) * 512);
+    const int a_stage = kTileM * pl.block_k + 512;
+    if (fixed + all_b + 3 * a_stage <= kSmemLimit) {
+      pl.resident_b = true;
+      pl.stages = (kSmemLimit - fixed - all_b) / a_stage;
+      if (pl.stages > kMaxStages) pl.stages = kMaxStages;
+      pl.smem = static_cast<size_t>(fixed) + all_b + static_cast<size_t>(pl.stages) * a_stage;
+    }
+  }
   const int device_sms = sm_count();
   const int sms = g_max_ctas > 0 && g_max_ctas < device_sms ? g_max_ctas : device_sms;
   pl.ctas = pl.total_tiles < sms ? pl.total_tiles : sms;
@@ -1500,6 +1547,8 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   p.resident_k = sc.resident_k, p.n_major = sc.n_major;
   p.act_exponent = act_exponent;
   p.convert_static = convert && act_exponent != nullptr ? 1 : 0;
+  p.weights_resident = pl.resident_b ? 1 : 0;
+  p.b_slots = pl.resident_b ? g->kh * g->kw * (g->cin / pl.block_k) : pl.stages;
   p.act_scales = static_cast<const uint8_t*>(act_scales);
   p.act_scale_tiles = (g->cin / 32 + 3) / 4;
   p.weight_scales = static_cast<const uint8_t*>(weight_scales);

@@ -273,3 +273,50 @@ def test_int8_bias_epilogue_with_fixed_switches_agrees_with_the_general_one(ops)
         general = ops.int8_conv2d.get("sm100")(*args, *geometry)
     assert same_bytes(fixed, general)
     assert same_bytes(fixed.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry))
+
+
+@pytest.mark.parametrize("max_ctas", [0, 3, 11])
+@pytest.mark.parametrize("case", [(2, 24, 30, 64, 64, 3), (2, 24, 30, 128, 128, 3), (2, 37, 41, 128, 256, 1), (2, 37, 41, 256, 128, 1),
+                                  (2, 24, 30, 96, 64, 5)], ids=lambda c: "c%d-%d_k%d" % c[3:])
+def test_resident_weights_agree_with_streamed_weights(ops, case, max_ctas):
+    """A layer with one output-channel tile whose weight matrix fits in shared memory loads it once per CTA; flag 2048 streams
+    it through the stage ring per tile and K step instead. Same bytes for the dense output, for GELU + static requantisation
+    and (1x1) for GELU + dynamic requantisation, also where the last round of 256-wide tiles is split."""
+    b, h, w, cin, cout, k = case
+    x, ce, wq, we, bias = _mx_operands(b, h, w, cin, cout, k, seed=41)
+    geometry = (k, k, 1, 1, k // 2, k // 2, 1, 1)
+    fused = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(x, ce, wq, oracle.swizzle_32_4_4(we), bias)
+
+    def run():
+        dense = fused(*xd, *geometry)
+        oe = to_dev(oracle.static_block_exponent(torch.nn.functional.gelu(dense.float()).cpu()))
+        outs = [dense, fused(*xd, *geometry, act="gelu", out_exponent=oe)]
+        if k == 1:
+            outs += list(fused(*xd, *geometry, act="gelu", dynamic_out=True))
+        return outs
+
+    with conv_schedule(0, max_ctas, flags=4096):  # resident at every tile width (the default keeps it to 64-wide tiles)
+        resident = run()
+    with conv_schedule(0, max_ctas, flags=2048):
+        streamed = run()
+    for a, b_ in zip(resident, streamed):
+        assert same_bytes(a, b_)
+    assert rel_l2(resident[0], oracle.mxfp8_conv2d(x, ce, wq, we, bias, *geometry)) < 1e-3
+
+
+def test_int8_resident_weights_agree_with_streamed_weights(ops):
+    b, h, w = 3, 24, 20
+    g = torch.Generator().manual_seed(9)
+    x = torch.randint(-127, 128, (b, h, w, 64), dtype=torch.int8, generator=g)
+    weight = torch.randint(-127, 128, (128, 9 * 64), dtype=torch.int8, generator=g)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    a_scale, w_scale = torch.tensor(0.02), torch.rand(128, generator=g) * 0.01 + 0.001
+    bias = torch.randn(128, generator=g).to(BF16)
+    args = to_dev(x, weight, a_scale, w_scale, bias)
+    with conv_schedule(0, 4, flags=4096):
+        resident = ops.int8_conv2d.get("sm100")(*args, *geometry)
+    with conv_schedule(0, 4, flags=2048):
+        streamed = ops.int8_conv2d.get("sm100")(*args, *geometry)
+    assert same_bytes(resident, streamed)
+    assert same_bytes(resident.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry))
