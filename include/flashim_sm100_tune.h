@@ -24,7 +24,8 @@ extern "C" {
 void fim_conv_tune(int block_n, int max_ctas, int flags);
 
 /* Depthwise launches: `variant` selects the thread layout (0 = automatic; 1: four columns per lane, four warps, three
- * CTAs per SM; 2: five warps, two CTAs; 3: two columns per lane, eight warps, two CTAs). A probe build also honours, in `probe_flags`,
+ * CTAs per SM; 2: five warps, two CTAs; 3: two columns per lane, eight warps, two CTAs; 4: as 1 with four CTAs per SM, which
+ * leaves 128 registers per thread and a four-chunk ring). A probe build also honours, in `probe_flags`,
  * 1: skip the FMAs, 2: skip the epilogue, 4: skip the loads and the waits for them (results invalid). */
 void fim_dw_tune(int variant, int probe_flags);
 

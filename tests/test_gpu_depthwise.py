@@ -127,7 +127,7 @@ def test_layout_handling(ops):
     assert ops.depthwise5x5_act.explain(*to_dev(x, w, b), "relu")["sm100"] == "selected"
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 def test_every_thread_layout_gives_the_same_results(ops, variant):
     """The kernel is compiled for several thread layouts (columns per lane x warps per CTA); the launcher picks one by
     image width. Each is forced in turn: dense outputs must be the bits of the automatic choice (the FMA order per
