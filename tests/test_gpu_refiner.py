@@ -44,10 +44,13 @@ def test_block_and_level_match_the_oracle():
     assert all(set(v) == {"sm100"} for v in counts.values()), counts  # nothing left the CUDA path
     for x, level, ref, out in zip(pyramid, model.levels, refs, outs):
         block = level.blocks[0](x.to(DEV))
-        assert rel_l2(block, oracle.refiner_block_ext(x, ref["blocks"][0])) < 5e-3
+        # measured 1.0e-4 to 1.3e-4 (a block ends in a bf16 rounding); a flipped E4M3 code inside it costs a few 1e-4
+        assert rel_l2(block, oracle.refiner_block_ext(x, ref["blocks"][0])) < 1e-3
         want = oracle.refiner_level_ext(x, ref)
         assert out.shape == want.shape == (3, x.shape[1], x.shape[2], 32) and out.dtype == BF16
-        assert rel_l2(out[..., :4], want[..., :4]) < 3e-2
+        # measured 5e-4 to 2.8e-3 over seeds: six quantisers in a row, each flips about one code in a thousand against the
+        # oracle (whose fp32 sums run in another order), and the 4-channel head sums few terms
+        assert rel_l2(out[..., :4], want[..., :4]) < 1e-2
     # chunked and unchunked execution produce the same bits (samples are independent)
     model.chunk = 8
     again = model([p.to(DEV) for p in pyramid])
