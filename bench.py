@@ -406,7 +406,8 @@ class StackWorkload(Workload):
         self.inputs = self.staging = self.model.static_inputs(self.inputs)
         self.result_host = [torch.empty((images, s, s, 32), dtype=torch.bfloat16).pin_memory() for s, _ in LEVELS]
         blocks = len(self.model.levels[0].blocks)
-        self.launches_per_step = sum(-(-images // self.model.chunk) * (4 + 3 * blocks) for _ in LEVELS)
+        # per level and chunk: the projection, three kernels per block and the head (the quantisers run inside the convs)
+        self.launches_per_step = sum(-(-images // self.model.chunk) * (2 + 3 * blocks) for _ in LEVELS)
 
     def pair_input(self, level: int, pair: int) -> torch.Tensor:
         """The two direction-images of global pair `pair` at pyramid level `level`: bf16 [2, s, s, c] ~ N(0, 1)."""
