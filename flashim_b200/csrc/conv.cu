@@ -135,23 +135,33 @@ __device__ __forceinline__ uint32_t idesc_i8(int block_n, int block_m = kTileM) 
 constexpr uint32_t kGeluSmemBytes = (kGeluEntries * 4u + 1023u) / 1024u * 1024u;  // keeps the tiles behind it 1024-byte aligned
 
 // GELU of two bf16 values in one word, as bf16: the erf form torch evaluates (x * 0.5 * (1 + erf(x / sqrt 2)) in fp32,
-// rounded to bf16), looked up instead of computed. `table2` holds the shared-memory address of the copy of kGeluTable in
-// both halves: per magnitude a
+// rounded to bf16), looked up instead of computed. `table` locates the shared-memory copy of kGeluTable: per magnitude a
 // 16-bit delta for either sign; result magnitude = max(a + delta, 0), result sign = input sign. Magnitudes below
 // kGeluBase share entry 0 (half the value: the exponent drops by one; zero stays zero), those above the table share the
 // last entry (x itself for positive values, -0 for negative ones). Exact for every bf16 input except subnormals, which
 // become zero. Eleven instructions per pair and no MUFU; the arithmetic form costs about forty.
-__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, uint32_t table2) {
+struct GeluTable {
+  uint32_t low2;    // the low 16 bits of the table's shared-memory address, in both halves of the word
+  uint32_t window;  // its upper 16 bits: zero for a single CTA; in a cluster the CTA's rank sits up there
+};
+__device__ __forceinline__ GeluTable gelu_table_at(uint32_t smem_address) {
+  GeluTable t;
+  t.low2 = (smem_address & 0xFFFFu) * 0x00010001u;
+  t.window = smem_address & 0xFFFF0000u;
+  return t;
+}
+__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t r, const GeluTable& table) {
   constexpr uint32_t kNegBase = ((0x10000u - static_cast<uint32_t>(kGeluBase - 1)) & 0xFFFFu) * 0x00010001u;
   constexpr uint32_t kLast = static_cast<uint32_t>(kGeluEntries - 1) * 0x00010001u;
   const uint32_t a = r & 0x7FFF7FFFu;
   const uint32_t t = __viaddmin_s16x2_relu(a, kNegBase, kLast);  // clamp(a - (base - 1), 0, entries - 1) in each half
-  // both entry addresses with one multiply-add: the table sits in the first 64 KB of the shared window, so an address
-  // fits a half and neither half carries into the other
-  const uint32_t at = t * 4u + table2;
+  // both entry addresses with one multiply-add: the table sits in the first 64 KB of the CTA's shared window, so the low
+  // 16 bits of an address fit a half and neither half carries into the other; a byte permute then puts each half under
+  // the window's upper bits
+  const uint32_t at = t * 4u + table.low2;
   uint32_t w0, w1, negative;
-  asm("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(at & 0xFFFFu));
-  asm("ld.shared.b32 %0, [%1];" : "=r"(w1) : "r"(at >> 16));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(__byte_perm(at, table.window, 0x7610)));
+  asm("ld.shared.b32 %0, [%1];" : "=r"(w1) : "r"(__byte_perm(at, table.window, 0x7632)));
   // byte 0 of `negative` = 0xFF when the low value is negative, byte 1 the same for the high value (sign replication of
   // bytes 1 and 3); each byte steers two selector nibbles: bytes 2-3 of w0 / w1 (the delta for negative values) or 0-1
   asm("prmt.b32 %0, %1, %2, 0x00B9;" : "=r"(negative) : "r"(r), "r"(0u));
@@ -294,7 +304,7 @@ __device__ __forceinline__ void round_chunk(const ConvParams& p, const EpilogueS
 // output format.
 template <bool INT8>
 __device__ __forceinline__ void finish_chunk(const ConvParams& p, const EpilogueSwitches& sw, uint32_t (&r)[16], int n, size_t pixel,
-                                             int b, int y, int x, bool valid, uint32_t gelu_table, uint32_t (&w)[16]) {
+                                             int b, int y, int x, bool valid, const GeluTable& gelu_table, uint32_t (&w)[16]) {
   const bool has_res = sw.has_residual;
   if (sw.act == kActGelu) {
 #pragma unroll
@@ -458,7 +468,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   // [GELU table][stages x A][stages x B][output panels][stages x scale tiles B][stages x scale tile A][static A scale tiles][bias]
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t panel_bytes = 4096u * p.out_elem;
-  const uint32_t smem_gelu = base;  // kGeluTable first, when the epilogue applies GELU: its addresses must fit 16 bits
+  const uint32_t smem_gelu = base;  // kGeluTable first, when the epilogue applies GELU: within 64 KB of the window's start
   const uint32_t smem_a = base + (p.act == kActGelu ? kGeluSmemBytes : 0u);
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + static_cast<uint32_t>(p.b_slots) * kBBytes;
@@ -941,7 +951,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
       const uint32_t row_at = static_cast<uint32_t>(lane) * kPitch + ((((static_cast<uint32_t>(lane) * kPitch) >> 7) & (kSlots - 1)) << 4);
       const uint32_t bias_at = smem_bias + static_cast<uint32_t>(group * kGroupColumns) * 4u;
       const uint32_t lane_tmem = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + group * kGroupColumns;
-      const uint32_t gelu2 = smem_gelu * 0x00010001u;
+      const GeluTable gelu2 = gelu_table_at(smem_gelu);
       const int row = quarter * 32 + lane;
       const int scale_tiles = ((p.cout >> 5) + 3) >> 2;         // 4-group tiles per row tile of the output scales
       const uint32_t scale_at = static_cast<uint32_t>(lane * 16 + quarter * 4);
@@ -1196,7 +1206,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           const int n = n0 + cgroup * kGroupColumns + g * 32;
           if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
-          finish_chunk<INT8>(p, sw, q[g], n, pixel, b, y, x, valid, smem_gelu * 0x00010001u, w);
+          finish_chunk<INT8>(p, sw, q[g], n, pixel, b, y, x, valid, gelu_table_at(smem_gelu), w);
           const uint32_t panel = take_panel();
           stage_row<16>(panel, panel_row, sw.out_elem, w);
           send_panel(panel, n);

@@ -320,3 +320,31 @@ def test_int8_resident_weights_agree_with_streamed_weights(ops):
         streamed = ops.int8_conv2d.get("sm100")(*args, *geometry)
     assert same_bytes(resident, streamed)
     assert same_bytes(resident.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry))
+
+
+def test_gelu_epilogue_inside_cta_pairs(ops):
+    """GELU looks its values up in a shared-memory table through 16-bit address halves; inside a cluster the second CTA's
+    shared-memory addresses carry its rank in their upper bits, which the look-up has to put back. INT8 pairs are the
+    default for 256-wide tiles (an int8_linear with GELU on 640 rows reaches them); the MXFP8 pair runs under flag 128."""
+    g = torch.Generator().manual_seed(12)
+    a = torch.randint(-127, 128, (640, 1024), dtype=torch.int8, generator=g)
+    w = torch.randint(-127, 128, (256, 1024), dtype=torch.int8, generator=g)
+    a_scale, w_scale = torch.tensor(0.01), torch.rand(256, generator=g) * 0.002 + 0.0002
+    bias = torch.randn(256, generator=g).to(BF16)
+    with conv_schedule(0, 4) as capped:
+        assert capped.schedule((1, 1, 640, 1024, 256, 1, 1, 0, 1), int8=True)["pairs"] == 1
+        got = ops.int8_linear.get("sm100")(*to_dev(a, w, a_scale, w_scale, bias), gelu=True)
+    assert same_bytes(got.cpu(), oracle.int8_linear(a, w, a_scale, w_scale, bias, gelu=True))
+
+    x, ce, wq, we, bias = _mx_operands(3, 24, 40, 256, 256, 3, seed=14)
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    fused = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(x, ce, wq, oracle.swizzle_32_4_4(we), bias)
+    with conv_schedule(0, 0, 64):
+        dense = fused(*xd, *geometry, act="gelu")
+        oe = to_dev(oracle.static_block_exponent(dense.cpu().float()))
+        single = fused(*xd, *geometry, act="gelu", out_exponent=oe)
+    with conv_schedule(0, 6, 128) as paired:
+        assert paired.schedule((3, 24, 40, 256, 256, 3, 3, 1, 1))["pairs"] == 1
+        assert same_bytes(fused(*xd, *geometry, act="gelu"), dense)
+        assert same_bytes(fused(*xd, *geometry, act="gelu", out_exponent=oe), single)
