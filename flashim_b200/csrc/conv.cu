@@ -435,7 +435,7 @@ __global__ void __launch_bounds__(CONVERT ? kConvertThreads : kThreads, 1)
 conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
             const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sfb_map,
             const __grid_constant__ CUtensorMap sfa_map, const __grid_constant__ CUtensorMap out_warp_map, const ConvParams p) {
-  static_assert(!PAIR || BN == 256, "CTA pairs are built for 256-wide tiles");
+  static_assert(!PAIR || BN == 256 || (BN == 128 && FMT == kFmtMx), "CTA pairs are built for 256-wide tiles (and 128-wide block-scaled ones)");
   static_assert(!CONVERT || (FMT == kFmtMx && !PAIR && BK == 128), "the converter feeds flat block-scaled layers");
   constexpr int kBlockThreads = CONVERT ? kConvertThreads : kThreads;
   static_assert((EPI & kEpiLean) == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the short epilogues serve flat block-scaled layers");
@@ -1323,6 +1323,14 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   // its loads are zero-filled and its stores clipped). The block-scaled form is correct too but measured slower than
   // single CTAs (its scale copies serialise the pair's tensor pipes): it only runs when asked for (tuning flag 128).
   pl.pair = bn == 256 && row_tiles >= 2 && !(g_debug_flags & 64) && (int8 || (g_debug_flags & 128)) && !convert;
+  // A 128-wide block-scaled tile moves as many operand bytes through shared memory per MMA as the tensor pipe takes
+  // twice as fast; a pair halves the weight bytes per CTA (64 rows each). Worth it for a spatial conv with many tiles
+  // (3x3 128 -> 128 at 400 x 400: 120 -> 111 us), not for a small one or a flat 1x1 layer, whose short epilogue serves
+  // single CTAs only; flag 16384 forces it.
+  if (bn == 128 && scaled && pl.block_k == 128 && row_tiles >= 2 && !convert && !(g_debug_flags & 64) &&
+      ((g_debug_flags & 16384) || (!pl.flat && row_tiles >= 8LL * sm_count()))) {
+    pl.pair = true;
+  }
   const long long total = (pl.pair ? (row_tiles + 1) / 2 : row_tiles) * pl.tiles_n;
   if (total > 0x3fffffffLL) return kUnsupported;
   pl.total_tiles = static_cast<int>(total);
@@ -1461,6 +1469,12 @@ int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cud
   if constexpr (FMT == kFmtI8 && BN == 256) {
     if (pl.fixed_epilogue == kEpiFixed && pl.pair && pl.block_k == 128) {
       return launch_conv<FMT, BN, 128, true, kEpiFixed>(maps, p, pl, stream);
+    }
+  }
+  if constexpr (BN == 128 && FMT == kFmtMx) {
+    if (pl.pair) {
+      if (pl.fixed_epilogue == kGeluStatic) return launch_conv<FMT, BN, 128, true, kGeluStatic>(maps, p, pl, stream);
+      return launch_conv<FMT, BN, 128, true>(maps, p, pl, stream);
     }
   }
   if constexpr (BN == 256 && FMT != kFmtBf16) {
@@ -1616,7 +1630,8 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
     const uint64_t k_total = static_cast<uint64_t>(g->kh) * g->kw * g->cin;
     const uint64_t dims[2] = {k_total, static_cast<uint64_t>(g->cout)};
     const uint64_t strides[1] = {k_total};
-    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.block_n < 128 ? pl.block_n : 128)};  // a pair's CTA loads 128 rows too
+    // rows per copy: a whole narrow tile, 128 rows of a wide one, or the half of the tile a CTA of a pair holds
+    const uint32_t box[2] = {static_cast<uint32_t>(pl.block_k), static_cast<uint32_t>(pl.pair ? pl.block_n / 2 : (pl.block_n < 128 ? pl.block_n : 128))};
     const int rcm = make_tensor_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weight, dims, strides, box, swizzle_for_bytes(pl.block_k));
     if (rcm != kOk) return rcm;
   }

@@ -19,7 +19,8 @@ extern "C" {
  * output panel and one store (as the spatial convs do) instead of one per warp, 1024 sends the 1x1 layers of a refiner
  * block through the general epilogue instead of the ones fixed at compile time, 2048 streams the weights of a layer through
  * the stage ring even where they would fit in shared memory for the whole launch, 4096 keeps them resident for every tile
- * width (by default only 64-wide tiles do). A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
+ * width (by default only 64-wide tiles do), 16384 runs 128-wide block-scaled tiles as CTA pairs whatever the size of the
+ * layer (by default large spatial convs do; 64 forbids pairs altogether). A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
  * bits 1, 2, 4, 8 (skip activation loads / weight loads / stores / scale copies), which make results invalid. */
 void fim_conv_tune(int block_n, int max_ctas, int flags);
 

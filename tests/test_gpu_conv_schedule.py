@@ -348,3 +348,33 @@ def test_gelu_epilogue_inside_cta_pairs(ops):
         assert paired.schedule((3, 24, 40, 256, 256, 3, 3, 1, 1))["pairs"] == 1
         assert same_bytes(fused(*xd, *geometry, act="gelu"), dense)
         assert same_bytes(fused(*xd, *geometry, act="gelu", out_exponent=oe), single)
+
+
+@pytest.mark.parametrize("max_ctas", [2, 6])
+@pytest.mark.parametrize("shape,cout", [((3, 24, 20), 128), ((2, 17, 19), 384)])
+def test_mxfp8_pairs_of_128_wide_tiles_agree_with_single_ctas(ops, shape, cout, max_ctas):
+    """Large spatial convs run their 128-wide block-scaled tiles as CTA pairs (64 weight rows per CTA); flag 16384 forces
+    the pair on a small problem, flag 64 forbids it. Same bytes with bias, with GELU + static requantisation (the
+    epilogue whose switches are fixed at compile time) and with ReLU + residual; an odd number of row tiles leaves the
+    last pair half empty, three channel tiles reload the resident weight scales."""
+    b, h, w = shape
+    x, ce, wq, we, bias = _mx_operands(b, h, w, 128, cout, 3, seed=23)
+    res = to_dev(torch.randn(b, h, w, cout, generator=torch.Generator().manual_seed(2)).to(BF16))
+    geometry = (3, 3, 1, 1, 1, 1, 1, 1)
+    fused = ops.mxfp8_conv2d_fused.get("sm100")
+    xd = to_dev(x, ce, wq, oracle.swizzle_32_4_4(we), bias)
+
+    def run(oe):
+        return (fused(*xd, *geometry), fused(*xd, *geometry, act="gelu", out_exponent=oe),
+                fused(*xd, *geometry, act="relu", residual=res))
+
+    with conv_schedule(0, max_ctas, 64) as single:
+        assert single.schedule((b, h, w, 128, cout, 3, 3, 1, 1))["pairs"] == 0
+        oe = to_dev(oracle.static_block_exponent(torch.nn.functional.gelu(fused(*xd, *geometry).float()).cpu()))
+        want = run(oe)
+    with conv_schedule(0, max_ctas, 16384) as paired:
+        assert paired.schedule((b, h, w, 128, cout, 3, 3, 1, 1))["pairs"] == 1
+        got = run(oe)
+    for a, b_ in zip(got, want):
+        assert same_bytes(a, b_)
+    assert rel_l2(got[0], oracle.mxfp8_conv2d(x, ce, wq, we, bias, *geometry)) < 1e-3
