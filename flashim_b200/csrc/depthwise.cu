@@ -40,15 +40,16 @@ __device__ __forceinline__ void store_if(uint16_t* at, uint16_t v, uint32_t on) 
 // channel, operands read from the halves of the packed words as they arrive from shared memory) instead of packed fp32
 // FMAs on unpacked values: the same bits (a bf16 product is exact in fp32), no unpacking, and the weights stay packed
 // (25 registers instead of 50). Measured per epilogue at 8x400x400x128: bf16 outputs 7-10 % faster (GELU 255 -> 238 us,
-// ReLU 205 -> 185), ReLU -> MXFP8 7 % faster, GELU -> MXFP8 unchanged and ReLU -> INT8 4 % slower (their long epilogues
-// are short of issue slots, and this form issues two instructions where the packed one issues one): those two keep the
-// packed form.
+// ReLU 205 -> 185), ReLU -> MXFP8 7 % faster, GELU -> MXFP8 unchanged at first (its long epilogue is short of issue slots,
+// and this form issues two instructions where the packed one issues one) and 8 % faster (329 -> 304 us) once the
+// registers the packed weights free hold the coefficient pairs of a packed GELU polynomial; ReLU -> INT8 4 % slower: it
+// keeps the packed fp32 form.
 #ifndef FIM_DW_MIXED_FMA
 #define FIM_DW_MIXED_FMA 1
 #endif
-__host__ __device__ constexpr bool mixed_fma_for(int mode, int act, int min_ctas) {
+__host__ __device__ constexpr bool mixed_fma_for(int mode, int min_ctas) {
   // (four CTAs per SM leave 128 registers per thread: only the packed weights fit)
-  return FIM_DW_MIXED_FMA != 0 && (min_ctas >= 4 || mode == 0 /* bf16 out */ || (mode == 1 /* MXFP8 out */ && act != kActGelu));
+  return FIM_DW_MIXED_FMA != 0 && (min_ctas >= 4 || mode != 2 /* every output but INT8 */);
 }
 
 // d = a * w + c per half of the packed bf16x2 words a and w, in fp32 (one rounding each)
@@ -100,9 +101,31 @@ __device__ __forceinline__ float gelu_phi(float x) {
   return fmaf(u, p, fmaxf(x, 0.0f));
 }
 
-template <int ACT>
+// The same on a pair of values with packed FMAs (one issue slot per Horner step of both); the coefficient pairs then live
+// in registers, which only the kernels with packed weights have to spare.
+__device__ __forceinline__ uint64_t gelu_phi2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t u = pack2(-fabsf(x0), -fabsf(x1));
+  uint64_t q = pack2(1.793454771359393e-06f, 1.793454771359393e-06f);
+  q = fma2(q, u, pack2(6.090417082305066e-05f, 6.090417082305066e-05f));
+  q = fma2(q, u, pack2(0.000926029053516686f, 0.000926029053516686f));
+  q = fma2(q, u, pack2(0.00849375780671835f, 0.00849375780671835f));
+  q = fma2(q, u, pack2(0.053937844932079315f, 0.053937844932079315f));
+  q = fma2(q, u, pack2(-0.45848050713539124f, -0.45848050713539124f));
+  q = fma2(q, u, pack2(1.1512467861175537f, 1.1512467861175537f));
+  q = fma2(q, u, pack2(-0.9999954700469971f, -0.9999954700469971f));
+  float q0, q1, p0, p1;
+  unpack2(q, q0, q1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(q0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(q1));
+  return fma2(u, pack2(p0, p1), pack2(fmaxf(x0, 0.0f), fmaxf(x1, 0.0f)));
+}
+
+template <int ACT, bool PACKED_GELU = false>
 __device__ __forceinline__ uint64_t activate2(uint64_t v) {
   if (ACT == kActNone) return v;
+  if (ACT == kActGelu && PACKED_GELU) return gelu_phi2(v);
   float lo, hi;
   unpack2(v, lo, hi);
   if (ACT == kActGelu) return pack2(gelu_phi(lo), gelu_phi(hi));
@@ -112,13 +135,13 @@ __device__ __forceinline__ uint64_t activate2(uint64_t v) {
 // Finish one output row of this lane: bias, activation and the epilogue of MODE for the lane's COLS pixels.
 // `out_row` points at this lane's channel pair of pixel (row, x0) in units of output pairs; `pixel0` is that pixel's
 // index in the batch; `cols_ok` has bit j set when column x0 + j exists (0 for a lane without channels).
-template <int MODE, int ACT, int COLS>
+template <int MODE, int ACT, int COLS, bool PACKED_GELU = false>
 __device__ __forceinline__ void emit_row(const DwParams& p, const uint64_t (&acc)[COLS], uint64_t bias2, void* out_row,
                                          size_t pixel0, int c, uint32_t cols_ok, const Int8Quantizer& int8, int lane) {
   const size_t pair_stride = static_cast<size_t>(p.channels >> 1);
   uint64_t v[COLS];
 #pragma unroll
-  for (int j = 0; j < COLS; ++j) v[j] = activate2<ACT>(add2(acc[j], bias2));
+  for (int j = 0; j < COLS; ++j) v[j] = activate2<ACT, PACKED_GELU>(add2(acc[j], bias2));
   if (MODE == kOutBf16) {
     uint32_t* out = static_cast<uint32_t*>(out_row);
 #pragma unroll
@@ -213,7 +236,7 @@ struct CopyCursor {
 // also issues the copies.
 template <int MODE, int ACT, int COLS, int WARPS, int MIN_CTAS, bool PROBE>
 __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __grid_constant__ CUtensorMap in_map, const DwParams p) {
-  constexpr bool kMixedFma = mixed_fma_for(MODE, ACT, MIN_CTAS);
+  constexpr bool kMixedFma = mixed_fma_for(MODE, MIN_CTAS);
   constexpr int kStages = ring_stages(MIN_CTAS);
   constexpr int kTileCols = WARPS * COLS;
   constexpr uint32_t kRowBytes = (kTileCols + 4) * kChannels * 2;
@@ -442,7 +465,7 @@ __global__ void __launch_bounds__(32 * WARPS, MIN_CTAS) dw5x5_kernel(const __gri
               uint64_t done[COLS];
 #pragma unroll
               for (int j = 0; j < COLS; ++j) done[j] = pack2(facc[(ph + 1) % 5][j][0], facc[(ph + 1) % 5][j][1]);
-              emit_row<MODE, ACT, COLS>(p, done, bias2, out_row, pixel0, c, valid ? cols_ok : 0u, int8_scale, lane);
+              emit_row<MODE, ACT, COLS, true>(p, done, bias2, out_row, pixel0, c, valid ? cols_ok : 0u, int8_scale, lane);
             } else {
               emit_row<MODE, ACT, COLS>(p, acc[(ph + 1) % 5], bias2, out_row, pixel0, c, valid ? cols_ok : 0u, int8_scale, lane);
             }
