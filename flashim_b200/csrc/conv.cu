@@ -216,17 +216,18 @@ __device__ __forceinline__ void load_bias_pairs(uint32_t bias_at, int i, uint64_
   asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(bias_at + i * 16));
 }
 
-// bf16x2 words r[16] -> E4M3 codes of value * 2**-e (e in [-127, 127]), four per output word. The scaling is one
+// bf16x2 words r[IN] -> E4M3 codes of value * 2**-e (e in [-127, 127]), four per output word. The scaling is one
 // mixed-precision FMA per value (fp32 = bf16 * bf16 + -0, exact: a bf16 times a power of two; the addend -0 keeps the
 // sign of a zero product), which reads the halves of the packed word directly and runs at the full fp32 rate; unpacking
 // with shifts and masks first costs two half-rate integer instructions per pair.
-template <int WORDS>  // only the first eight words of `w` are written
-__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[16], int e, uint32_t (&w)[WORDS]) {
+template <int IN, int WORDS>  // IN bf16x2 words in, IN / 2 words of `w` written
+__device__ __forceinline__ void scale_to_e4m3(const uint32_t (&r)[IN], int e, uint32_t (&w)[WORDS]) {
+  static_assert(IN % 2 == 0 && WORDS >= IN / 2, "four codes per output word");
   // 2**-e as bf16 bits in both halves; 2**-127 (e = 127) is a bf16 subnormal, which the instruction takes as it is
   const uint32_t inv16 = e == 127 ? 0x0040u : static_cast<uint32_t>(127 - e) << 7;
   const uint32_t inv = inv16 * 0x00010001u;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < IN / 2; ++i) {
     float a, b, c, d;
     asm("{\n\t.reg .b16 xl, xh, yl, yh, s, t;\n\t"
         "mov.b32 {xl, xh}, %4;\n\tmov.b32 {yl, yh}, %5;\n\tmov.b32 {s, t}, %6;\n\t"
@@ -901,24 +902,21 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           uint32_t w[8];
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(from + row * 256 + piece * 32));
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(from + row * 256 + piece * 32 + 16));
-          float v[16];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) v[2 * k] = bf16_lo(w[k]), v[2 * k + 1] = bf16_hi(w[k]);
+          // the arithmetic of the conv epilogue's requantiser, on the packed words (the same bits as the standalone
+          // quantisers, which work in fp32: a bf16 maximum, an exact power-of-two scaling)
           int e = static_e;
           if (!p.convert_static) {
-            float amax = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) amax = fmaxf(amax, fabsf(v[k]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            e = e8m0_exponent(amax);
+            uint32_t m = bf16x2_absmax(bf16x2_absmax(bf16x2_absmax(w[0], w[1]), bf16x2_absmax(w[2], w[3])),
+                                       bf16x2_absmax(bf16x2_absmax(w[4], w[5]), bf16x2_absmax(w[6], w[7])));
+            uint32_t top = max(m & 0x7FFFu, (m >> 16) & 0x7FFFu);
+            top = max(top, __shfl_xor_sync(0xffffffffu, top, 1));
+            e = e8m0_exponent_bits(top << 16);
             if ((piece & 1) == 0) {
               asm volatile("st.shared.u8 [%0], %1;" ::"r"(scale_tile + (row & 31) * 16 + (row >> 5) * 4 + group), "r"(e + 127) : "memory");
             }
           }
-          const float inv = exp2_int(-e);
           uint32_t q[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) q[k] = e4m3x4(v[4 * k] * inv, v[4 * k + 1] * inv, v[4 * k + 2] * inv, v[4 * k + 3] * inv);
+          scale_to_e4m3(w, e, q);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(to + row * 128 + ((piece ^ (row & 7)) << 4)), "r"(q[0]), "r"(q[1]),
                        "r"(q[2]), "r"(q[3])
                        : "memory");
