@@ -407,7 +407,9 @@ class StackWorkload(Workload):
         self.result_host = [torch.empty((images, s, s, 32), dtype=torch.bfloat16).pin_memory() for s, _ in LEVELS]
         blocks = len(self.model.levels[0].blocks)
         # per level and chunk: the projection, three kernels per block and the head (the quantisers run inside the convs)
-        self.launches_per_step = sum(-(-images // self.model.chunk) * (2 + 3 * blocks) for _ in LEVELS)
+        # (a projection wider than one 256-column tile is fed by the standalone quantiser: one more launch)
+        self.launches_per_step = sum(-(-images // self.model.chunk) * (2 + 3 * blocks + (1 if c > 256 or c % 128 else 0) + (1 if c % 128 else 0))
+                                     for _, c in LEVELS)
 
     def pair_input(self, level: int, pair: int) -> torch.Tensor:
         """The two direction-images of global pair `pair` at pyramid level `level`: bf16 [2, s, s, c] ~ N(0, 1)."""
