@@ -12,16 +12,21 @@ extern "C" {
 
 /* Overrides for the following conv launches of this process (all 0 = automatic): `block_n` forces the output-channel
  * tile (64 / 128 / 256); `max_ctas` caps the persistent grid, so that a small problem makes every CTA walk many tiles;
- * `flags` selects between schedules that all produce the same bits: 16 keeps the last partial round of tiles at full
- * width, 64 disables CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; default for INT8 with
- * 256-wide tiles), 128 enables them for MXFP8 too, 256 reloads the weight scales for every tile instead of keeping the
- * first K iterations resident in tensor memory, 512 makes the four warps of an epilogue group of a 1x1 conv share one
- * output panel and one store (as the spatial convs do) instead of one per warp, 1024 sends the 1x1 layers of a refiner
- * block through the general epilogue instead of the ones fixed at compile time, 2048 streams the weights of a layer through
- * the stage ring even where they would fit in shared memory for the whole launch, 4096 keeps them resident for every tile
- * width (by default only 64-wide tiles do), 16384 runs 128-wide block-scaled tiles as CTA pairs whatever the size of the
- * layer (by default large spatial convs do; 64 forbids pairs altogether). A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours
- * bits 1, 2, 4, 8 (skip activation loads / weight loads / stores / scale copies), which make results invalid. */
+ * `flags` selects between schedules that all produce the same bits:
+ *    16  keeps the last partial round of tiles at full width;
+ *    32  lets the epilogue poll for its accumulator without sleeping between polls;
+ *    64  disables CTA pairs (clusters of two CTAs on one cta_group::2 instruction stream; the default for INT8 with
+ *        256-wide tiles and for large spatial block-scaled convs with 128-wide tiles);
+ *   128  enables pairs for block-scaled 256-wide tiles too;
+ *   256  reloads the weight scales for every tile instead of keeping the first K iterations resident in tensor memory;
+ *   512  makes the four warps of an epilogue group of a 1x1 conv share one output panel and one store (as the spatial
+ *        convs do) instead of one per warp;
+ *  1024  sends every call through the general epilogue instead of the ones whose switches are fixed at compile time;
+ *  2048  streams the weights of a layer through the stage ring even where they are kept in shared memory by default;
+ *  4096  keeps them resident for every tile width where they fit (by default only 64-wide tiles do);
+ * 16384  runs 128-wide block-scaled tiles as CTA pairs whatever the size of the layer.
+ * A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours bits 1, 2, 4, 8 (skip activation loads / weight
+ * loads / stores / scale copies), which make results invalid, and 8192 (the MMA warp of CTA 0 prints its cycle counts). */
 void fim_conv_tune(int block_n, int max_ctas, int flags);
 
 /* Depthwise launches: `variant` selects the thread layout (0 = automatic; 1: four columns per lane, four warps, three
