@@ -1323,10 +1323,11 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   pl.pair = bn == 256 && row_tiles >= 2 && !(g_debug_flags & 64) && (int8 || (g_debug_flags & 128)) && !convert;
   // A 128-wide block-scaled tile moves as many operand bytes through shared memory per MMA as the tensor pipe takes
   // twice as fast; a pair halves the weight bytes per CTA (64 rows each). Worth it for a spatial conv with many tiles
-  // (3x3 128 -> 128 at 400 x 400: 120 -> 111 us), not for a small one or a flat 1x1 layer, whose short epilogue serves
-  // single CTAs only; flag 16384 forces it.
+  // (3x3 128 -> 128 at 400 x 400: 118 -> 107 us), not for a small one, not for a flat 1x1 layer, whose short epilogue
+  // serves single CTAs only, and not with a GELU epilogue (117 -> 123 us: the two epilogues of a pair release one shared
+  // accumulator barrier, and the heavier they are the longer the MMAs wait for the slower one); flag 16384 forces it.
   if (bn == 128 && scaled && pl.block_k == 128 && row_tiles >= 2 && !convert && !(g_debug_flags & 64) &&
-      ((g_debug_flags & 16384) || (!pl.flat && row_tiles >= 8LL * sm_count()))) {
+      ((g_debug_flags & 16384) || (!pl.flat && !gelu && row_tiles >= 8LL * sm_count()))) {
     pl.pair = true;
   }
   const long long total = (pl.pair ? (row_tiles + 1) / 2 : row_tiles) * pl.tiles_n;
