@@ -403,6 +403,36 @@ def _(x, weight, a_scale, w_scale, bias, residual, out_scale, kh, kw, sh, sw, ph
     return x.new_empty((b, ho, wo, weight.shape[0]), dtype=_OUT_DTYPES[out_mode])
 
 
+@torch.library.custom_op("flashim_b200::int8_conv2d_maxpool", mutates_args=())
+def int8_conv2d_maxpool_launch(
+    x: Tensor, weight: Tensor, a_scale: Tensor, w_scale: Tensor, bias: Tensor | None, out_scale: Tensor, kh: int, kw: int,
+    sh: int, sw: int, ph: int, pw: int, dh: int, dw: int, act: int,
+) -> tuple[Tensor, Tensor]:
+    """One launch for both outputs of ``int8_conv2d_maxpool``: the bf16 conv output and, taken from the same tiles before
+    they leave shared memory, its 2x2 max pool as INT8 codes."""
+    x, weight, w_scale, bias = (_aligned(t) for t in (x, weight, w_scale, bias))
+    b, h, w, _ = x.shape
+    cout = weight.shape[0]
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
+    out = torch.empty((b, ho, wo, cout), device=x.device, dtype=torch.bfloat16)
+    pooled = torch.empty((b, ho // 2, wo // 2, cout), device=x.device, dtype=torch.int8)
+    geometry = _geometry(x, cout, kh, kw, sh, sw, ph, pw, dh, dw)
+    epilogue = _epilogue(bias, None, act, _native.OUT_BF16, out_scale=out_scale)
+    code = _native.library().fim_int8_conv2d_maxpool(
+        x.data_ptr(), weight.data_ptr(), _ptr(a_scale), _ptr(w_scale), ctypes.byref(geometry), ctypes.byref(epilogue),
+        out.data_ptr(), pooled.data_ptr(), status_word(x.device).data_ptr(), _stream(x))
+    _finish(code, f"int8_conv2d_maxpool {tuple(x.shape)} -> {cout} k{kh}x{kw} s{sh}x{sw}", x.device)
+    return out, pooled
+
+
+@int8_conv2d_maxpool_launch.register_fake
+def _(x, weight, a_scale, w_scale, bias, out_scale, kh, kw, sh, sw, ph, pw, dh, dw, act):
+    b, h, w, _ = x.shape
+    ho, wo = _out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)
+    return (x.new_empty((b, ho, wo, weight.shape[0]), dtype=torch.bfloat16),
+            x.new_empty((b, ho // 2, wo // 2, weight.shape[0]), dtype=torch.int8))
+
+
 @torch.library.custom_op("flashim_b200::bf16_conv2d", mutates_args=())
 def bf16_conv2d_launch(x: Tensor, weight: Tensor, bias: Tensor | None, residual: Tensor | None, kh: int, kw: int, sh: int, sw: int,
                        ph: int, pw: int, dh: int, dw: int, act: int) -> Tensor:
@@ -618,10 +648,15 @@ def register(ops=None, device_spec=None, feature=None) -> None:
 
         @ops.int8_conv2d_maxpool.register("sm100", device=spec, requires=requires, priority=3, when=pool_when)
         def int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, *, relu=False, out_scale):
-            # two launches: the conv writes its bf16 output (which the caller keeps), the pool reads it back (from L2 while
-            # it fits) and writes a quarter as many int8 codes
-            out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
             scale = out_scale.to(device=x.device, dtype=torch.float32).reshape(1)
+            b, h, w, _ = x.shape
+            if min(_out_size(h, kh, ph, dh, sh), _out_size(w, kw, pw, dw, sw)) >= 2 and x.shape[-1] % 64 == 0:
+                # one launch: the epilogue pools each bf16 tile while it lies in shared memory for its own store
+                return int8_conv2d_maxpool_launch(
+                    x, weight, a_scale.float().reshape(1), w_scale.float().contiguous(), None if bias is None else bias.contiguous(),
+                    scale, kh, kw, sh, sw, ph, pw, dh, dw, act_code["relu" if relu else "none"])
+            # an output without a whole 2x2 window, or 32 / 96 / ... input channels: the conv, then the pooling pass
+            out = int8_conv2d(x, weight, a_scale, w_scale, bias, kh, kw, sh, sw, ph, pw, dh, dw, relu=relu)
             return out, maxpool2_quantize_int8(out, scale)
 
     if hasattr(ops, "int8_conv2d_accumulators"):

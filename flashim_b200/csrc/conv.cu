@@ -91,6 +91,7 @@ struct ConvParams {
   int weights_resident;      // 1: the layer's whole weight matrix is loaded once per CTA and stays in shared memory
   int convert_static;        // bf16 activations: 1 = quantise with act_exponent, 0 = per pixel and 32 channels on the fly
   int warp_panels;           // flat 1x1 convs: every epilogue warp stages and stores its own 32 rows (no barrier between warps)
+  int pool;                  // INT8, bf16 output: the 2x2 max pool of the output also leaves the epilogue, as INT8 codes (out_scale)
   int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no activation loads, 2 = no weight loads, 4 = no output stores, 8 = no scale copies
 };
 
@@ -180,8 +181,10 @@ __device__ __forceinline__ uint32_t idesc_bf16(int block_n, int block_m = kTileM
 // panels per group), which removes the tests, the parameter loads and the register moves at their joins: about a third
 // of the epilogue's instructions. kEpiLean = the shorter epilogue of a flat block-scaled 1x1 layer (bias present; bf16
 // output, or E4M3 with per-pixel scales when kEpiDynamic; GELU when kEpiGelu; a dense bf16 residual over every output
-// channel when kEpiResidual): the layers a refiner block is made of.
-constexpr int kEpiGelu = 1, kEpiDynamic = 2, kEpiResidual = 4, kEpiLean = 8, kEpiFixed = 16, kEpiStatic = 32;
+// channel when kEpiResidual): the layers a refiner block is made of. kEpiPool = the general epilogue of an INT8 conv with
+// bf16 output that also writes the 2x2 max pool of its tiles as INT8 codes.
+constexpr uint32_t kPoolPanelBytes = 1024;  // 32 pooled pixels x 32 INT8 channels
+constexpr int kEpiGelu = 1, kEpiDynamic = 2, kEpiResidual = 4, kEpiLean = 8, kEpiFixed = 16, kEpiStatic = 32, kEpiPool = 64;
 
 struct EpilogueSwitches {
   int act, out_mode;
@@ -439,6 +442,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   static_assert(!PAIR || BN == 256 || (BN == 128 && FMT == kFmtMx), "CTA pairs are built for 256-wide tiles (and 128-wide block-scaled ones)");
   static_assert(!CONVERT || (FMT == kFmtMx && !PAIR && BK == 128), "the converter feeds flat block-scaled layers");
   constexpr int kBlockThreads = CONVERT ? kConvertThreads : kThreads;
+  static_assert((EPI & kEpiPool) == 0 || (FMT == kFmtI8 && EPI == kEpiPool), "the pooled output belongs to the INT8 conv's general epilogue");
   static_assert((EPI & kEpiLean) == 0 || (FMT == kFmtMx && !PAIR && BN >= 128), "the short epilogues serve flat block-scaled layers");
   constexpr bool INT8 = FMT == kFmtI8;
   constexpr bool SCALED = FMT == kFmtMx;  // operands carry E8M0 block scales
@@ -473,7 +477,8 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   const uint32_t smem_a = base + (p.act == kActGelu ? kGeluSmemBytes : 0u);
   const uint32_t smem_b = smem_a + p.stages * kABytes;
   const uint32_t smem_out = smem_b + static_cast<uint32_t>(p.b_slots) * kBBytes;
-  const uint32_t smem_sfb = smem_out + kPanelGroups * p.panels_per_half * panel_bytes;
+  const uint32_t smem_pool = smem_out + kPanelGroups * p.panels_per_half * panel_bytes;  // pooled panels: two of 1 KB per group
+  const uint32_t smem_sfb = smem_pool + (p.pool ? kPanelGroups * 2u * kPoolPanelBytes : 0u);
   const uint32_t smem_sfa = smem_sfb + static_cast<uint32_t>(p.b_slots) * kScaleTilesB * 512;
   const uint32_t smem_sfa_static = smem_sfa + p.stages * 512;
   const uint32_t smem_bias = smem_sfa_static + ((p.cin + 127) / 128) * 512;  // fp32, tiles_n * BN entries
@@ -510,7 +515,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     tma_prefetch_desc(&act_map);
     tma_prefetch_desc(&weight_map);
     tma_prefetch_desc(&out_map);
-    if (p.warp_panels) tma_prefetch_desc(&out_warp_map);
+    if (p.warp_panels || p.pool) tma_prefetch_desc(&out_warp_map);
   }
   if (warp == 1) {
     if (PAIR) {
@@ -1079,6 +1084,29 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     const uint32_t own_panels = smem_out + static_cast<uint32_t>(warp - 2) * sw.panels * own_bytes;
     const bool store = !(probe_flags(p) & 4);
     constexpr int kGroupColumns = BN / kEpiGroups;
+    // The pooled second output (int8_conv2d_maxpool): once a chunk's 128 rows x 32 channels lie staged as bf16 for their
+    // own store, thread t takes eight channels (one 16-byte slot) of pooled pixel t / 4: the maximum over the four rows of
+    // its 2x2 window, quantised to INT8, into a panel of 32 pooled pixels x 32 bytes that a second TMA store writes through
+    // `out_warp_map` (here: the tensor map of the pooled output, boxes of tile_w / 2 x tile_h / 2 pixels). The tile's
+    // origin and sides are even (the host's choice), so every window lies inside one tile.
+    constexpr bool pool = (EPI & kEpiPool) != 0;  // a kernel of its own: the general epilogue pays nothing for it
+    uint32_t pool_from[4] = {0u, 0u, 0u, 0u}, pool_to = 0u;  // byte offsets into a staged panel / a pooled panel
+    const uint32_t pool_panels = smem_pool + group * 2u * kPoolPanelBytes;
+    bool pool_active = false;
+    Int8Quantizer pool_quantizer = {};
+    if (pool) {
+      const int half_w = p.tile_w >> 1, pp = row >> 2, slot = row & 3;
+      const int py = pp / half_w, px = pp - py * half_w;
+      pool_active = pp < half_w * (p.tile_h >> 1);
+      const int r00 = 2 * py * p.tile_w + 2 * px;
+      const int rows4[4] = {r00, r00 + 1, r00 + p.tile_w, r00 + p.tile_w + 1};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {  // where stage_row<16> put that slot of a 64-byte row
+        pool_from[i] = static_cast<uint32_t>(rows4[i]) * 64u + ((static_cast<uint32_t>(slot) ^ ((static_cast<uint32_t>(rows4[i]) >> 1) & 3u)) << 4);
+      }
+      pool_to = static_cast<uint32_t>(pp) * 32u + static_cast<uint32_t>(slot) * 8u;
+      pool_quantizer = make_int8_quantizer(__ldg(p.out_scale));
+    }
     uint32_t tile_it = 0, chunk_it = 0;
     for (int tile = worker; tile < p.total_tiles; tile += workers, ++tile_it) {
       if (kTileSets == 2 && (tile_it & 1u) != tile_set) continue;  // the other set's tile
@@ -1146,7 +1174,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
         return panel;
       };
-      auto send_panel = [&](uint32_t panel, int n) {
+      auto send_panel = [&](uint32_t panel, int n, bool commit = true) {
         fence_async_proxy();
         if (own) {
           __syncwarp();
@@ -1159,6 +1187,34 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         named_barrier(bar_id, 128);
         if (leader_warp && store && elect_one()) {
           tma_store_4d(&out_map, panel, n * static_cast<int>(sw.out_elem), x0, y0, b);
+          if (commit) bulk_commit();
+        }
+      };
+      // the pooled panel of the chunk staged in `panel` (every row of it: send_panel's barrier has passed); its store joins
+      // the bulk group of the chunk's own store, so the wait that frees an output panel frees the pooled panel of the
+      // same parity with it
+      auto send_pooled = [&](uint32_t panel, uint32_t parity, int n) {
+        const uint32_t pooled = pool_panels + parity * kPoolPanelBytes;
+        if (pool_active) {
+          uint32_t v[4][4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i][0]), "=r"(v[i][1]), "=r"(v[i][2]), "=r"(v[i][3]) : "r"(panel + pool_from[i]));
+          }
+          uint32_t m[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) m[j] = bf16x2_max(bf16x2_max(v[0][j], v[1][j]), bf16x2_max(v[2][j], v[3][j]));
+          const uint32_t q0 = int8_pack4(pool_quantizer, bf16_lo(m[0]), bf16_hi(m[0]), bf16_lo(m[1]), bf16_hi(m[1]));
+          const uint32_t q1 = int8_pack4(pool_quantizer, bf16_lo(m[2]), bf16_hi(m[2]), bf16_lo(m[3]), bf16_hi(m[3]));
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(pooled + pool_to), "r"(q0), "r"(q1) : "memory");
+        }
+        fence_async_proxy();
+        named_barrier(bar_id, 128);
+        if (leader_warp && elect_one()) {
+          // (a tile past the last whole window, next to an odd edge, has no pooled pixel)
+          if (store && (x0 >> 1) < (p.out_w >> 1) && (y0 >> 1) < (p.out_h >> 1)) {
+            tma_store_4d(&out_warp_map, pooled, n, x0 >> 1, y0 >> 1, b);
+          }
           bulk_commit();
         }
       };
@@ -1205,9 +1261,11 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
           if (n >= n_end) continue;  // uniform over the four warps of this group
           uint32_t w[16];
           finish_chunk<INT8>(p, sw, q[g], n, pixel, b, y, x, valid, gelu_table_at(smem_gelu), w);
+          const uint32_t parity = chunk_it & 1u;
           const uint32_t panel = take_panel();
           stage_row<16>(panel, panel_row, sw.out_elem, w);
-          send_panel(panel, n);
+          send_panel(panel, n, !pool);
+          if (pool) send_pooled(panel, parity, n);
         }
       }
     }
@@ -1261,7 +1319,7 @@ int out_elem_bytes(int out_mode) {
 }
 
 int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat, int out_elem, bool gelu, Plan* plan,
-              bool convert = false) {
+              bool convert = false, bool pool = false) {
   // `g.cin` counts bytes of K per tap here (a BF16 layer arrives with its channel count doubled)
   const bool int8 = fmt == kFmtI8, scaled = fmt == kFmtMx;
   if (g.batch <= 0 || g.height <= 0 || g.width <= 0 || g.cin <= 0 || g.cout <= 0) return kBadArgument;
@@ -1305,6 +1363,7 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
     pl.tile_h = 1, pl.tile_w = kTileM;
     for (int tw = 4; tw <= kTileM; ++tw) {
       const int th = kTileM / tw;
+      if (pool && ((tw | th) & 1)) continue;  // every 2x2 pooling window inside one tile
       if (tw * g.stride_w > 256 || th * g.stride_h > 256) continue;  // a TMA box spans at most 256 positions per dimension
       const double covered = static_cast<double>(ceil_div(out_w, tw)) * ceil_div(out_h, th) * kTileM;
       const double eff = static_cast<double>(out_w) * out_h / covered;
@@ -1344,8 +1403,9 @@ int make_plan(const FimConvGeometry& g, int fmt, bool per_pixel, bool allow_flat
   const int epilogue_groups = 4;  // four-warp groups with output panels of their own
   const int gelu_bytes = gelu ? static_cast<int>(kGeluSmemBytes) : 0;
   const int raw_bytes = convert ? 1024 + kRawStages * static_cast<int>(kRawBytes) : 0;  // landing ring (+ its alignment)
+  const int pool_bytes = pool ? epilogue_groups * 2 * static_cast<int>(kPoolPanelBytes) : 0;
   const int fixed = 1024 + epilogue_groups * pl.panels_per_half * 4096 * out_elem + ((g.cin + 127) / 128) * 512 + bias_bytes + gelu_bytes +
-                    raw_bytes;
+                    raw_bytes + pool_bytes;
   pl.stages = (kSmemLimit - fixed) / stage_bytes;
   if (pl.stages > kMaxStages) pl.stages = kMaxStages;
   if (pl.stages < 2) return kUnsupported;
@@ -1465,6 +1525,19 @@ int launch_conv_k(const ConvMaps& maps, const ConvParams& p, const Plan& pl, cud
       }
     }
   }
+  if constexpr (FMT == kFmtI8) {
+    if (pl.fixed_epilogue == kEpiPool) {  // the general epilogue + the pooled second output
+      if (pl.block_k != 128 && pl.block_k != 64) return kUnsupported;
+      if constexpr (BN == 256) {
+        if (pl.pair) {
+          return pl.block_k == 128 ? launch_conv<FMT, BN, 128, true, kEpiPool>(maps, p, pl, stream)
+                                   : launch_conv<FMT, BN, 64, true, kEpiPool>(maps, p, pl, stream);
+        }
+      }
+      return pl.block_k == 128 ? launch_conv<FMT, BN, 128, false, kEpiPool>(maps, p, pl, stream)
+                               : launch_conv<FMT, BN, 64, false, kEpiPool>(maps, p, pl, stream);
+    }
+  }
   if constexpr (FMT == kFmtI8 && BN == 256) {
     if (pl.fixed_epilogue == kEpiFixed && pl.pair && pl.block_k == 128) {
       return launch_conv<FMT, BN, 128, true, kEpiFixed>(maps, p, pl, stream);
@@ -1503,7 +1576,7 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 
 int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act_scales, const void* weight,
              const void* weight_scales, const float* a_scale, const float* w_scale, const FimConvGeometry* geometry,
-             const FimConvEpilogue* ep, void* out, int* status, void* stream, bool convert = false) {
+             const FimConvEpilogue* ep, void* out, int* status, void* stream, bool convert = false, void* pooled = nullptr) {
   const bool int8 = fmt == kFmtI8;
   if (geometry == nullptr || ep == nullptr) return kBadArgument;
   if (geometry->batch == 0 || geometry->height == 0 || geometry->width == 0) return kOk;
@@ -1533,14 +1606,17 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
       (weight_scales && !aligned16(weight_scales)) || (act_scales && !aligned16(act_scales)) || (w_scale && !aligned16(w_scale))) {
     return kBadLayout;
   }
+  const bool pool = pooled != nullptr;
+  if (pool && !(int8 && ep->out_mode == FIM_OUT_BF16 && ep->out_scale != nullptr && aligned16(pooled))) return kBadArgument;
+  if (pool && geometry->cin % 64) return kUnsupported;
   const int out_elem = out_elem_bytes(ep->out_mode);
   // one activation scale per pixel and 32 channels: given by the caller, or formed on chip from bf16 activations
   const bool per_pixel = act_scales != nullptr || (convert && act_exponent == nullptr);
 
   // a 1x1 conv is a plain GEMM over flattened pixels when the residual (if any) is dense NHWC
-  bool allow_flat = true;
+  bool allow_flat = !pool;  // pooling windows need the tile to be a patch of the image
   Plan pl;
-  {
+  if (allow_flat) {
     Plan probe;
     const int rc0 = make_plan(*g, fmt, per_pixel, true, out_elem, ep->act == FIM_ACT_GELU, &probe, convert);
     if (rc0 != kOk) return rc0;
@@ -1550,8 +1626,9 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
       if (!dense) allow_flat = false;
     }
   }
-  const int rc = make_plan(*g, fmt, per_pixel, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl, convert);
+  const int rc = make_plan(*g, fmt, per_pixel, allow_flat, out_elem, ep->act == FIM_ACT_GELU, &pl, convert, pool);
   if (rc != kOk) return rc;
+  if (pool && (pl.out_h < 2 || pl.out_w < 2 || pl.panels_per_half != 2)) return kUnsupported;  // no whole window: nothing to pool
 
   const Schedule sc = make_schedule(*g, pl, fmt != kFmtMx, per_pixel);
   ConvParams p;
@@ -1586,6 +1663,7 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   p.out_exponent = ep->out_exponent;
   p.out_scales = static_cast<uint8_t*>(ep->out_scales);
   p.out_scale = ep->out_scale;
+  p.pool = pool ? 1 : 0;
   p.status = status;
   p.debug = g_debug_flags;
   p.poll_backoff_ns = (g_debug_flags & 32) ? 0u : 200u;
@@ -1650,6 +1728,14 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
       if (rcw != kOk) return rcw;
       p.warp_panels = 1;
     }
+    if (pool) {  // the pooled output [B, Ho / 2, Wo / 2, Cout] INT8, stored in boxes of a quarter tile x 32 channels
+      const uint64_t prow = static_cast<uint64_t>(g->cout), ph = static_cast<uint64_t>(pl.out_h / 2), pw = static_cast<uint64_t>(pl.out_w / 2);
+      const uint64_t pdims[4] = {prow, pw, ph, static_cast<uint64_t>(o_b)};
+      const uint64_t pstrides[3] = {prow, pw * prow, ph * pw * prow};
+      const uint32_t pbox[4] = {32, static_cast<uint32_t>(pl.tile_w / 2), static_cast<uint32_t>(pl.tile_h / 2), 1};
+      const int rcp = make_tensor_map(&maps.out_warp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, pooled, pdims, pstrides, pbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rcp != kOk) return rcp;
+    }
   }
   if (fmt == kFmtMx && p.warp_panels && !pl.pair && pl.block_n >= 128 && pl.block_k == 128 && p.bias != nullptr &&
       !(g_debug_flags & 1024)) {
@@ -1664,8 +1750,10 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   }
   if (pl.fixed_epilogue == 0 && p.bias != nullptr && p.residual == nullptr && pl.panels_per_half == 2 && !(g_debug_flags & 1024)) {
     if (fmt == kFmtMx && p.act == kActGelu && p.out_mode == FIM_OUT_E4M3_STATIC) pl.fixed_epilogue = kEpiFixed | kEpiGelu | kEpiStatic;
-    if (fmt == kFmtI8 && p.act == kActNone && p.out_mode == FIM_OUT_BF16) pl.fixed_epilogue = kEpiFixed;
+    if (fmt == kFmtI8 && p.act == kActNone && p.out_mode == FIM_OUT_BF16 && !pool) pl.fixed_epilogue = kEpiFixed;
   }
+
+  if (pool) pl.fixed_epilogue = kEpiPool;
 
   // scale tiles as tensors of 128 four-byte words per 512-byte tile: the loads of a CTA pair go through these
   maps.sfb = act_map, maps.sfa = act_map;
@@ -1723,6 +1811,13 @@ extern "C" int fim_int8_conv2d(const void* x, const void* weight, const float* a
                                const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status,
                                void* stream) {
   return run_conv(kFmtI8, x, nullptr, nullptr, weight, nullptr, a_scale, w_scale, geometry, epilogue, out, status, stream);
+}
+
+extern "C" int fim_int8_conv2d_maxpool(const void* x, const void* weight, const float* a_scale, const float* w_scale,
+                                       const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, void* pooled,
+                                       int* status, void* stream) {
+  if (pooled == nullptr) return kBadArgument;
+  return run_conv(kFmtI8, x, nullptr, nullptr, weight, nullptr, a_scale, w_scale, geometry, epilogue, out, status, stream, false, pooled);
 }
 
 extern "C" int fim_bf16_conv2d(const void* x, const void* weight, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue,

@@ -201,6 +201,16 @@ int fim_mxfp8_conv2d_bf16(const void* x_bf16, const int8_t* act_exponent, const 
 int fim_int8_conv2d(const void* x, const void* weight, const float* a_scale, const float* w_scale,
                     const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, int* status, void* stream);
 
+/* fim_int8_conv2d (FIM_OUT_BF16 only) whose epilogue also writes the second output of ops.int8_conv2d_maxpool: `pooled`,
+ * int8 [B, Ho / 2, Wo / 2, cout], the 2x2 / stride-2 max pool of the bf16 output quantised with `epilogue->out_scale`
+ * (a trailing odd row or column is dropped, as F.max_pool2d does). The pool is taken from the bf16 tile while it lies in
+ * shared memory for its own store: the output is not read back. Ho, Wo >= 2 and cin % 64 == 0, else
+ * FIM_ERR_UNSUPPORTED (the caller then runs fim_int8_conv2d and fim_maxpool2_quantize_int8). Replaces
+ * ops.int8_conv2d_maxpool (flashim/ops/conv.py:209-222; the POOL epilogue of flashim/backends/triton/conv.py:798-805). */
+int fim_int8_conv2d_maxpool(const void* x, const void* weight, const float* a_scale, const float* w_scale,
+                            const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out, void* pooled, int* status,
+                            void* stream);
+
 /* BF16 conv: x bf16 NHWC, weight bf16 [cout, kh*kw*cin] in (ky, kx, c) order, fp32 accumulation on the tensor cores
  * (kind::f16), epilogue bias -> bf16 (FIM_OUT_BF16) or fp32 (FIM_OUT_F32), activation and residual as above. The
  * pointwise product of ops.depthwise5x5_relu_pointwise (flashim/ops/conv.py:67-87; kernel

@@ -275,6 +275,35 @@ def test_int8_bias_epilogue_with_fixed_switches_agrees_with_the_general_one(ops)
     assert same_bytes(fixed.cpu(), oracle.int8_conv2d(x, weight, a_scale, w_scale, bias, *geometry))
 
 
+@pytest.mark.parametrize("max_ctas", [0, 4, 10])
+@pytest.mark.parametrize("case", [(2, 44, 52, 64, 64, 3), (3, 37, 41, 128, 256, 3), (2, 50, 50, 64, 96, 1), (1, 31, 78, 256, 512, 3)],
+                         ids=lambda c: "%dx%dx%d_c%d-%d_k%d" % c)
+def test_pool_in_the_int8_epilogue_over_many_tiles_per_cta(ops, case, max_ctas):
+    """int8_conv2d_maxpool takes the 2x2 max pool from each bf16 tile while it lies in shared memory for its own store. With
+    the CTAs capped every CTA (or CTA pair, at 256 output channels) walks several tiles, so the pooled panels are reused
+    many times; odd heights and widths leave tiles with a dropped row or column, and 96 channels a partial channel tile.
+    Both outputs equal the oracle's bytes, and the pooled one equals the separate pooling pass over the bf16 output."""
+    b, h, w, cin, cout, k = case
+    g = torch.Generator().manual_seed(h * w + cout)
+    x = torch.randint(-127, 128, (b, h, w, cin), dtype=torch.int8, generator=g)
+    weight = torch.randint(-127, 128, (cout, k * k * cin), dtype=torch.int8, generator=g)
+    w_scale = torch.rand(cout, generator=g) * 2e-4 + 1e-5
+    bias = torch.randn(cout, generator=g).to(BF16)
+    a_scale, out_scale = torch.tensor(0.03), torch.tensor(0.04)
+    geometry = (k, k, 1, 1, k // 2, k // 2, 1, 1)
+    from flashim_b200.backends.sm100 import kernels
+    with conv_schedule(0, max_ctas) as capped:
+        if max_ctas:
+            sched = capped.schedule((b, h, w, cin, cout, k, k, k // 2, 1), int8=True)
+            assert sched["tiles"] >= 2 * sched["ctas"] // (2 if sched["pairs"] else 1)
+        out, pooled = ops.int8_conv2d_maxpool.get("sm100")(*to_dev(x, weight, a_scale, w_scale, bias), *geometry, relu=True,
+                                                           out_scale=to_dev(out_scale))
+    want_out, want_pooled = oracle.int8_conv2d_maxpool(x, weight, a_scale, w_scale, bias, *geometry, relu=True, out_scale=out_scale)
+    assert same_bytes(out.cpu(), want_out)
+    assert pooled.shape == want_pooled.shape and torch.equal(pooled.cpu(), want_pooled)
+    assert torch.equal(pooled, kernels.maxpool2_quantize_int8(out, to_dev(out_scale.reshape(1))))
+
+
 @pytest.mark.parametrize("max_ctas", [0, 3, 11])
 @pytest.mark.parametrize("case", [(2, 24, 30, 64, 64, 3), (2, 24, 30, 128, 128, 3), (2, 37, 41, 128, 256, 1), (2, 37, 41, 256, 128, 1),
                                   (2, 24, 30, 96, 64, 5)], ids=lambda c: "c%d-%d_k%d" % c[3:])
