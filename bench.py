@@ -406,9 +406,11 @@ class StackWorkload(Workload):
         self.inputs = self.staging = self.model.static_inputs(self.inputs)
         self.result_host = [torch.empty((images, s, s, 32), dtype=torch.bfloat16).pin_memory() for s, _ in LEVELS]
         blocks = len(self.model.levels[0].blocks)
-        # per level and chunk: the projection, three kernels per block and the head (the quantisers run inside the convs)
+        # per level and chunk: the projection, the kernels of each block (depthwise + the residual MLP as one kernel at 128
+        # and 256 channels, else depthwise + up conv + down conv) and the head (the quantisers run inside the convs)
         # (a projection wider than one 256-column tile is fed by the standalone quantiser: one more launch)
-        self.launches_per_step = sum(-(-images // self.model.chunk) * (2 + 3 * blocks + (1 if c > 256 or c % 128 else 0) + (1 if c % 128 else 0))
+        self.launches_per_step = sum(-(-images // self.model.chunk) * (2 + (2 if c in (128, 256) else 3) * blocks
+                                                                       + (1 if c > 256 or c % 128 else 0) + (1 if c % 128 else 0))
                                      for _, c in LEVELS)
 
     def pair_input(self, level: int, pair: int) -> torch.Tensor:

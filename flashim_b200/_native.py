@@ -76,6 +76,7 @@ SIGNATURES: dict[str, tuple] = {
     "fim_mxfp8_conv2d": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_mxfp8_conv2d_bf16": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_int8_conv2d": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
+    "fim_mxfp8_gelu_mlp_residual": (_I, [_P] * 10 + [ctypes.c_longlong, _I, _P, _P]),
     "fim_int8_conv2d_maxpool": (_I, [_P, _P, _P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P, _P]),
     "fim_bf16_conv2d": (_I, [_P, _P, ctypes.POINTER(ConvGeometry), ctypes.POINTER(ConvEpilogue), _P, _P, _P]),
     "fim_gelu_quantize_mxfp8": (_I, [_P, _P, _P, _P, _L, _I, _P]),

@@ -377,6 +377,28 @@ def _(x, act_exponent, act_scales, weight, weight_scales, bias, residual, out_ex
     return x.new_empty((b, ho, wo, cout), dtype=_OUT_DTYPES[out_mode]), x.new_empty((n,), dtype=torch.uint8)
 
 
+@torch.library.custom_op("flashim_b200::mxfp8_gelu_mlp_residual", mutates_args=())
+def mxfp8_gelu_mlp_residual_launch(x: Tensor, x_scales: Tensor, w1: Tensor, w1_scales: Tensor, b1: Tensor, w2: Tensor,
+                                   w2_scales: Tensor, b2: Tensor, residual: Tensor) -> Tensor:
+    """E4M3 ``x [..., C]`` with swizzled per-pixel scales -> bf16 ``[..., C]``: up conv, GELU, requantisation, down conv and
+    residual add in one kernel (C = 128 or 256)."""
+    x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2 = (_aligned(t) for t in (x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2))
+    residual = _aligned(residual.contiguous())
+    channels = x.shape[-1]
+    rows = x.numel() // channels
+    out = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16)
+    code = _native.library().fim_mxfp8_gelu_mlp_residual(
+        x.data_ptr(), x_scales.data_ptr(), w1.data_ptr(), w1_scales.data_ptr(), b1.data_ptr(), w2.data_ptr(), w2_scales.data_ptr(),
+        b2.data_ptr(), residual.data_ptr(), out.data_ptr(), rows, channels, status_word(x.device).data_ptr(), _stream(x))
+    _finish(code, f"mxfp8_gelu_mlp_residual {tuple(x.shape)}", x.device)
+    return out
+
+
+@mxfp8_gelu_mlp_residual_launch.register_fake
+def _(x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2, residual):
+    return x.new_empty(x.shape, dtype=torch.bfloat16)
+
+
 @torch.library.custom_op("flashim_b200::int8_conv2d", mutates_args=())
 def int8_conv2d_launch(
     x: Tensor, weight: Tensor, a_scale: Tensor | None, w_scale: Tensor | None, bias: Tensor | None, residual: Tensor | None,
@@ -593,6 +615,25 @@ def register(ops=None, device_spec=None, feature=None) -> None:
                 x, None if per_pixel else act_scale, act_scale if per_pixel else None, weight, weight_scales, bias, residual,
                 out_exponent, kh, kw, sh, sw, ph, pw, dh, dw, act_code[act], mode)
             return (out, scales) if dynamic_out else out
+
+    if hasattr(ops, "mxfp8_gelu_mlp_residual"):
+        def mlp_residual_when(x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2, residual):
+            c = x.shape[-1]
+            rows = x.numel() // max(c, 1)
+            return (
+                have() and _cuda(x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2, residual) and c in (128, 256)
+                and x.dtype == E4M3 and x.is_contiguous() and w1.dtype == E4M3 and w2.dtype == E4M3
+                and w1.is_contiguous() and w2.is_contiguous() and tuple(w1.shape) == (2 * c, c) and tuple(w2.shape) == (c, 2 * c)
+                and x_scales.dtype == torch.uint8 and x_scales.numel() == swizzled_scale_bytes(rows, c // BLOCK)
+                and w1_scales.dtype == torch.uint8 and w1_scales.numel() == swizzled_scale_bytes(2 * c, c // BLOCK)
+                and w2_scales.dtype == torch.uint8 and w2_scales.numel() == swizzled_scale_bytes(c, 2 * c // BLOCK)
+                and b1.dtype == torch.bfloat16 and b1.numel() == 2 * c and b2.dtype == torch.bfloat16 and b2.numel() == c
+                and residual.dtype == torch.bfloat16 and residual.shape == x.shape
+            )
+
+        @ops.mxfp8_gelu_mlp_residual.register("sm100", device=spec, requires=requires, priority=3, when=mlp_residual_when)
+        def mxfp8_gelu_mlp_residual(x, x_scales, w1, w1_scales, b1, w2, w2_scales, b2, residual):
+            return mxfp8_gelu_mlp_residual_launch(x, x_scales, w1, w1_scales, b1.contiguous(), w2, w2_scales, b2.contiguous(), residual)
 
     def bf16_in_when(x, act_exponent, weight, weight_scales, bias, *, act="none", residual=None, out_exponent=None,
                      dynamic_out=False, out_fp32=False):

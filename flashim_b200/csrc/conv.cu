@@ -1291,6 +1291,435 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
   }
 }
 
+// ---- residual MLP of a refiner block: x W1^T + b1 -> GELU -> per-pixel MXFP8 -> W2^T + b2 + residual, one kernel ----------
+//
+// The 1x1 up conv (C -> 2C, GELU, dynamic requantisation) and the 1x1 down conv (2C -> C, residual) of a block as one
+// persistent kernel: the hidden tensor never leaves the SM. Per tile of 128 pixels the MMA warp forms the hidden
+// activations 128 channels at a time in one tensor-memory accumulator; sixteen hidden-block warps (32 pixels x 32 hidden
+// channels each: exactly one scale block per lane) add the bias, round to bf16, apply the table GELU, form the block's
+// E8M0 exponent and write the E4M3 bytes straight into a K-major swizzled operand tile in shared memory, with the scale
+// bytes in a 512-byte scale tile beside it; the MMA warp then multiplies that tile into the second accumulator (all C
+// output channels) while the next 128 hidden channels are being formed (the first product of block g + 1 is issued
+// ahead of the second product of block g, across tile boundaries too). Four output warps, one per lane quarter of
+// tensor memory, add bias and residual to the finished second accumulator and store bf16 rows; the residual reaches
+// them by TMA, in panels of the output panels' shape, four chunks ahead. The same MMAs in the same order as the two
+// separate launches, the same epilogue arithmetic: the same bits. KC = C / 128 (1 or 2). 22 warps: TMA producer, MMA
+// issuer, 16 hidden-block warps, 4 output warps.
+constexpr uint32_t kMlpTile = 128u * 128u;  // bytes of one operand tile: 128 rows x 128 bytes of K
+constexpr int kMlpThreads = kThreads + 128;  // + four output warps (one per lane quarter of tensor memory)
+constexpr uint32_t kMlpPanels = 2, kMlpPanelBytes = 32u * 64u;  // output panels per output warp: 32 rows x 32 bf16 channels
+constexpr uint32_t kMlpResidualSlots = 4;  // residual panels (same shape) each output warp keeps in flight
+struct MlpParams {
+  int rows, row_tiles, stages;
+  const uint8_t* x_scales;   // per-pixel scales of x: swizzled tiles, KC per row tile
+  const uint8_t* w1_scales;  // [2C / 128 row tiles][KC] tiles
+  const uint8_t* w2_scales;  // [KC row tiles][2C / 128] tiles
+  const __nv_bfloat16* bias1;  // [2C]
+  const __nv_bfloat16* bias2;  // [C]
+  const __nv_bfloat16* residual;  // [rows, C], dense
+  int* status;
+  uint32_t poll_backoff_ns;
+  int debug;  // probe builds only (FIM_PROBE_BUILD): 1 = no residual loads, 2 = the output warps only drain, 4 = no GELU / requantisation arithmetic
+};
+__device__ __forceinline__ int probe_flags(const MlpParams& p) { return FIM_PROBE_BUILD ? p.debug : 0; }
+
+struct MlpControl {
+  uint64_t w_full[kMaxStages], w_empty[kMaxStages];
+  uint64_t x_full, x_empty, acc1_full, acc1_empty, acc2_full, acc2_empty;
+  uint64_t h_full[2], h_empty[2];
+  uint64_t res_full[4][kMlpResidualSlots];  // per output warp: its residual panels have landed
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+
+template <int KC>
+__global__ void __launch_bounds__(kMlpThreads, 1)
+mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w1_map, const __grid_constant__ CUtensorMap w2_map,
+           const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap res_map, const MlpParams p) {
+  constexpr int C = 128 * KC, HB = 2 * KC;            // channels; hidden blocks of 128 channels
+  constexpr uint32_t kUnitBytes = KC * kMlpTile;      // a weight unit: W1 rows of one hidden block, or W2 columns of one
+  constexpr uint32_t kPanels = kMlpPanels, kPanelBytes = kMlpPanelBytes;
+  constexpr uint32_t kAcc1 = 0, kAcc2 = 128, kSfa1 = 128 + C, kSfa2 = kSfa1 + 4 * KC, kSfbRing = kSfa2 + 8;
+
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) MlpControl ctl;
+
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t smem_gelu = base;
+  const uint32_t smem_x = base + kGeluSmemBytes;
+  const uint32_t smem_w = smem_x + kUnitBytes;
+  const uint32_t smem_h = smem_w + static_cast<uint32_t>(p.stages) * kUnitBytes;
+  const uint32_t smem_out = smem_h + 2u * kMlpTile;
+  const uint32_t smem_res = smem_out + 4u * kPanels * kPanelBytes;  // residual panels: kMlpResidualSlots per output warp
+  const uint32_t smem_xsf = smem_res + 4u * kMlpResidualSlots * kPanelBytes;
+  const uint32_t smem_wsf = smem_xsf + KC * 512u;
+  const uint32_t smem_hsf = smem_wsf + static_cast<uint32_t>(p.stages) * KC * 512u;
+  const uint32_t smem_bias1 = smem_hsf + 2u * 512u;  // fp32 [2C]
+  const uint32_t smem_bias2 = smem_bias1 + 2u * C * 4u;  // fp32 [C]
+
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+  const int worker = static_cast<int>(blockIdx.x), workers = static_cast<int>(gridDim.x);
+
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&ctl.w_full[s], 1);
+      mbar_init(&ctl.w_empty[s], 1);
+    }
+    mbar_init(&ctl.x_full, 1);
+    mbar_init(&ctl.x_empty, 1);
+    mbar_init(&ctl.acc1_full, 1);
+    mbar_init(&ctl.acc1_empty, 16);
+    mbar_init(&ctl.acc2_full, 1);
+    mbar_init(&ctl.acc2_empty, 4);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ctl.h_full[b], 16);
+      mbar_init(&ctl.h_empty[b], 1);
+    }
+    for (int w = 0; w < 4; ++w) {
+      for (uint32_t i = 0; i < kMlpResidualSlots; ++i) mbar_init(&ctl.res_full[w][i], 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&x_map);
+    tma_prefetch_desc(&w1_map);
+    tma_prefetch_desc(&w2_map);
+    tma_prefetch_desc(&out_map);
+    tma_prefetch_desc(&res_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl.tmem_base, kTmemColumns);
+    tmem_relinquish();
+  }
+  for (int i = threadIdx.x; i < 3 * C; i += kMlpThreads) {  // both biases widened to fp32 once per CTA
+    const float value = __bfloat162float(i < 2 * C ? p.bias1[i] : p.bias2[i - 2 * C]);
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_bias1 + i * 4), "f"(value) : "memory");
+  }
+  for (int i = threadIdx.x; i < kGeluEntries; i += kMlpThreads) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(smem_gelu + i * 4), "r"(kGeluTable[i]) : "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+  const uint32_t w_full0 = smem_u32(&ctl.w_full[0]), w_empty0 = smem_u32(&ctl.w_empty[0]);
+  const uint32_t x_full = smem_u32(&ctl.x_full), x_empty = smem_u32(&ctl.x_empty);
+  const uint32_t acc1_full = smem_u32(&ctl.acc1_full), acc1_empty = smem_u32(&ctl.acc1_empty);
+  const uint32_t acc2_full = smem_u32(&ctl.acc2_full), acc2_empty = smem_u32(&ctl.acc2_empty);
+  const uint32_t h_full0 = smem_u32(&ctl.h_full[0]), h_empty0 = smem_u32(&ctl.h_empty[0]);
+
+  if (warp == 0) {
+    // ===== TMA producer: the tile's activations, then its weight units in the order the MMA warp takes them =====
+    if (elect_one()) {
+      const uint32_t stages = in_register(static_cast<uint32_t>(p.stages));
+      uint32_t s = 0, phase = 0;
+      bool alive = true;
+      // one weight unit into the ring: KC tiles of 128 rows x 128 bytes and their KC scale tiles
+      auto unit = [&](const CUtensorMap* map, int k0, int k_step, int row0, int row_step, const uint8_t* scales, int scale_step) {
+        if (!mbar_wait_addr(w_empty0 + 8 * s, phase ^ 1, abort_flag, p.status, kStatusWaitEmpty)) {
+          alive = false;
+          return;
+        }
+        const uint32_t bar = w_full0 + 8 * s;
+        mbar_expect_tx_addr(bar, KC * (kMlpTile + 512u));
+#pragma unroll
+        for (int i = 0; i < KC; ++i) {
+          tma_load_2d_addr(smem_w + s * kUnitBytes + i * kMlpTile, map, bar, k0 + i * k_step, row0 + i * row_step);
+          bulk_load_addr(smem_wsf + (s * KC + i) * 512u, scales + static_cast<size_t>(i) * scale_step * 512, 512, bar);
+        }
+        if (++s == stages) s = 0, phase ^= 1;
+      };
+      // The units follow the MMA warp's order over the CTA's hidden blocks g = 0, 1, ... (HB per tile, across tiles): the
+      // first product of block g + 1 is issued before the second product of block g, so that a block's accumulator is
+      // ready when the epilogue warps finish the block before it, also across a tile boundary.
+      const int my_tiles = worker < p.row_tiles ? (p.row_tiles - worker + workers - 1) / workers : 0;
+      const uint32_t blocks = static_cast<uint32_t>(my_tiles) * HB;
+      auto activations = [&](uint32_t t) {  // the t-th tile of this CTA: its pixels and their scale tiles
+        if (!mbar_wait_addr(x_empty, (t & 1u) ^ 1u, abort_flag, p.status, kStatusWaitEmpty)) {
+          alive = false;
+          return;
+        }
+        const int m = worker + static_cast<int>(t) * workers;
+        mbar_expect_tx_addr(x_full, KC * (kMlpTile + 512u));
+#pragma unroll
+        for (int j = 0; j < KC; ++j) {
+          tma_load_4d_addr(smem_x + j * kMlpTile, &x_map, x_full, j * 128, m * kTileM, 0, 0);
+          bulk_load_addr(smem_xsf + j * 512u, p.x_scales + (static_cast<size_t>(m) * KC + j) * 512, 512, x_full);
+        }
+      };
+      // W1 rows of hidden block h: K chunks j at columns 128 j; scale tiles (row tile h, K tile j)
+      auto first_unit = [&](uint32_t g) {
+        const int h = static_cast<int>(g & (HB - 1));
+        if (h == 0) activations(g / HB);
+        if (alive) unit(&w1_map, 0, 128, h * 128, 0, p.w1_scales + static_cast<size_t>(h) * KC * 512, 1);
+      };
+      if (blocks != 0) first_unit(0);
+      for (uint32_t g = 0; g < blocks && alive; ++g) {
+        if (g + 1 < blocks) first_unit(g + 1);
+        // W2 columns of hidden block h: row tiles i at rows 128 i; scale tiles (row tile i, K tile h)
+        const int h = static_cast<int>(g & (HB - 1));
+        if (alive) unit(&w2_map, h * 128, 0, 0, 128, p.w2_scales + static_cast<size_t>(h) * 512, HB);
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (elect_one()) {
+      const uint32_t stages = in_register(static_cast<uint32_t>(p.stages));
+      const uint64_t x_desc = kmajor_desc(smem_x, 128), w_desc0 = kmajor_desc(smem_w, 128), h_desc0 = kmajor_desc(smem_h, 128);
+      const uint64_t xsf_desc = scale_desc(smem_xsf), wsf_desc0 = scale_desc(smem_wsf), hsf_desc0 = scale_desc(smem_hsf);
+      const uint32_t idesc1 = idesc_mxf8(128), idesc2 = idesc_mxf8(C);
+      uint32_t s = 0, phase = 0;
+      bool alive = true;
+      const int my_tiles = worker < p.row_tiles ? (p.row_tiles - worker + workers - 1) / workers : 0;
+      const uint32_t blocks = static_cast<uint32_t>(my_tiles) * HB;  // hidden blocks of this CTA, across its tiles
+      // the first product of hidden block g: acc1 = x W1[block]^T
+      auto first = [&](uint32_t g) {
+        const uint32_t h = g & (HB - 1), t = g / HB;
+        if (h == 0) {
+          if (!mbar_wait_addr(x_full, t & 1u, abort_flag, p.status, kStatusWaitFull)) {
+            alive = false;
+            return;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int j = 0; j < KC; ++j) tc_copy_scales(tmem + kSfa1 + 4 * j, xsf_desc + static_cast<uint64_t>((j * 512u) >> 4));
+        }
+        if (!mbar_wait_addr(acc1_empty, (g & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTmemEmpty) ||
+            !mbar_wait_addr(w_full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
+          alive = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t sfb = tmem + kSfbRing + s * 4 * KC;
+#pragma unroll
+        for (int j = 0; j < KC; ++j) tc_copy_scales(sfb + 4 * j, wsf_desc0 + static_cast<uint64_t>(((s * KC + j) * 512u) >> 4));
+#pragma unroll
+        for (int j = 0; j < KC; ++j) {
+          const uint64_t a_desc = x_desc + static_cast<uint64_t>((j * kMlpTile) >> 4);
+          const uint64_t b_desc = w_desc0 + static_cast<uint64_t>((s * kUnitBytes + j * kMlpTile) >> 4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t scaled = idesc1 + static_cast<uint32_t>(k) * ((1u << 29) | (1u << 4));
+            tc_mma_mxf8(tmem + kAcc1, a_desc + 2 * k, b_desc + 2 * k, scaled, tmem + kSfa1 + 4 * j, sfb + 4 * j, (j > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(&ctl.w_empty[s]);
+        tc_commit(&ctl.acc1_full);
+        if (h == HB - 1) tc_commit(&ctl.x_empty);  // the tile's activations have been read for the last time
+        if (++s == stages) s = 0, phase ^= 1;
+      };
+      // the second product of hidden block g: acc2 (+)= H[buffer] x W2 unit
+      auto second = [&](uint32_t g) {
+        const uint32_t b = g & 1u, h = g & (HB - 1), t = g / HB;
+        if (h == 0 && !mbar_wait_addr(acc2_empty, (t & 1u) ^ 1u, abort_flag, p.status, kStatusWaitTmemEmpty)) {
+          alive = false;
+          return;
+        }
+        if (!mbar_wait_addr(h_full0 + 8 * b, (g >> 1) & 1u, abort_flag, p.status, kStatusWaitFull) ||
+            !mbar_wait_addr(w_full0 + 8 * s, phase, abort_flag, p.status, kStatusWaitFull)) {
+          alive = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t sfa = tmem + kSfa2 + 4 * b, sfb = tmem + kSfbRing + s * 4 * KC;
+        tc_copy_scales(sfa, hsf_desc0 + static_cast<uint64_t>((b * 512u) >> 4));
+#pragma unroll
+        for (int i = 0; i < KC; ++i) tc_copy_scales(sfb + 4 * i, wsf_desc0 + static_cast<uint64_t>(((s * KC + i) * 512u) >> 4));
+        const uint64_t a_desc = h_desc0 + static_cast<uint64_t>((b * kMlpTile) >> 4);
+        const uint64_t b_desc = w_desc0 + static_cast<uint64_t>((s * kUnitBytes) >> 4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t scaled = idesc2 + static_cast<uint32_t>(k) * ((1u << 29) | (1u << 4));
+          tc_mma_mxf8(tmem + kAcc2, a_desc + 2 * k, b_desc + 2 * k, scaled, sfa, sfb, (k > 0 || h != 0) ? 1u : 0u);
+        }
+        tc_commit(&ctl.w_empty[s]);
+        tc_commit(&ctl.h_empty[b]);
+        if (h == HB - 1) tc_commit(&ctl.acc2_full);
+        if (++s == stages) s = 0, phase ^= 1;
+      };
+      // block g + 1's first product goes ahead of block g's second one: its accumulator is then ready when the epilogue
+      // warps finish block g, also where block g + 1 opens the next tile
+      if (blocks != 0) first(0);
+      for (uint32_t g = 0; g < blocks && alive; ++g) {
+        if (g + 1 < blocks) first(g + 1);
+        if (alive) second(g);
+      }
+    }
+  } else if (warp < 2 + 16) {
+    // ===== hidden-block warps: lanes 32 * (w % 4) ... of tensor memory, 32 hidden channels (w - 2) / 4 of every block =====
+    const int quarter = warp & 3, group = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const GeluTable gelu2 = gelu_table_at(smem_gelu);
+    const uint32_t lane_tmem = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kAcc1 + group * 32;
+    // where this lane's 32 hidden bytes go in a K-major 128-byte-swizzled tile, and its scale byte in the scale tile
+    const uint32_t h_row = static_cast<uint32_t>(row) * 128u;
+    const uint32_t h_at0 = h_row + (((2u * group) ^ (static_cast<uint32_t>(row) & 7u)) << 4);
+    const uint32_t h_at1 = h_row + (((2u * group + 1u) ^ (static_cast<uint32_t>(row) & 7u)) << 4);
+    const uint32_t hsf_at = static_cast<uint32_t>(lane * 16 + quarter * 4 + group);
+    const int my_tiles = worker < p.row_tiles ? (p.row_tiles - worker + workers - 1) / workers : 0;
+    const uint32_t blocks = static_cast<uint32_t>(my_tiles) * HB;
+    for (uint32_t g = 0; g < blocks; ++g) {
+      if (!mbar_wait_warp(acc1_full, g & 1u, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+      tc_fence_after();
+      uint32_t raw[32], r[16];
+      tmem_load_32(lane_tmem, raw);
+      tmem_load_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_addr(acc1_empty);  // the accumulator goes back before the long arithmetic
+      const uint32_t bias_chunk = smem_bias1 + ((g & (HB - 1)) * 128u + static_cast<uint32_t>(group) * 32u) * 4u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint64_t b0, b1;
+        load_bias_pairs(bias_chunk, i, b0, b1);
+        float v0, v1, v2, v3;
+        unpack2(add2(pack2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1])), b0), v0, v1);
+        unpack2(add2(pack2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3])), b1), v2, v3);
+        r[2 * i] = pack_bf16(v0, v1);
+        r[2 * i + 1] = pack_bf16(v2, v3);
+      }
+      int e = 0;
+      uint32_t w[8];
+      if (!(probe_flags(p) & 4)) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = gelu_bf16x2(r[i], gelu2);
+      uint32_t mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = bf16x2_absmax(r[2 * i], r[2 * i + 1]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mx[i] = bf16x2_absmax(mx[2 * i], mx[2 * i + 1]);
+      mx[0] = bf16x2_absmax(bf16x2_absmax(mx[0], mx[1]), bf16x2_absmax(mx[2], mx[3]));
+      const uint32_t top = max(mx[0] & 0x7FFFu, (mx[0] >> 16) & 0x7FFFu);
+      e = e8m0_exponent_bits(top << 16);
+      scale_to_e4m3(r, e, w);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = r[i];
+      }
+      // the operand buffer of this hidden block: free once the second product that last read it has completed
+      const uint32_t b = g & 1u;
+      if (!mbar_wait_warp(h_empty0 + 8 * b, ((g >> 1) & 1u) ^ 1u, abort_flag, p.status, kStatusWaitEmpty)) break;
+      const uint32_t tile_at = smem_h + b * kMlpTile;
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_at + h_at0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_at + h_at1), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+      asm volatile("st.shared.u8 [%0], %1;" ::"r"(smem_hsf + b * 512u + hsf_at), "r"(e + 127) : "memory");
+      fence_async_proxy();  // the second product reads these bytes through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive_addr(h_full0 + 8 * b);
+    }
+  } else {
+    // ===== output warps: one per lane quarter; bias, residual and bf16 rows of every output channel of its 32 pixels.
+    // Few instructions but a long chain per chunk (tensor-memory load, residual panel, store): warps of their own keep
+    // that latency off the hidden-block warps, whose arithmetic is what a tile takes. =====
+    const int quarter = warp & 3;
+    const uint32_t lane_tmem = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + kAcc2;
+    const uint32_t my_panels = smem_out + static_cast<uint32_t>(warp - 18) * kPanels * kPanelBytes;
+    // 16-byte slot i of this lane's 64-byte panel row sits at row_at ^ (i << 4) (the swizzle a TMA store of such rows reads)
+    const uint32_t row_at = static_cast<uint32_t>(lane) * 64u + ((((static_cast<uint32_t>(lane) * 64u) >> 7) & 3u) << 4);
+    constexpr int kChunks = 4 * KC;
+    // The residual of this warp's 32 pixels arrives by TMA, one panel of 32 channels per copy (the shape and swizzle of an
+    // output panel), kMlpResidualSlots chunks ahead of its use; rows past the end of the tensor arrive as zeros. The
+    // lane that issued a copy is the one that re-issues into the slot after the warp has read it.
+    const uint32_t my_res = smem_res + static_cast<uint32_t>(warp - 18) * kMlpResidualSlots * kPanelBytes;
+    const uint32_t res_full0 = smem_u32(&ctl.res_full[warp - 18][0]);
+    const int my_tiles = worker < p.row_tiles ? (p.row_tiles - worker + workers - 1) / workers : 0;
+    const uint32_t chunks = static_cast<uint32_t>(my_tiles) * kChunks;
+    const bool load_residual = !(probe_flags(p) & 1);
+    auto ask = [&](uint32_t n) {  // chunk n of this CTA's sequence into slot n % slots
+      if (n < chunks && elect_one()) {
+        const uint32_t slot = n & (kMlpResidualSlots - 1u);
+        const int m = worker + static_cast<int>(n / kChunks) * workers, c = static_cast<int>(n % kChunks);
+        if (load_residual) {
+          mbar_expect_tx_addr(res_full0 + 8 * slot, kPanelBytes);
+          tma_load_4d_addr(my_res + slot * kPanelBytes, &res_map, res_full0 + 8 * slot, c * 64, m * kTileM + quarter * 32, 0, 0);
+        } else {
+          mbar_arrive_addr(res_full0 + 8 * slot);
+        }
+      }
+    };
+    for (uint32_t n = 0; n < kMlpResidualSlots; ++n) ask(n);
+    uint32_t tile_it = 0, chunk_it = 0;
+    bool alive = true;
+    for (int m = worker; m < p.row_tiles && alive; m += workers, ++tile_it) {
+      if (!mbar_wait_warp(acc2_full, tile_it & 1u, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t raw[32], r[16];
+        tmem_load_32(lane_tmem + c * 32, raw);
+        tmem_load_wait();
+        if (c + 1 == kChunks) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_addr(acc2_empty);
+        }
+        if (probe_flags(p) & 2) continue;
+        const uint32_t bias_chunk = smem_bias2 + static_cast<uint32_t>(c * 32) * 4u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint64_t b0, b1;
+          load_bias_pairs(bias_chunk, i, b0, b1);
+          float v0, v1, v2, v3;
+          unpack2(add2(pack2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1])), b0), v0, v1);
+          unpack2(add2(pack2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3])), b1), v2, v3);
+          r[2 * i] = pack_bf16(v0, v1);
+          r[2 * i + 1] = pack_bf16(v2, v3);
+        }
+        {
+          const uint32_t slot = chunk_it & (kMlpResidualSlots - 1u);
+          if (!mbar_wait_warp(res_full0 + 8 * slot, (chunk_it / kMlpResidualSlots) & 1u, abort_flag, p.status, kStatusWaitFull)) {
+            alive = false;
+            break;
+          }
+          const uint32_t from = my_res + slot * kPanelBytes + row_at;
+#pragma unroll
+          for (uint32_t i = 0; i < 4; ++i) {
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(from ^ (i << 4)));
+            r[4 * i] = bf16x2_add(r[4 * i], v.x);
+            r[4 * i + 1] = bf16x2_add(r[4 * i + 1], v.y);
+            r[4 * i + 2] = bf16x2_add(r[4 * i + 2], v.z);
+            r[4 * i + 3] = bf16x2_add(r[4 * i + 3], v.w);
+          }
+          __syncwarp();  // every lane has read the slot
+          ask(chunk_it + kMlpResidualSlots);
+        }
+        const uint32_t panel = my_panels + (chunk_it & (kPanels - 1u)) * kPanelBytes;
+        ++chunk_it;
+        const uint32_t at = panel + row_at;
+        if (elect_one()) bulk_wait_read<kPanels - 1>();  // the store that last read this panel has finished with it
+        __syncwarp();
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at ^ (i << 4)), "r"(r[4 * i]), "r"(r[4 * i + 1]), "r"(r[4 * i + 2]),
+                       "r"(r[4 * i + 3])
+                       : "memory");
+        }
+        fence_async_proxy();
+        __syncwarp();
+        if (elect_one()) {
+          tma_store_4d(&out_map, panel, c * 64, m * kTileM + quarter * 32, 0, 0);
+          bulk_commit();
+        }
+      }
+    }
+    if (elect_one()) bulk_wait_read<0>();
+  }
+
+  if (ctl.abort_flag) {
+    // a wait ran out somewhere in this CTA: let copies in flight land before shared memory goes away
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemColumns);
+  }
+}
+
 // ---- host ------------------------------------------------------------------------------------------------------------
 
 int g_forced_block_n = 0;
@@ -1787,6 +2216,96 @@ int run_conv(int fmt, const void* x, const int8_t* act_exponent, const void* act
   return launch_conv_k<kFmtMx, 256>(maps, p, pl, s);
 }
 
+template <int KC>
+int launch_mlp(const CUtensorMap& x_map, const CUtensorMap& w1_map, const CUtensorMap& w2_map, const CUtensorMap& out_map,
+               const CUtensorMap& res_map, const MlpParams& p, int ctas, size_t smem, cudaStream_t stream) {
+  static bool configured[kMaxDevices] = {};
+  const int device = current_device();
+  if (device < 0 || device >= kMaxDevices || !configured[device]) {
+    const cudaError_t e = cudaFuncSetAttribute(mlp_kernel<KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (device >= 0 && device < kMaxDevices) configured[device] = true;
+  }
+  mlp_kernel<KC><<<ctas, kMlpThreads, smem, stream>>>(x_map, w1_map, w2_map, out_map, res_map, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int run_mlp(const void* x, const void* x_scales, const void* w1, const void* w1_scales, const void* bias1, const void* w2,
+            const void* w2_scales, const void* bias2, const void* residual, void* out, long long rows, int channels, int* status,
+            void* stream) {
+  if (rows < 0 || channels <= 0) return kBadArgument;
+  if (rows == 0) return kOk;
+  if (x == nullptr || x_scales == nullptr || w1 == nullptr || w1_scales == nullptr || bias1 == nullptr || w2 == nullptr ||
+      w2_scales == nullptr || bias2 == nullptr || residual == nullptr || out == nullptr) {
+    return kBadArgument;
+  }
+  if (channels != 128 && channels != 256) return kUnsupported;  // the second accumulator holds every output channel
+  if (rows > 0x7fffffffLL - kTileM) return kUnsupported;
+  for (const void* ptr : {x, x_scales, w1, w1_scales, bias1, w2, w2_scales, bias2, residual, static_cast<const void*>(out)}) {
+    if (!aligned16(ptr)) return kBadLayout;
+  }
+  const int kc = channels / 128, c = channels;
+  const uint32_t unit = static_cast<uint32_t>(kc) * (kMlpTile + 512u);
+  const uint32_t fixed = 1024u + kGeluSmemBytes + unit + 2u * (kMlpTile + 512u) + 4u * (kMlpPanels + kMlpResidualSlots) * kMlpPanelBytes + 3u * c * 4u;
+  int stages = static_cast<int>((kSmemLimit - fixed) / unit);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return kUnsupported;
+  const size_t smem = fixed + static_cast<size_t>(stages) * unit;
+
+  MlpParams p;
+  p.rows = static_cast<int>(rows);
+  p.row_tiles = static_cast<int>((rows + kTileM - 1) / kTileM);
+  p.stages = stages;
+  p.x_scales = static_cast<const uint8_t*>(x_scales);
+  p.w1_scales = static_cast<const uint8_t*>(w1_scales);
+  p.w2_scales = static_cast<const uint8_t*>(w2_scales);
+  p.bias1 = static_cast<const __nv_bfloat16*>(bias1);
+  p.bias2 = static_cast<const __nv_bfloat16*>(bias2);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.status = status;
+  p.poll_backoff_ns = (g_debug_flags & 32) ? 0u : 200u;
+  p.debug = g_debug_flags;
+
+  CUtensorMap x_map, w1_map, w2_map, out_map, res_map;
+  {
+    const uint64_t dims[4] = {static_cast<uint64_t>(c), static_cast<uint64_t>(rows), 1, 1};
+    const uint64_t strides[3] = {static_cast<uint64_t>(c), static_cast<uint64_t>(rows) * c, static_cast<uint64_t>(rows) * c};
+    const uint32_t box[4] = {128, static_cast<uint32_t>(kTileM), 1, 1};
+    const int rc = make_tensor_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(c), static_cast<uint64_t>(2 * c)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(c)};
+    const uint32_t box[2] = {128, 128};
+    const int rc = make_tensor_map(&w1_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w1, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(2 * c), static_cast<uint64_t>(c)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(2 * c)};
+    const uint32_t box[2] = {128, 128};
+    const int rc = make_tensor_map(&w2_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
+  {
+    const uint64_t row = static_cast<uint64_t>(c) * 2;
+    const uint64_t dims[4] = {row, static_cast<uint64_t>(rows), 1, 1};
+    const uint64_t strides[3] = {row, static_cast<uint64_t>(rows) * row, static_cast<uint64_t>(rows) * row};
+    const uint32_t box[4] = {64, 32, 1, 1};
+    const int rc = make_tensor_map(&out_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != kOk) return rc;
+    const int rcr = make_tensor_map(&res_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, residual, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rcr != kOk) return rcr;
+  }
+  const int device_sms = sm_count();
+  const int sms = g_max_ctas > 0 && g_max_ctas < device_sms ? g_max_ctas : device_sms;
+  const int ctas = p.row_tiles < sms ? p.row_tiles : sms;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return kc == 1 ? launch_mlp<1>(x_map, w1_map, w2_map, out_map, res_map, p, ctas, smem, s)
+                 : launch_mlp<2>(x_map, w1_map, w2_map, out_map, res_map, p, ctas, smem, s);
+}
+
 }  // namespace
 }  // namespace fim
 
@@ -1823,6 +2342,13 @@ extern "C" int fim_int8_conv2d_maxpool(const void* x, const void* weight, const 
 extern "C" int fim_bf16_conv2d(const void* x, const void* weight, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue,
                                void* out, int* status, void* stream) {
   return run_conv(kFmtBf16, x, nullptr, nullptr, weight, nullptr, nullptr, nullptr, geometry, epilogue, out, status, stream);
+}
+
+extern "C" int fim_mxfp8_gelu_mlp_residual(const void* x, const void* x_scales_swizzled, const void* w1, const void* w1_scales_swizzled,
+                                           const void* bias1, const void* w2, const void* w2_scales_swizzled, const void* bias2,
+                                           const void* residual, void* out, long long rows, int channels, int* status, void* stream) {
+  return run_mlp(x, x_scales_swizzled, w1, w1_scales_swizzled, bias1, w2, w2_scales_swizzled, bias2, residual, out, rows, channels, status,
+                 stream);
 }
 
 extern "C" int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]) {

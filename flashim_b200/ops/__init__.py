@@ -74,6 +74,10 @@ mxfp8_conv2d_bf16 = Op("mxfp8_conv2d_bf16", doc="(x bf16 [B, H, W, Cin], act_exp
                        "bias, *, act, residual, out_exponent, dynamic_out, out_fp32): a 1x1 mxfp8_conv2d_fused whose "
                        "activation quantiser (static exponents, or per pixel and 32 channels when act_exponent is None) "
                        "runs inside the conv kernel; the same bits as quantising first")
+mxfp8_gelu_mlp_residual = Op("mxfp8_gelu_mlp_residual", doc="(x E4M3 [..., C], x_scales uint8 swizzled, w1 E4M3 [2C, C], w1_scales, b1, "
+                             "w2 E4M3 [C, 2C], w2_scales, b2, residual bf16 [..., C]) -> bf16 [..., C]: the residual MLP of a refiner "
+                             "block (1x1 up conv + GELU + per-pixel requantisation, 1x1 down conv + residual) in one launch, "
+                             "the hidden tensor staying on chip; C = 128 or 256; the same bits as the two convs")
 int8_conv2d_accumulators = Op("int8_conv2d_accumulators", doc="(x, weight, kh, kw, sh, sw, ph, pw, dh, dw) -> int32 "
                               "[B, Ho, Wo, Cout]: the raw sums of int8_conv2d")
 

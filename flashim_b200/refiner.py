@@ -71,6 +71,12 @@ class RefinerBlock(nn.Module):
         """``x`` bf16 ``[B, H, W, C]`` -> bf16 ``[B, H, W, C]``."""
         b, h, w, c = x.shape
         q, s = ops.depthwise5x5_act_mxfp8(x.permute(0, 3, 1, 2), self.dw_weight, self.dw_bias, "gelu")
+        if c in (128, 256) and x.is_contiguous():
+            # up conv, GELU, requantisation, down conv and residual add in one launch: the hidden tensor stays on chip
+            # (the same bits as the two launches below)
+            return ops.mxfp8_gelu_mlp_residual(
+                q.view(b, h, w, c), s, self.up.weight.view(torch.float8_e4m3fn), self.up.weight_scales, self.up.bias,
+                self.down.weight.view(torch.float8_e4m3fn), self.down.weight_scales, self.down.bias, x)
         hq, hs = self.up(q.view(b, h, w, c), s, act="gelu", dynamic_out=True)
         return self.down(hq, hs, residual=x)
 

@@ -218,6 +218,19 @@ int fim_int8_conv2d_maxpool(const void* x, const void* weight, const float* a_sc
 int fim_bf16_conv2d(const void* x, const void* weight, const FimConvGeometry* geometry, const FimConvEpilogue* epilogue, void* out,
                     int* status, void* stream);
 
+/* The residual MLP of a refiner block in one launch: out = (quantise(GELU(x W1^T + b1)) W2^T + b2) + residual over `rows`
+ * pixels of `channels` (128 or 256, else FIM_ERR_UNSUPPORTED) channels. x: E4M3 [rows, C] with per-pixel scales
+ * (`x_scales_swizzled`, E8M0 bytes in the 128x4 swizzled layout over rows, as the depthwise producer writes them); w1 E4M3
+ * [2C, C], w2 E4M3 [C, 2C], their scales swizzled; b1 bf16 [2C], b2 bf16 [C]; residual and out bf16 [rows, C], dense. The
+ * hidden activations (bias -> bf16 -> GELU -> one E8M0 exponent per pixel and 32 channels -> E4M3) stay in shared memory
+ * as the operand of the second product. Bit-identical to fim_mxfp8_conv2d with FIM_ACT_GELU + FIM_OUT_E4M3_DYNAMIC
+ * followed by fim_mxfp8_conv2d with a residual. The counterpart in the reference keeps the hidden tile on chip the same
+ * way: _mxfp8_gelu_mlp_kernel (flashim/backends/triton/gemm.py:558-613, op flashim/ops/gemm.py:146-157), there with
+ * static scales and without the residual. */
+int fim_mxfp8_gelu_mlp_residual(const void* x, const void* x_scales_swizzled, const void* w1, const void* w1_scales_swizzled,
+                                const void* bias1, const void* w2, const void* w2_scales_swizzled, const void* bias2,
+                                const void* residual, void* out, long long rows, int channels, int* status, void* stream);
+
 /* Tile configuration the conv entry points would use for a geometry (for reports and tests): writes
  * {tile_rows, tile_cols, block_n, block_k, stages, ctas}. Returns 0 or FIM_ERR_UNSUPPORTED. */
 int fim_conv_plan(const FimConvGeometry* geometry, int int8, int per_pixel_scales, int plan[6]);
