@@ -1306,9 +1306,10 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
 // separate launches, the same epilogue arithmetic: the same bits. KC = C / 128 (1 or 2). 22 warps: TMA producer, MMA
 // issuer, 16 hidden-block warps, 4 output warps.
 constexpr uint32_t kMlpTile = 128u * 128u;  // bytes of one operand tile: 128 rows x 128 bytes of K
-constexpr int kMlpThreads = kThreads + 128;  // + four output warps (one per lane quarter of tensor memory)
+constexpr int kMlpOutWarps = 8;  // output warps: two per lane quarter of tensor memory, which take alternate 32-channel chunks
+constexpr int kMlpThreads = kThreads + 32 * kMlpOutWarps;
 constexpr uint32_t kMlpPanels = 2, kMlpPanelBytes = 32u * 64u;  // output panels per output warp: 32 rows x 32 bf16 channels
-constexpr uint32_t kMlpResidualSlots = 4;  // residual panels (same shape) each output warp keeps in flight
+constexpr uint32_t kMlpResidualSlots = 2;  // residual panels (same shape) each output warp keeps in flight
 struct MlpParams {
   int rows, row_tiles, stages;
   const uint8_t* x_scales;   // per-pixel scales of x: swizzled tiles, KC per row tile
@@ -1327,7 +1328,7 @@ struct MlpControl {
   uint64_t w_full[kMaxStages], w_empty[kMaxStages];
   uint64_t x_full, x_empty, acc1_full, acc1_empty, acc2_full, acc2_empty;
   uint64_t h_full[2], h_empty[2];
-  uint64_t res_full[4][kMlpResidualSlots];  // per output warp: its residual panels have landed
+  uint64_t res_full[kMlpOutWarps][kMlpResidualSlots];  // per output warp: its residual panels have landed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -1351,8 +1352,8 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
   const uint32_t smem_w = smem_x + kUnitBytes;
   const uint32_t smem_h = smem_w + static_cast<uint32_t>(p.stages) * kUnitBytes;
   const uint32_t smem_out = smem_h + 2u * kMlpTile;
-  const uint32_t smem_res = smem_out + 4u * kPanels * kPanelBytes;  // residual panels: kMlpResidualSlots per output warp
-  const uint32_t smem_xsf = smem_res + 4u * kMlpResidualSlots * kPanelBytes;
+  const uint32_t smem_res = smem_out + kMlpOutWarps * kPanels * kPanelBytes;  // residual panels: kMlpResidualSlots per output warp
+  const uint32_t smem_xsf = smem_res + kMlpOutWarps * kMlpResidualSlots * kPanelBytes;
   const uint32_t smem_wsf = smem_xsf + KC * 512u;
   const uint32_t smem_hsf = smem_wsf + static_cast<uint32_t>(p.stages) * KC * 512u;
   const uint32_t smem_bias1 = smem_hsf + 2u * 512u;  // fp32 [2C]
@@ -1372,12 +1373,12 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
     mbar_init(&ctl.acc1_full, 1);
     mbar_init(&ctl.acc1_empty, 16);
     mbar_init(&ctl.acc2_full, 1);
-    mbar_init(&ctl.acc2_empty, 4);
+    mbar_init(&ctl.acc2_empty, kMlpOutWarps);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ctl.h_full[b], 16);
       mbar_init(&ctl.h_empty[b], 1);
     }
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < kMlpOutWarps; ++w) {
       for (uint32_t i = 0; i < kMlpResidualSlots; ++i) mbar_init(&ctl.res_full[w][i], 1);
     }
     mbar_fence_init();
@@ -1617,7 +1618,9 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
     const uint32_t my_panels = smem_out + static_cast<uint32_t>(warp - 18) * kPanels * kPanelBytes;
     // 16-byte slot i of this lane's 64-byte panel row sits at row_at ^ (i << 4) (the swizzle a TMA store of such rows reads)
     const uint32_t row_at = static_cast<uint32_t>(lane) * 64u + ((((static_cast<uint32_t>(lane) * 64u) >> 7) & 3u) << 4);
-    constexpr int kChunks = 4 * KC;
+    constexpr int kShare = kMlpOutWarps / 4;  // warps per lane quarter: warp `turn` of them takes chunks turn, turn + kShare, ...
+    constexpr int kChunks = 4 * KC / kShare;   // chunks of a tile this warp handles
+    const int turn = (warp - 18) >> 2;
     // The residual of this warp's 32 pixels arrives by TMA, one panel of 32 channels per copy (the shape and swizzle of an
     // output panel), kMlpResidualSlots chunks ahead of its use; rows past the end of the tensor arrive as zeros. The
     // lane that issued a copy is the one that re-issues into the slot after the warp has read it.
@@ -1629,7 +1632,7 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
     auto ask = [&](uint32_t n) {  // chunk n of this CTA's sequence into slot n % slots
       if (n < chunks && elect_one()) {
         const uint32_t slot = n & (kMlpResidualSlots - 1u);
-        const int m = worker + static_cast<int>(n / kChunks) * workers, c = static_cast<int>(n % kChunks);
+        const int m = worker + static_cast<int>(n / kChunks) * workers, c = static_cast<int>(n % kChunks) * kShare + turn;
         if (load_residual) {
           mbar_expect_tx_addr(res_full0 + 8 * slot, kPanelBytes);
           tma_load_4d_addr(my_res + slot * kPanelBytes, &res_map, res_full0 + 8 * slot, c * 64, m * kTileM + quarter * 32, 0, 0);
@@ -1645,11 +1648,12 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
       if (!mbar_wait_warp(acc2_full, tile_it & 1u, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
+      for (int mine = 0; mine < kChunks; ++mine) {
+        const int c = mine * kShare + turn;
         uint32_t raw[32], r[16];
         tmem_load_32(lane_tmem + c * 32, raw);
         tmem_load_wait();
-        if (c + 1 == kChunks) {
+        if (mine + 1 == kChunks) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_addr(acc2_empty);
@@ -2246,7 +2250,7 @@ int run_mlp(const void* x, const void* x_scales, const void* w1, const void* w1_
   }
   const int kc = channels / 128, c = channels;
   const uint32_t unit = static_cast<uint32_t>(kc) * (kMlpTile + 512u);
-  const uint32_t fixed = 1024u + kGeluSmemBytes + unit + 2u * (kMlpTile + 512u) + 4u * (kMlpPanels + kMlpResidualSlots) * kMlpPanelBytes + 3u * c * 4u;
+  const uint32_t fixed = 1024u + kGeluSmemBytes + unit + 2u * (kMlpTile + 512u) + kMlpOutWarps * (kMlpPanels + kMlpResidualSlots) * kMlpPanelBytes + 3u * c * 4u;
   int stages = static_cast<int>((kSmemLimit - fixed) / unit);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return kUnsupported;
