@@ -588,7 +588,16 @@ def kernel_table(device, steps: int) -> list[dict]:
     bu = randn(2 * c, scale=0.02)
     add("conv_kernel<mxfp8> 1x1 up + bias + GELU + dynamic requant", f"8x{size}x{size}x{c} -> {2 * c}",
         lambda: fused(*nxtq(), wu, su, bu, 1, 1, 1, 1, 0, 0, 1, 1, act="gelu", dynamic_out=True),
-        2.0 * pixels * c * 2 * c, pixels * (c + 2 * c) * (1 + 1 / 32), "hbm", "conv_mxfp8_1x1_up_refiner_level_400x400x128")
+        2.0 * pixels * c * 2 * c, pixels * (c + 2 * c) * (1 + 1 / 32), "hbm", "conv_mxfp8_1x1_up_400x400x128")
+    # the same layer with its down conv in the same kernel (what the stack runs at 128 and 256 channels): the hidden tensor
+    # stays on chip, so the launch reads x and the residual and writes the block's output
+    wd = randn(c, 2 * c, dtype=e4m3, scale=0.05)
+    sd = swizzle_scales(torch.zeros(c, 2 * c // 32, dtype=torch.int8)).to(device)
+    bd = randn(c, scale=0.02)
+    residual = randn(n, size, size, c)
+    add("mlp_kernel<mxfp8> 1x1 up + GELU + requant + 1x1 down + residual", f"8x{size}x{size}x{c}",
+        lambda: ops.mxfp8_gelu_mlp_residual.get("sm100")(*nxtq(), wu, su, bu, wd, sd, bd, residual),
+        2.0 * pixels * c * 2 * c * 2, pixels * c * (1 + 1 / 32 + 2 + 2), "hbm", "mlp_mxfp8_refiner_level_400x400x128")
     return rows
 
 
