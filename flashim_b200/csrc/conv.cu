@@ -1561,15 +1561,28 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
     const uint32_t hsf_at = static_cast<uint32_t>(lane * 16 + quarter * 4 + group);
     const int my_tiles = worker < p.row_tiles ? (p.row_tiles - worker + workers - 1) / workers : 0;
     const uint32_t blocks = static_cast<uint32_t>(my_tiles) * HB;
+#if FIM_PROBE_BUILD
+    long long c_wait = 0, c_load = 0, c_math = 0, c_hwait = 0, c_write = 0;
+    const long long c_start = clock64();
+#endif
     for (uint32_t g = 0; g < blocks; ++g) {
+#if FIM_PROBE_BUILD
+      const long long c0 = clock64();
+#endif
       if (!mbar_wait_warp(acc1_full, g & 1u, abort_flag, p.status, kStatusWaitTmemFull, true, p.poll_backoff_ns)) break;
       tc_fence_after();
+#if FIM_PROBE_BUILD
+      const long long c1 = clock64();
+#endif
       uint32_t raw[32], r[16];
       tmem_load_32(lane_tmem, raw);
       tmem_load_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_addr(acc1_empty);  // the accumulator goes back before the long arithmetic
+#if FIM_PROBE_BUILD
+      const long long c2 = clock64();
+#endif
       const uint32_t bias_chunk = smem_bias1 + ((g & (HB - 1)) * 128u + static_cast<uint32_t>(group) * 32u) * 4u;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -1601,7 +1614,13 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
       }
       // the operand buffer of this hidden block: free once the second product that last read it has completed
       const uint32_t b = g & 1u;
+#if FIM_PROBE_BUILD
+      const long long c3 = clock64();
+#endif
       if (!mbar_wait_warp(h_empty0 + 8 * b, ((g >> 1) & 1u) ^ 1u, abort_flag, p.status, kStatusWaitEmpty)) break;
+#if FIM_PROBE_BUILD
+      const long long c4 = clock64();
+#endif
       const uint32_t tile_at = smem_h + b * kMlpTile;
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_at + h_at0), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_at + h_at1), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
@@ -1609,7 +1628,18 @@ mlp_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CU
       fence_async_proxy();  // the second product reads these bytes through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive_addr(h_full0 + 8 * b);
+#if FIM_PROBE_BUILD
+      const long long c5 = clock64();
+      c_wait += c1 - c0, c_load += c2 - c1, c_math += c3 - c2, c_hwait += c4 - c3, c_write += c5 - c4;
+#endif
     }
+#if FIM_PROBE_BUILD
+    if ((p.debug & 8192) && blockIdx.x == 0 && lane == 0 && (warp == 2 || warp == 17)) {
+      printf("hidden warp %d: %u blocks; per block wait %.0f load %.0f math %.0f buffer wait %.0f write %.0f clk; total %lld clk\n", warp, blocks,
+             double(c_wait) / blocks, double(c_load) / blocks, double(c_math) / blocks, double(c_hwait) / blocks, double(c_write) / blocks,
+             clock64() - c_start);
+    }
+#endif
   } else {
     // ===== output warps: two per lane quarter; bias, residual and bf16 rows of every other 32-channel chunk of its 32 pixels.
     // Few instructions but a long chain per chunk (tensor-memory load, residual panel, store): warps of their own keep

@@ -28,7 +28,8 @@ extern "C" {
  * A library built with -DFIM_PROBE_BUILD=1 (never shipped) also honours bits 1, 2, 4, 8 (skip activation loads / weight
  * loads / stores / scale copies), which make results invalid, and 8192 (the MMA warp of CTA 0 prints its cycle counts).
  * `max_ctas` and flag 32 also apply to fim_mxfp8_gelu_mlp_residual; in a probe build its bits are 1 (no residual loads),
- * 2 (the output warps only drain the accumulator) and 4 (no GELU / requantisation arithmetic), results invalid. */
+ * 2 (the output warps only drain the accumulator) and 4 (no GELU / requantisation arithmetic), results invalid, and 8192
+ * (two of its hidden-block warps print their cycle counts per block). */
 void fim_conv_tune(int block_n, int max_ctas, int flags);
 
 /* Depthwise launches: `variant` selects the thread layout (0 = automatic; 1: four columns per lane, four warps, three
