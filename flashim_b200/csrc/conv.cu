@@ -26,9 +26,10 @@ namespace fim {
 namespace {
 
 constexpr int kThreads = 576;  // producer warp, MMA warp, 16 epilogue warps
-// A layer that takes bf16 activations adds four converter warps, which quantise each 128 x 128 tile on its way from the
-// TMA landing ring into the K-major stage the MMAs read.
-constexpr int kConverterWarps = 4, kConvertThreads = kThreads + 32 * kConverterWarps;
+// A layer that takes bf16 activations adds eight converter warps, which quantise each 128 x 128 tile on its way from the
+// TMA landing ring into the K-major stage the MMAs read (four warps measured 10 to 18 % slower: the quantiser arithmetic
+// of a tile, not its bytes, is what such a layer waits for).
+constexpr int kConverterWarps = 8, kConvertThreads = kThreads + 32 * kConverterWarps;
 constexpr int kRawStages = 2;                       // landing ring of bf16 tiles
 constexpr uint32_t kRawBytes = 128u * 128u * 2u;    // 128 pixels x 128 channels of bf16
 constexpr int kTileM = 128;
@@ -885,7 +886,7 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
     }
   } else if (CONVERT && warp >= 2 + 16) {
     // ===== converter: bf16 landing tile -> E4M3 K-major stage (+ the stage's activation-scale tile) =====
-    // 1024 pieces of 16 channels per tile, eight per thread: piece t = (row t / 8, channels 16 * (t % 8) ...); the two
+    // 1024 pieces of 16 channels per tile, four per thread: piece t = (row t / 8, channels 16 * (t % 8) ...); the two
     // lanes of a 32-channel block are neighbours. A warp reads 1 KB of consecutive shared memory per step and writes four
     // rows of the 128-byte-swizzled stage, both without bank conflicts.
     const int ctid = static_cast<int>(threadIdx.x) - 32 * (2 + 16);
@@ -901,9 +902,10 @@ conv_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__
         }
         const uint32_t from = smem_raw + raw_s * kRawBytes, to = smem_a + s * kABytes, scale_tile = smem_sfa + s * 512;
         const int static_e = p.convert_static ? static_cast<int>(__ldg(p.act_exponent + j * 4 + group)) : 0;
+        constexpr int kRowsPerPass = 4 * kConverterWarps;  // eight threads per row
 #pragma unroll 2
-        for (int i = 0; i < 8; ++i) {
-          const int row = i * 16 + (ctid >> 3);
+        for (int i = 0; i < kTileM / kRowsPerPass; ++i) {
+          const int row = i * kRowsPerPass + (ctid >> 3);
           uint32_t w[8];
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(from + row * 256 + piece * 32));
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(from + row * 256 + piece * 32 + 16));
